@@ -1,0 +1,157 @@
+/*
+ * pyptx_b200 -- C ABI of the B200 (sm_100a) kernel library.
+ *
+ * This header is the drop-in boundary.  It plays the role that the launch
+ * shim plays in the reference project: a process-local registry of
+ * "handles", and one generic launch entry that takes raw device pointers
+ * in inputs-then-outputs order plus a CUDA stream.
+ *
+ * Differences from the reference shim, by design:
+ *   - a handle names an ahead-of-time compiled kernel + its static shape,
+ *     not a JIT-loaded CUfunction; nothing is compiled at run time;
+ *   - TMA descriptors are encoded on the host per launch and passed to the
+ *     kernel by value, so no device slot is patched and two launches with
+ *     different pointers never race;
+ *   - every device-side wait is bounded; a wait that gives up records a
+ *     status word that pb200_device_status() returns.
+ *
+ * Conventions (same as the reference shim, pyptx/_shim/pyptx_launch.cc:316-467):
+ *   - functions return 0 on success and a negative code on failure;
+ *   - `err_out`, when not NULL, points at a caller-owned buffer of at least
+ *     PB200_ERR_LEN bytes that receives a NUL-terminated message;
+ *   - nothing throws or aborts across this boundary;
+ *   - launches are asynchronous on `stream`; the library never synchronises
+ *     on the launch path and allocates no device memory.
+ *
+ * All pointers given to pb200_launch_raw must be device pointers on the
+ * current CUDA device, 16-byte aligned, to contiguous row-major arrays.
+ */
+#ifndef PYPTX_B200_H_
+#define PYPTX_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PB200_ERR_LEN 128
+
+#if defined(__GNUC__)
+#define PB200_API __attribute__((visibility("default")))
+#else
+#define PB200_API
+#endif
+
+/* ---- error codes (0..-8 mirror pyptx/_shim/pyptx_launch.cc:316-467) ---- */
+#define PB200_OK                    0
+#define PB200_ERR_NO_CUDA          -1  /* CUDA runtime / driver not usable        */
+#define PB200_ERR_UNKNOWN_HANDLE   -2  /* handle not in the registry              */
+#define PB200_ERR_NO_TMA_API       -3  /* cuTensorMapEncodeTiled not resolvable   */
+#define PB200_ERR_ARG_COUNT        -4  /* wrong number of buffer pointers         */
+#define PB200_ERR_TMA_ENCODE       -5  /* tensor-map encode failed                */
+#define PB200_ERR_LAUNCH           -7  /* kernel launch failed                    */
+#define PB200_ERR_CLUSTER          -8  /* cluster launch unsupported              */
+#define PB200_ERR_BAD_SHAPE        -9  /* shape / option rejected at create time  */
+#define PB200_ERR_MISALIGNED      -10  /* a buffer pointer is NULL or not 16-B aligned */
+#define PB200_ERR_DEVICE_TIMEOUT  -11  /* a bounded device-side wait gave up      */
+#define PB200_ERR_BAD_KERNEL      -12  /* unknown kernel id                       */
+
+/* ---- kernel ids: each names one reference entry point ------------------ */
+/* build_rms_norm            examples/blackwell/rms_norm.py:26 (body examples/hopper/rms_norm.py:63-182)
+ *   dims = {B, N}            fparams = {eps}
+ *   buffers: x[B,N] f32, w[N] f32 -> y[B,N] f32                                   */
+#define PB200_K_RMS_NORM       1
+/* build_layer_norm          examples/blackwell/layer_norm.py:32 (body examples/hopper/layer_norm.py:57-225)
+ *   dims = {B, N}            fparams = {eps}
+ *   buffers: x[B,N], w[N], b[N] f32 -> y[B,N] f32                                 */
+#define PB200_K_LAYER_NORM     2
+/* build_fused_silu_mul      examples/blackwell/swiglu.py:32 (body examples/hopper/swiglu.py:48-156)
+ *   dims = {M, F}
+ *   buffers: gate[M,F], up[M,F] f32 -> out[M,F] f32                               */
+#define PB200_K_SWIGLU         3
+/* build_softmax             examples/hopper/softmax.py:49-182
+ *   dims = {B, N}
+ *   buffers: x[B,N] f32 -> y[B,N] f32                                             */
+#define PB200_K_SOFTMAX        4
+/* build_gemm                examples/blackwell/gemm_highperf_blackwell.py:69-313
+ *   dims = {M, N, K}         flags: PB200_F_OUT_BF16
+ *   buffers: A[M,K] bf16, B_T[N,K] bf16 -> D[M,N] f32 (or bf16)                   */
+#define PB200_K_GEMM_1SM       5
+/* build_gemm_2sm            examples/blackwell/gemm_highperf_blackwell.py:902-1246
+ *   same dims / buffers as PB200_K_GEMM_1SM; M must divide by 256                 */
+#define PB200_K_GEMM_2SM       6
+/* build_grouped_gemm        examples/blackwell/grouped_gemm.py:61-289
+ *   dims = {G, M, N, K}      flags: PB200_F_OUT_BF16
+ *   buffers: A[G*M,K] bf16, B_T[G*N,K] bf16 -> C[G*M,N] f32 (or bf16)             */
+#define PB200_K_GROUPED_GEMM   7
+/* build_flash_attention_hopper  examples/hopper/experimental/flash_attention_hopper.py:44-465
+ *   dims = {batch*heads, M_q, N_seq, head_dim}   fparams = {sm_scale}
+ *   flags: PB200_F_CAUSAL, PB200_F_OUT_BF16, PB200_F_K_TRANSPOSED
+ *   buffers: Q[BH,M_q,d] bf16, K[BH,N_seq,d] bf16 (or K_t[BH,d,N_seq] with
+ *            PB200_F_K_TRANSPOSED, the reference's layout), V[BH,N_seq,d] bf16
+ *            -> O[BH,M_q,d] f32 (or bf16)                                         */
+#define PB200_K_FLASH_ATTN     8
+
+/* ---- create-time flags -------------------------------------------------- */
+#define PB200_F_OUT_BF16       (1ull << 0)  /* round the output to bf16            */
+#define PB200_F_CAUSAL         (1ull << 1)  /* attention: lower-triangular mask    */
+#define PB200_F_K_TRANSPOSED   (1ull << 2)  /* attention: K given as (d, N_seq)    */
+
+/* Launch geometry of a handle, as the reference's Kernel object exposes it
+ * (pyptx/kernel.py:402-447: grid, block, cluster, smem). */
+typedef struct pb200_geometry {
+    uint32_t grid[3];
+    uint32_t block[3];
+    uint32_t cluster[3];
+    uint32_t smem_bytes;
+    uint32_t n_inputs;
+    uint32_t n_outputs;
+} pb200_geometry;
+
+/* Registers a (kernel, static shape, options) record and returns a handle
+ * > 0, or a negative error code.  Replaces pyptx_shim_register_launch +
+ * pyptx_shim_add_scalar_param + pyptx_shim_add_tma_spec
+ * (pyptx/_shim/pyptx_launch.cc:239-285): geometry, scalar parameters and
+ * tensor-map layouts all follow from (kernel_id, dims, fparams, flags). */
+PB200_API int64_t pb200_create(int32_t kernel_id,
+                     const int64_t* dims, size_t n_dims,
+                     const double* fparams, size_t n_fparams,
+                     uint64_t flags, char* err_out);
+
+/* Launches the kernel behind `handle` on `stream` (a cudaStream_t / CUstream
+ * passed as an integer).  `buffer_ptrs` holds n_buffers device pointers:
+ * the inputs in spec order, then the outputs.
+ * Replaces pyptx_shim_launch_raw (pyptx/_shim/pyptx_launch.cc:484-492);
+ * same argument list, same return convention. */
+PB200_API int pb200_launch_raw(int64_t handle, uint64_t stream,
+                     void** buffer_ptrs, size_t n_buffers, char* err_out);
+
+/* Fills `out` with the launch geometry of `handle`.
+ * Counterpart of the Kernel.grid/.block/.cluster/.smem accessors
+ * (pyptx/kernel.py:402-447). */
+PB200_API int pb200_geometry_of(int64_t handle, pb200_geometry* out);
+
+/* Registry maintenance: pyptx_shim_has_handle, pyptx_shim_registry_size,
+ * pyptx_shim_clear_registry (pyptx/_shim/pyptx_launch.cc:287-301). */
+PB200_API int    pb200_has_handle(int64_t handle);
+PB200_API size_t pb200_registry_size(void);
+PB200_API void   pb200_clear_registry(void);
+PB200_API int    pb200_destroy(int64_t handle);
+
+/* Synchronises the current device and returns the device-side status word:
+ * 0 if no bounded wait has given up since the last call, else
+ * PB200_ERR_DEVICE_TIMEOUT with a description in err_out.  Reading clears it.
+ * The reference has no counterpart: its device waits are unbounded
+ * (pyptx/ptx.py:2311-2337). */
+PB200_API int pb200_device_status(char* err_out);
+
+/* Library version and the architecture the kernels were compiled for. */
+PB200_API const char* pb200_version(void);
+PB200_API const char* pb200_arch(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PYPTX_B200_H_ */

@@ -1,0 +1,465 @@
+// bf16 GEMM for sm_100a on the 5th-generation tensor cores:
+//   D[M,N] = A[M,K] * B_T[N,K]^T,  fp32 accumulation in TMEM, f32 or bf16 output.
+// One kernel template covers the three reference entry points
+//   build_gemm          (1-SM MMA, 128x256 tile per CTA)
+//   build_gemm_2sm      (cta_group::2 MMA, 256x256 tile per 2-CTA cluster)
+//   build_grouped_gemm  (G independent problems stacked along the row axis)
+// (examples/blackwell/gemm_highperf_blackwell.py:69-313, :902-1246,
+//  examples/blackwell/grouped_gemm.py:61-289).
+//
+// Structure (what differs from the reference's kernels and why):
+//   * persistent: one CTA (or CTA pair) per SM walks a static list of output
+//     tiles, so barrier setup, TMEM allocation and pipeline fill are paid once
+//     per SM instead of once per tile;
+//   * warp specialised: warp 0 = TMA producer, warp 1 = MMA issuer (+ TMEM
+//     owner), warps 2-5 = epilogue.  Producer and issuer are single threads;
+//   * the accumulator is double buffered in TMEM (2 x BN fp32 columns, the
+//     whole 512 when BN = 256), so the epilogue of tile i overlaps the main loop
+//     of tile i+1;
+//   * shared-memory ring slots are released by tcgen05.commit, i.e. when the
+//     MMAs that read them have retired, never right after issue;
+//   * the epilogue goes TMEM -> registers -> swizzled shared memory -> TMA
+//     store, one 32-row x 128-byte box per warp, so every global write is a full
+//     128-byte line;
+//   * tiles are rasterised in bands of `band` M-tiles so that the ~148 tiles in
+//     flight share A and B panels through L2;
+//   * tensor maps are kernel parameters (__grid_constant__), encoded per launch;
+//   * every mbarrier wait is bounded and reports through a status word.
+//
+// 2-SM protocol: both CTAs of a pair load their own 128 rows of A and their own
+// BN/2 rows of B_T with cta_group::2 TMA loads that signal the leader's "full"
+// barrier; the leader (cluster rank 0) issues the M=256 MMAs, which read both
+// CTAs' shared memory and write both CTAs' TMEM; it releases a ring slot with
+// two commits, one to its own "empty" barrier and one to the peer's (address
+// from mapa); epilogue warps of both CTAs arrive on the leader's "tmem empty"
+// barrier.  No copy in this file is multicast.
+#include "common.cuh"
+#include "ptx.cuh"
+
+#include <cuda_bf16.h>
+
+#include <atomic>
+
+namespace pb200 {
+namespace {
+
+using namespace ptx;
+
+constexpr int BM = 128;          // rows per CTA tile (TMEM lanes)
+constexpr int BK = 64;           // bf16 elements per k-tile = one 128-byte swizzle row
+constexpr int UMMA_K = 16;       // K per tcgen05.mma for 16-bit operands
+constexpr int kThreads = 192;    // 6 warps
+constexpr int kEpiWarps = 4;
+constexpr int kStageRows = 32;   // rows per epilogue store box (one warp)
+constexpr int kStageBytes = kStageRows * 128;  // 4 KiB, swizzle-128B image
+constexpr uint32_t kDebugDirectStore = 1u << 16;  // create flag: bypass the TMA-store epilogue
+
+struct GemmShape {
+    int tiles_m;      // tiles along M per group (a tile is BM*CTA_GROUP rows)
+    int tiles_n;
+    int k_tiles;
+    int groups;
+    int rows_per_group_a;   // M  (row offset of group g in A and D is g*M)
+    int rows_per_group_b;   // N  (row offset of group g in B_T is g*N)
+    int band;               // M-tiles per raster band
+    int n_total;            // leading dimension of D (elements)
+};
+
+template <int BN, int CTA_GROUP>
+struct SmemPlan {
+    static constexpr int kBRows = BN / CTA_GROUP;            // rows of B_T this CTA loads
+    static constexpr int kABytes = BM * BK * 2;              // 16 KiB
+    static constexpr int kBBytes = kBRows * BK * 2;
+    static constexpr int kStage = kABytes + kBBytes;
+    static constexpr int kEpiBytes = kEpiWarps * 2 * kStageBytes;   // 32 KiB
+    static constexpr int kBarBytes = 1024;
+    static constexpr int kBudget = 227 * 1024 - 1024;        // minus alignment slack
+    static constexpr int kStagesMax = (kBudget - kEpiBytes - kBarBytes) / kStage;
+    static constexpr int kStages = kStagesMax > 8 ? 8 : kStagesMax;
+    static constexpr int kTotal = kStages * kStage + kEpiBytes + kBarBytes + 1024;
+    static constexpr uint32_t kTxBytes = (uint32_t)kStage * CTA_GROUP;
+};
+
+// tile index -> (group, m-tile, n-tile).  Within a group, tiles are numbered
+// band by band: a band is `band` consecutive M-tiles, walked M-fastest.
+__device__ __forceinline__ void tile_coords(const GemmShape& s, int t, int& g, int& tm, int& tn) {
+    const int per_group = s.tiles_m * s.tiles_n;
+    g = t / per_group;
+    int r = t - g * per_group;
+    const int band_tiles = s.band * s.tiles_n;
+    const int b = r / band_tiles;
+    r -= b * band_tiles;
+    const int m0 = b * s.band;
+    const int width = min(s.band, s.tiles_m - m0);
+    tn = r / width;
+    tm = m0 + (r - tn * width);
+}
+
+template <int BN, int CTA_GROUP, typename OutT, bool DIRECT>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
+            const __grid_constant__ CUtensorMap tmap_b,
+            const __grid_constant__ CUtensorMap tmap_d,
+            OutT* __restrict__ d_ptr, GemmShape shape, int* status, int kernel_id) {
+    using Plan = SmemPlan<BN, CTA_GROUP>;
+    constexpr int kStages = Plan::kStages;
+    constexpr int kChunkCols = 128 / (int)sizeof(OutT);     // columns per 128-byte store row
+    constexpr int kChunks = BN / kChunkCols;
+    constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+    constexpr uint32_t kIdesc = make_idesc_f16(BM * CTA_GROUP, BN);
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t s_a = smem_base;
+    const uint32_t s_b = s_a + kStages * Plan::kABytes;
+    const uint32_t s_epi = s_b + kStages * Plan::kBBytes;
+    const uint32_t s_bar = s_epi + Plan::kEpiBytes;
+    const uint32_t bar_full = s_bar;                       // [kStages]
+    const uint32_t bar_empty = bar_full + 8 * kStages;     // [kStages]
+    const uint32_t bar_tfull = bar_empty + 8 * kStages;    // [2]
+    const uint32_t bar_tempty = bar_tfull + 16;            // [2]
+    const uint32_t s_tmem_slot = bar_tempty + 16;
+    const uint32_t s_abort = s_tmem_slot + 8;
+    volatile uint32_t* tmem_slot_gen = (volatile uint32_t*)(smem_gen + (s_tmem_slot - smem_base));
+    volatile int* abort_gen = (volatile int*)(smem_gen + (s_abort - smem_base));
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t cta_rank = CTA_GROUP == 2 ? cluster_ctarank() : 0u;
+    const bool is_leader = cta_rank == 0;
+    const int unit = CTA_GROUP == 2 ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;      // tile walker id
+    const int n_units = CTA_GROUP == 2 ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+    const int n_tiles = shape.groups * shape.tiles_m * shape.tiles_n;
+
+    WaitCtx ctx{status, abort_gen, kernel_id};
+
+    if (threadIdx.x == 0) {
+        *abort_gen = 0;
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar_tfull + 8 * b, 1);
+            mbar_init(bar_tempty + 8 * b, kEpiWarps * CTA_GROUP);
+        }
+        fence_mbarrier_init();
+        fence_proxy_async_smem();
+        prefetch_tmap(&tmap_a);
+        prefetch_tmap(&tmap_b);
+        if (!DIRECT) prefetch_tmap(&tmap_d);
+    }
+    if (warp == 1) {
+        tmem_alloc<CTA_GROUP>(s_tmem_slot, kTmemCols);
+        tmem_relinquish<CTA_GROUP>();
+    }
+    tc_fence_before_sync();
+    if (CTA_GROUP == 2) cluster_sync_all(); else __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot_gen;
+
+    if (warp == 0) {
+        // ------------------------- TMA producer -------------------------
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 0;
+            const uint32_t full_leader = CTA_GROUP == 2 ? map_to_cta(bar_full, 0) : bar_full;
+            bool ok = true;
+            for (int t = unit; t < n_tiles && ok; t += n_units) {
+                int g, tm, tn;
+                tile_coords(shape, t, g, tm, tn);
+                const int row_a = g * shape.rows_per_group_a + (tm * CTA_GROUP + (int)cta_rank) * BM;
+                const int row_b = g * shape.rows_per_group_b + tn * BN + (int)cta_rank * Plan::kBRows;
+                for (int kt = 0; kt < shape.k_tiles; ++kt) {
+                    if (!(ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, ctx, 1))) break;
+                    const uint32_t dst_a = s_a + stage * Plan::kABytes;
+                    const uint32_t dst_b = s_b + stage * Plan::kBBytes;
+                    if (CTA_GROUP == 1) {
+                        mbar_arrive_expect_tx(bar_full + 8 * stage, Plan::kTxBytes);
+                        tma_load_2d(dst_a, &tmap_a, bar_full + 8 * stage, kt * BK, row_a);
+                        tma_load_2d(dst_b, &tmap_b, bar_full + 8 * stage, kt * BK, row_b);
+                    } else {
+                        if (is_leader) mbar_arrive_expect_tx(bar_full + 8 * stage, Plan::kTxBytes);
+                        tma_load_2d_pair(dst_a, &tmap_a, full_leader + 8 * stage, kt * BK, row_a);
+                        tma_load_2d_pair(dst_b, &tmap_b, full_leader + 8 * stage, kt * BK, row_b);
+                    }
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------- MMA issuer ---------------------------
+        if (lane == 0 && is_leader) {
+            int stage = 0; uint32_t phase = 0;
+            const uint32_t empty_peer = CTA_GROUP == 2 ? map_to_cta(bar_empty, 1) : 0u;
+            const uint32_t tfull_peer = CTA_GROUP == 2 ? map_to_cta(bar_tfull, 1) : 0u;
+            bool ok = true;
+            int local = 0;
+            for (int t = unit; t < n_tiles && ok; t += n_units, ++local) {
+                const int buf = local & 1;
+                const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
+                if (!(ok = mbar_wait(bar_tempty + 8 * buf, acc_phase ^ 1u, ctx, 2))) break;
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+                for (int kt = 0; kt < shape.k_tiles; ++kt) {
+                    if (!(ok = mbar_wait(bar_full + 8 * stage, phase, ctx, 3))) break;
+                    tc_fence_after_sync();
+                    const uint64_t da = make_desc_kmajor_sw128(s_a + stage * Plan::kABytes);
+                    const uint64_t db = make_desc_kmajor_sw128(s_b + stage * Plan::kBBytes);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // +32 bytes along K inside the 128-byte swizzle row = +2 in the encoded address.
+                        umma_f16_ss<CTA_GROUP>(d_tmem, da + 2 * k, db + 2 * k, kIdesc, (kt | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit<CTA_GROUP>(bar_empty + 8 * stage);
+                    if (CTA_GROUP == 2) umma_commit<CTA_GROUP>(empty_peer + 8 * stage);
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                umma_commit<CTA_GROUP>(bar_tfull + 8 * buf);
+                if (CTA_GROUP == 2) umma_commit<CTA_GROUP>(tfull_peer + 8 * buf);
+            }
+        }
+    } else {
+        // ------------------------- epilogue (warps 2..5) -----------------
+        const int q = warp & 3;                         // TMEM lane quarter this warp may read
+        const int ew = warp - 2;                        // staging buffer owner index
+        const uint32_t stage_buf = s_epi + (uint32_t)ew * 2u * kStageBytes;
+        const uint32_t tempty_leader = CTA_GROUP == 2 ? map_to_cta(bar_tempty, 0) : bar_tempty;
+        bool ok = true;
+        int local = 0;
+        int flip = 0;
+        for (int t = unit; t < n_tiles && ok; t += n_units, ++local) {
+            int g, tm, tn;
+            tile_coords(shape, t, g, tm, tn);
+            const int buf = local & 1;
+            const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
+            const int row0 = g * shape.rows_per_group_a + (tm * CTA_GROUP + (int)cta_rank) * BM + q * 32;
+            const int col0 = tn * BN;
+            ok = mbar_wait(bar_tfull + 8 * buf, acc_phase, ctx, 4);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
+#pragma unroll 1
+            for (int c = 0; c < kChunks; ++c) {
+                uint32_t v[32];
+                if (sizeof(OutT) == 4) {
+                    tmem_ld_32x32b_x32(t_row + (uint32_t)(c * 32), v);
+                    tmem_ld_wait();
+                } else {
+                    uint32_t lo[32], hi[32];
+                    tmem_ld_32x32b_x32(t_row + (uint32_t)(c * 64), lo);
+                    tmem_ld_32x32b_x32(t_row + (uint32_t)(c * 64 + 32), hi);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(lo[2 * i]), __uint_as_float(lo[2 * i + 1]));
+                        v[i] = *reinterpret_cast<uint32_t*>(&p);
+                        __nv_bfloat162 r = __floats2bfloat162_rn(__uint_as_float(hi[2 * i]), __uint_as_float(hi[2 * i + 1]));
+                        v[16 + i] = *reinterpret_cast<uint32_t*>(&r);
+                    }
+                }
+                if (c == kChunks - 1) {
+                    // All TMEM reads of this accumulator are done: hand it back to the MMA issuer.
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (CTA_GROUP == 2) mbar_arrive_cluster(tempty_leader + 8 * buf);
+                        else mbar_arrive(bar_tempty + 8 * buf);
+                    }
+                }
+                if (DIRECT) {
+                    OutT* dst = d_ptr + (size_t)(row0 + lane) * shape.n_total + col0 + c * kChunkCols;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        reinterpret_cast<uint4*>(dst)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                } else {
+                    const uint32_t sb = stage_buf + (uint32_t)flip * kStageBytes;
+                    // The store that last read this buffer was issued two chunks ago.
+                    if (lane == 0) tma_store_wait_read<1>();
+                    __syncwarp();
+                    const uint32_t row_addr = sb + (uint32_t)lane * 128u;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        st_shared_v4(row_addr + (uint32_t)((j ^ (lane & 7)) << 4),
+                                     v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&tmap_d, sb, col0 + c * kChunkCols, row0);
+                        tma_store_commit();
+                    }
+                    flip ^= 1;
+                }
+            }
+        }
+        if (!DIRECT && lane == 0) tma_store_wait_all<0>();
+    }
+
+    // ------------------------- teardown --------------------------------------
+    tc_fence_before_sync();
+    if (CTA_GROUP == 2) cluster_sync_all(); else __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after_sync();
+        tmem_dealloc<CTA_GROUP>(tmem_base, kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+int pick_bn(int64_t n) {
+    if (n % 256 == 0) return 256;
+    if (n % 128 == 0) return 128;
+    if (n % 64 == 0) return 64;
+    return 0;
+}
+
+template <int BN, int CTA_GROUP, typename OutT, bool DIRECT>
+int launch_variant(const Record& r, cudaStream_t stream, void** p, const GemmShape& shape, char* err) {
+    using Plan = SmemPlan<BN, CTA_GROUP>;
+    auto kernel = gemm_kernel<BN, CTA_GROUP, OutT, DIRECT>;
+    static std::atomic<uint64_t> attr_set{0};   // bit per device
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!(attr_set.load(std::memory_order_relaxed) & (1ull << (dev & 63)))) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::kTotal);
+        if (e != cudaSuccess) { set_err(err, "cudaFuncSetAttribute(smem=%d): %s", Plan::kTotal, cudaGetErrorString(e)); return PB200_ERR_LAUNCH; }
+        attr_set.fetch_or(1ull << (dev & 63), std::memory_order_relaxed);
+    }
+    const int64_t G = r.kernel_id == PB200_K_GROUPED_GEMM ? r.dims[0] : 1;
+    const int64_t M = r.dims[r.n_dims - 3], N = r.dims[r.n_dims - 2], K = r.dims[r.n_dims - 1];
+    CUtensorMap ta, tb, td;
+    {
+        uint64_t dims[2] = {(uint64_t)K, (uint64_t)(G * M)};
+        uint64_t str[1] = {(uint64_t)K * 2};
+        uint32_t box[2] = {BK, BM};
+        int rc = make_tensor_map(&ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p[0], dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, err);
+        if (rc) return rc;
+    }
+    {
+        uint64_t dims[2] = {(uint64_t)K, (uint64_t)(G * N)};
+        uint64_t str[1] = {(uint64_t)K * 2};
+        uint32_t box[2] = {BK, (uint32_t)Plan::kBRows};
+        int rc = make_tensor_map(&tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p[1], dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, err);
+        if (rc) return rc;
+    }
+    {
+        uint64_t dims[2] = {(uint64_t)N, (uint64_t)(G * M)};
+        uint64_t str[1] = {(uint64_t)N * sizeof(OutT)};
+        uint32_t box[2] = {128 / sizeof(OutT), kStageRows};
+        int rc = make_tensor_map(&td, sizeof(OutT) == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                                 2, p[2], dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, err);
+        if (rc) return rc;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(r.geom.grid[0], 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = Plan::kTotal;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CTA_GROUP;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    OutT* d_ptr = (OutT*)p[2];
+    int* status = device_status_ptr();
+    int kid = r.kernel_id;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, td, d_ptr, shape, status, kid);
+    if (e != cudaSuccess) {
+        set_err(err, "gemm launch failed (BN=%d cta_group=%d grid=%u smem=%d): %s", BN, CTA_GROUP, r.geom.grid[0],
+                Plan::kTotal, cudaGetErrorString(e));
+        return CTA_GROUP == 2 ? PB200_ERR_CLUSTER : PB200_ERR_LAUNCH;
+    }
+    return PB200_OK;
+}
+
+GemmShape make_shape(const Record& r, int bn, int cta_group) {
+    const int64_t G = r.kernel_id == PB200_K_GROUPED_GEMM ? r.dims[0] : 1;
+    const int64_t M = r.dims[r.n_dims - 3], N = r.dims[r.n_dims - 2], K = r.dims[r.n_dims - 1];
+    GemmShape s;
+    s.tiles_m = (int)(M / (BM * cta_group));
+    s.tiles_n = (int)(N / bn);
+    s.k_tiles = (int)(K / BK);
+    s.groups = (int)G;
+    s.rows_per_group_a = (int)M;
+    s.rows_per_group_b = (int)N;
+    int band = (int)r.dims[7];            // stored by plan_gemm
+    s.band = band < 1 ? 1 : (band > s.tiles_m ? s.tiles_m : band);
+    s.n_total = (int)N;
+    return s;
+}
+
+}  // namespace
+
+// dims: {M,N,K} (+ optional band) for the dense kernels, {G,M,N,K} (+ optional band) for grouped.
+int plan_gemm(Record& r, char* err) {
+    const bool grouped = r.kernel_id == PB200_K_GROUPED_GEMM;
+    const int need = grouped ? 4 : 3;
+    if (r.n_dims != need && r.n_dims != need + 1) {
+        set_err(err, "gemm kernel %d needs %d dims (+1 optional raster band), got %d", r.kernel_id, need, r.n_dims);
+        return PB200_ERR_BAD_SHAPE;
+    }
+    int64_t band = 16;
+    if (r.n_dims == need + 1) { band = r.dims[need]; r.n_dims = need; }
+    if (band < 1) { set_err(err, "raster band must be at least 1"); return PB200_ERR_BAD_SHAPE; }
+    r.dims[7] = band;
+    const int64_t G = grouped ? r.dims[0] : 1;
+    const int64_t M = r.dims[need - 3], N = r.dims[need - 2], K = r.dims[need - 1];
+    const int cta_group = r.kernel_id == PB200_K_GEMM_2SM ? 2 : 1;
+    if (G < 1 || M < 1 || N < 1 || K < 1) { set_err(err, "G, M, N, K must be positive"); return PB200_ERR_BAD_SHAPE; }
+    if (M % (BM * cta_group) != 0) { set_err(err, "M=%lld must be divisible by %d", (long long)M, BM * cta_group); return PB200_ERR_BAD_SHAPE; }
+    if (K % BK != 0) { set_err(err, "K=%lld must be divisible by %d", (long long)K, BK); return PB200_ERR_BAD_SHAPE; }
+    const int bn = pick_bn(N);
+    if (bn == 0 || (!grouped && bn != 256)) {
+        set_err(err, "N=%lld must be divisible by %d", (long long)N, grouped ? 64 : 256);
+        return PB200_ERR_BAD_SHAPE;
+    }
+    if (G * M > 0x7fffffffLL || G * N > 0x7fffffffLL || K > 0x7fffffffLL) { set_err(err, "extent exceeds 2^31-1"); return PB200_ERR_BAD_SHAPE; }
+    const int64_t tiles = G * (M / (BM * cta_group)) * (N / bn);
+    int64_t units = sm_count() / cta_group;
+    if (units > tiles) units = tiles;
+    pb200_geometry& g = r.geom;
+    g.grid[0] = (uint32_t)(units * cta_group); g.grid[1] = g.grid[2] = 1;
+    g.block[0] = kThreads; g.block[1] = g.block[2] = 1;
+    g.cluster[0] = (uint32_t)cta_group; g.cluster[1] = g.cluster[2] = 1;
+    g.smem_bytes = bn == 256 ? (cta_group == 2 ? SmemPlan<256, 2>::kTotal : SmemPlan<256, 1>::kTotal)
+                 : bn == 128 ? SmemPlan<128, 1>::kTotal : SmemPlan<64, 1>::kTotal;
+    g.n_inputs = 2; g.n_outputs = 1;
+    return PB200_OK;
+}
+
+int launch_gemm(const Record& r, cudaStream_t stream, void** p, char* err) {
+    const int64_t N = r.dims[r.n_dims - 2];
+    const int bn = pick_bn(N);
+    const int cta_group = r.kernel_id == PB200_K_GEMM_2SM ? 2 : 1;
+    const bool bf16_out = (r.flags & PB200_F_OUT_BF16) != 0;
+    const bool direct = (r.flags & kDebugDirectStore) != 0;
+    Record rr = r;
+    // The grid was planned without a device; clamp it to this device's SM count.
+    {
+        const int64_t units = sm_count() / cta_group;
+        if ((int64_t)rr.geom.grid[0] > units * cta_group) rr.geom.grid[0] = (uint32_t)(units * cta_group);
+    }
+    GemmShape shape = make_shape(rr, bn, cta_group);
+#define PB200_GEMM_CASE(BN_, CG_)                                                                       \
+    if (bn == BN_ && cta_group == CG_) {                                                                \
+        if (bf16_out) return direct ? launch_variant<BN_, CG_, __nv_bfloat16, true>(rr, stream, p, shape, err)  \
+                                    : launch_variant<BN_, CG_, __nv_bfloat16, false>(rr, stream, p, shape, err); \
+        return direct ? launch_variant<BN_, CG_, float, true>(rr, stream, p, shape, err)               \
+                      : launch_variant<BN_, CG_, float, false>(rr, stream, p, shape, err);             \
+    }
+    PB200_GEMM_CASE(256, 1)
+    PB200_GEMM_CASE(256, 2)
+    PB200_GEMM_CASE(128, 1)
+    PB200_GEMM_CASE(64, 1)
+#undef PB200_GEMM_CASE
+    set_err(err, "no gemm variant for BN=%d cta_group=%d", bn, cta_group);
+    return PB200_ERR_BAD_SHAPE;
+}
+
+}  // namespace pb200

@@ -1,0 +1,403 @@
+// Row-wise f32 kernels for sm_100a: RMSNorm, LayerNorm, SwiGLU (silu(g)*u), softmax.
+//
+// These are HBM-bound (0.25-0.5 flop per byte), so the design is about bytes in
+// flight, not arithmetic:
+//   * one CTA owns one row at a time and keeps the whole row in registers
+//     (x is read from HBM exactly once; the second pass runs out of registers);
+//   * every global access is a 128-bit vector, consecutive lanes touch
+//     consecutive 16-byte segments (fully coalesced 512-byte warp requests);
+//   * all of a thread's loads are issued before the first use, so a CTA of
+//     256 threads x 8 float4 has 32 KiB outstanding, and 6-8 resident CTAs per
+//     SM cover the HBM latency-bandwidth product;
+//   * row reductions are warp shuffles plus one shared-memory exchange
+//     (one __syncthreads per reduction, no serial tail);
+//   * inputs are read with the streaming/no-allocate path and outputs written
+//     with streaming stores, since nothing is reused.
+//
+// Math follows the reference kernels' formulas
+// (examples/hopper/rms_norm.py:105-162, layer_norm.py:120-215,
+//  swiglu.py:100-140, softmax.py:100-170) with two deliberate changes that
+// tighten accuracy to 1e-5 relative of an fp32 CPU evaluation: full-precision
+// rsqrtf/expf/division instead of the .approx instructions, and a two-pass
+// variance (sum of squared deviations from the mean, taken over registers)
+// instead of E[x^2]-mean^2.
+#include "common.cuh"
+
+namespace pb200 {
+namespace {
+
+constexpr int kWarp = 32;
+
+__device__ __forceinline__ float4 ld_stream(const float4* p) {
+    float4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void st_stream(float4* p, const float4& v) {
+    asm volatile("st.global.cs.v4.f32 [%0], {%1,%2,%3,%4};"
+                 :: "l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = kWarp / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = kWarp / 2; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide reduction with a single barrier: each warp publishes its partial,
+// then every thread folds all partials itself.  `slot` must alternate between
+// two buffers on consecutive calls so that a warp that races ahead to the next
+// reduction cannot overwrite partials that a slower warp has not read yet.
+template <int THREADS, bool IS_MAX>
+__device__ __forceinline__ float block_reduce(float v, float* slot) {
+    constexpr int NW = THREADS / kWarp;
+    v = IS_MAX ? warp_max(v) : warp_sum(v);
+    if (NW == 1) return v;
+    if ((threadIdx.x & (kWarp - 1)) == 0) slot[threadIdx.x / kWarp] = v;
+    __syncthreads();
+    float r = slot[0];
+#pragma unroll
+    for (int i = 1; i < NW; ++i) r = IS_MAX ? fmaxf(r, slot[i]) : r + slot[i];
+    return r;
+}
+
+// ---------------------------------------------------------------------------
+// RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w
+// ---------------------------------------------------------------------------
+template <int THREADS, int VPT>
+__global__ void __launch_bounds__(THREADS)
+rms_norm_kernel(const float4* __restrict__ x, const float4* __restrict__ w,
+                float4* __restrict__ y, int rows, int n4, float inv_n, float eps) {
+    __shared__ float red[2][kWarp];
+    int flip = 0;
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const float4* xr = x + (size_t)row * n4;
+        float4* yr = y + (size_t)row * n4;
+        float4 v[VPT];
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            int idx = threadIdx.x + i * THREADS;
+            v[i] = idx < n4 ? ld_stream(xr + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i)
+            ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+        float tot = block_reduce<THREADS, false>(ss, red[flip]);
+        flip ^= 1;
+        float rstd = rsqrtf(tot * inv_n + eps);
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            int idx = threadIdx.x + i * THREADS;
+            if (idx < n4) {
+                float4 g = __ldg(w + idx);
+                float4 o;
+                o.x = v[i].x * rstd * g.x;
+                o.y = v[i].y * rstd * g.y;
+                o.z = v[i].z * rstd * g.z;
+                o.w = v[i].w * rstd * g.w;
+                st_stream(yr + idx, o);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// LayerNorm: y = (x - mean) * rsqrt(var + eps) * w + b, var over registers
+// ---------------------------------------------------------------------------
+template <int THREADS, int VPT>
+__global__ void __launch_bounds__(THREADS)
+layer_norm_kernel(const float4* __restrict__ x, const float4* __restrict__ w,
+                  const float4* __restrict__ b, float4* __restrict__ y,
+                  int rows, int n4, float inv_n, float eps) {
+    __shared__ float red[2][kWarp];
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const float4* xr = x + (size_t)row * n4;
+        float4* yr = y + (size_t)row * n4;
+        float4 v[VPT];
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            int idx = threadIdx.x + i * THREADS;
+            v[i] = idx < n4 ? ld_stream(xr + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+        float mean = block_reduce<THREADS, false>(s, red[0]) * inv_n;
+        float q = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            int idx = threadIdx.x + i * THREADS;
+            if (idx < n4) {
+                float dx = v[i].x - mean, dy = v[i].y - mean, dz = v[i].z - mean, dw = v[i].w - mean;
+                q += dx * dx + dy * dy + dz * dz + dw * dw;
+            }
+        }
+        float var = block_reduce<THREADS, false>(q, red[1]) * inv_n;
+        float rstd = rsqrtf(var + eps);
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            int idx = threadIdx.x + i * THREADS;
+            if (idx < n4) {
+                float4 g = __ldg(w + idx);
+                float4 c = __ldg(b + idx);
+                float4 o;
+                o.x = (v[i].x - mean) * rstd * g.x + c.x;
+                o.y = (v[i].y - mean) * rstd * g.y + c.y;
+                o.z = (v[i].z - mean) * rstd * g.z + c.z;
+                o.w = (v[i].w - mean) * rstd * g.w + c.w;
+                st_stream(yr + idx, o);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Softmax: y = exp(x - max) / sum(exp(x - max))
+// ---------------------------------------------------------------------------
+template <int THREADS, int VPT>
+__global__ void __launch_bounds__(THREADS)
+softmax_kernel(const float4* __restrict__ x, float4* __restrict__ y, int rows, int n4) {
+    __shared__ float red[2][kWarp];
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const float4* xr = x + (size_t)row * n4;
+        float4* yr = y + (size_t)row * n4;
+        float4 v[VPT];
+        const float ninf = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            int idx = threadIdx.x + i * THREADS;
+            v[i] = idx < n4 ? ld_stream(xr + idx) : make_float4(ninf, ninf, ninf, ninf);
+        }
+        float m = ninf;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) m = fmaxf(m, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+        m = block_reduce<THREADS, true>(m, red[0]);
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            v[i].x = expf(v[i].x - m);
+            v[i].y = expf(v[i].y - m);
+            v[i].z = expf(v[i].z - m);
+            v[i].w = expf(v[i].w - m);
+            s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+        }
+        s = block_reduce<THREADS, false>(s, red[1]);
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            int idx = threadIdx.x + i * THREADS;
+            if (idx < n4) {
+                float4 o;
+                o.x = v[i].x / s;
+                o.y = v[i].y / s;
+                o.z = v[i].z / s;
+                o.w = v[i].w / s;
+                st_stream(yr + idx, o);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Rows too long for the register-resident kernels: three streaming passes.
+// The second and third pass re-read the row, which a 126 MB L2 serves.
+// MODE 0 = RMSNorm, 1 = LayerNorm, 2 = softmax.
+// ---------------------------------------------------------------------------
+template <int MODE>
+__global__ void __launch_bounds__(1024)
+long_row_kernel(const float4* __restrict__ x, const float4* __restrict__ w,
+                const float4* __restrict__ b, float4* __restrict__ y,
+                int rows, int n4, float inv_n, float eps) {
+    constexpr int THREADS = 1024;
+    __shared__ float red[2][kWarp];
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const float4* xr = x + (size_t)row * n4;
+        float4* yr = y + (size_t)row * n4;
+        float a = MODE == 2 ? -INFINITY : 0.f;
+        for (int idx = threadIdx.x; idx < n4; idx += THREADS) {
+            float4 t = xr[idx];
+            if (MODE == 0) a += t.x * t.x + t.y * t.y + t.z * t.z + t.w * t.w;
+            if (MODE == 1) a += (t.x + t.y) + (t.z + t.w);
+            if (MODE == 2) a = fmaxf(a, fmaxf(fmaxf(t.x, t.y), fmaxf(t.z, t.w)));
+        }
+        float first = block_reduce<THREADS, MODE == 2>(a, red[0]);
+        float second = 0.f;
+        if (MODE != 0) {
+            float mean = first * inv_n;
+            float q = 0.f;
+            for (int idx = threadIdx.x; idx < n4; idx += THREADS) {
+                float4 t = xr[idx];
+                if (MODE == 1) {
+                    float dx = t.x - mean, dy = t.y - mean, dz = t.z - mean, dw = t.w - mean;
+                    q += dx * dx + dy * dy + dz * dz + dw * dw;
+                } else {
+                    q += (expf(t.x - first) + expf(t.y - first)) + (expf(t.z - first) + expf(t.w - first));
+                }
+            }
+            second = block_reduce<THREADS, false>(q, red[1]);
+        }
+        for (int idx = threadIdx.x; idx < n4; idx += THREADS) {
+            float4 t = xr[idx];
+            float4 o;
+            if (MODE == 0) {
+                float rstd = rsqrtf(first * inv_n + eps);
+                float4 g = __ldg(w + idx);
+                o.x = t.x * rstd * g.x; o.y = t.y * rstd * g.y; o.z = t.z * rstd * g.z; o.w = t.w * rstd * g.w;
+            } else if (MODE == 1) {
+                float mean = first * inv_n;
+                float rstd = rsqrtf(second * inv_n + eps);
+                float4 g = __ldg(w + idx);
+                float4 c = __ldg(b + idx);
+                o.x = (t.x - mean) * rstd * g.x + c.x; o.y = (t.y - mean) * rstd * g.y + c.y;
+                o.z = (t.z - mean) * rstd * g.z + c.z; o.w = (t.w - mean) * rstd * g.w + c.w;
+            } else {
+                o.x = expf(t.x - first) / second; o.y = expf(t.y - first) / second;
+                o.z = expf(t.z - first) / second; o.w = expf(t.w - first) / second;
+            }
+            st_stream(yr + idx, o);
+        }
+        __syncthreads();  // red[] is reused by the next row
+    }
+}
+
+// ---------------------------------------------------------------------------
+// SwiGLU: out = silu(gate) * up = gate / (1 + exp(-gate)) * up, flat over M*F.
+// Each thread keeps UNROLL independent 16-byte loads per operand in flight.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float silu_mul(float g, float u) {
+    return g / (1.0f + expf(-g)) * u;
+}
+
+template <int THREADS, int UNROLL>
+__global__ void __launch_bounds__(THREADS)
+swiglu_kernel(const float4* __restrict__ gate, const float4* __restrict__ up,
+              float4* __restrict__ out, size_t total4) {
+    const size_t tile = (size_t)THREADS * UNROLL;
+    for (size_t base = (size_t)blockIdx.x * tile; base < total4; base += (size_t)gridDim.x * tile) {
+        float4 g[UNROLL], u[UNROLL];
+#pragma unroll
+        for (int i = 0; i < UNROLL; ++i) {
+            size_t idx = base + threadIdx.x + (size_t)i * THREADS;
+            if (idx < total4) { g[i] = ld_stream(gate + idx); u[i] = ld_stream(up + idx); }
+        }
+#pragma unroll
+        for (int i = 0; i < UNROLL; ++i) {
+            size_t idx = base + threadIdx.x + (size_t)i * THREADS;
+            if (idx < total4) {
+                float4 o;
+                o.x = silu_mul(g[i].x, u[i].x);
+                o.y = silu_mul(g[i].y, u[i].y);
+                o.z = silu_mul(g[i].z, u[i].z);
+                o.w = silu_mul(g[i].w, u[i].w);
+                st_stream(out + idx, o);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Host side: pick a (THREADS, VPT) instantiation that covers N with the row in
+// registers, and a grid that is one CTA per row (the hardware block scheduler
+// balances the rows over the SMs; the per-CTA row loop only matters when the
+// row count exceeds the grid limit).
+// ---------------------------------------------------------------------------
+struct RowConfig { int threads; int vpt; };
+
+RowConfig pick_row_config(int64_t n4) {
+    // Prefer 8 float4 per thread (32 KiB per 256-thread CTA in flight).
+    const RowConfig table[] = {
+        {32, 1}, {32, 2}, {32, 4}, {64, 4}, {128, 4}, {128, 8}, {256, 8}, {512, 8}, {1024, 8},
+    };
+    for (const RowConfig& c : table)
+        if ((int64_t)c.threads * c.vpt >= n4) return c;
+    return {1024, 0};  // long-row kernel
+}
+
+template <int THREADS, int VPT>
+void launch_one(int kid, dim3 grid, cudaStream_t s, void** p, int rows, int n4, float inv_n, float eps) {
+    if (kid == PB200_K_RMS_NORM)
+        rms_norm_kernel<THREADS, VPT><<<grid, THREADS, 0, s>>>(
+            (const float4*)p[0], (const float4*)p[1], (float4*)p[2], rows, n4, inv_n, eps);
+    else if (kid == PB200_K_LAYER_NORM)
+        layer_norm_kernel<THREADS, VPT><<<grid, THREADS, 0, s>>>(
+            (const float4*)p[0], (const float4*)p[1], (const float4*)p[2], (float4*)p[3], rows, n4, inv_n, eps);
+    else
+        softmax_kernel<THREADS, VPT><<<grid, THREADS, 0, s>>>(
+            (const float4*)p[0], (float4*)p[1], rows, n4);
+}
+
+constexpr int kSwigluThreads = 256;
+constexpr int kSwigluUnroll = 4;
+
+}  // namespace
+
+int plan_row(Record& r, char* err) {
+    if (r.n_dims != 2) { set_err(err, "row kernel needs dims = {rows, cols}, got %d dims", r.n_dims); return PB200_ERR_BAD_SHAPE; }
+    const int64_t rows = r.dims[0], n = r.dims[1];
+    if (rows <= 0 || n <= 0) { set_err(err, "rows=%lld cols=%lld must be positive", (long long)rows, (long long)n); return PB200_ERR_BAD_SHAPE; }
+    if (n % 4 != 0) { set_err(err, "cols=%lld must be divisible by 4 (128-bit vector access)", (long long)n); return PB200_ERR_BAD_SHAPE; }
+    if (rows > 0x7fffffffLL || n > 0x7fffffffLL) { set_err(err, "rows/cols exceed 2^31-1"); return PB200_ERR_BAD_SHAPE; }
+    pb200_geometry& g = r.geom;
+    g.grid[1] = g.grid[2] = 1; g.block[1] = g.block[2] = 1;
+    g.cluster[0] = g.cluster[1] = g.cluster[2] = 1;
+    g.smem_bytes = 0;
+    g.n_outputs = 1;
+    if (r.kernel_id == PB200_K_SWIGLU) {
+        const int64_t total4 = rows * n / 4;
+        const int64_t tile = (int64_t)kSwigluThreads * kSwigluUnroll;
+        int64_t ctas = (total4 + tile - 1) / tile;
+        if (ctas > 0x7fffffffLL) ctas = 0x7fffffffLL;
+        g.grid[0] = (uint32_t)ctas; g.block[0] = kSwigluThreads;
+        g.n_inputs = 2;
+        return PB200_OK;
+    }
+    RowConfig c = pick_row_config(n / 4);
+    g.grid[0] = (uint32_t)rows; g.block[0] = (uint32_t)c.threads;
+    g.smem_bytes = 2 * kWarp * sizeof(float);
+    g.n_inputs = r.kernel_id == PB200_K_RMS_NORM ? 2 : r.kernel_id == PB200_K_LAYER_NORM ? 3 : 1;
+    return PB200_OK;
+}
+
+int launch_row(const Record& r, cudaStream_t s, void** p, char* err) {
+    const int rows = (int)r.dims[0];
+    const int n = (int)r.dims[1];
+    const int n4 = n / 4;
+    const float inv_n = 1.0f / (float)n;
+    const float eps = (float)r.fparams[0];
+    dim3 grid(r.geom.grid[0]);
+    if (r.kernel_id == PB200_K_SWIGLU) {
+        swiglu_kernel<kSwigluThreads, kSwigluUnroll><<<grid, kSwigluThreads, 0, s>>>(
+            (const float4*)p[0], (const float4*)p[1], (float4*)p[2], (size_t)rows * n4);
+    } else {
+        RowConfig c = pick_row_config(n4);
+        const int kid = r.kernel_id;
+#define PB200_ROW_CASE(T, V) \
+        if (c.threads == T && c.vpt == V) launch_one<T, V>(kid, grid, s, p, rows, n4, inv_n, eps); else
+        PB200_ROW_CASE(32, 1) PB200_ROW_CASE(32, 2) PB200_ROW_CASE(32, 4) PB200_ROW_CASE(64, 4)
+        PB200_ROW_CASE(128, 4) PB200_ROW_CASE(128, 8) PB200_ROW_CASE(256, 8) PB200_ROW_CASE(512, 8)
+        PB200_ROW_CASE(1024, 8)
+        {
+            if (kid == PB200_K_RMS_NORM)
+                long_row_kernel<0><<<grid, 1024, 0, s>>>((const float4*)p[0], (const float4*)p[1], nullptr,
+                                                        (float4*)p[2], rows, n4, inv_n, eps);
+            else if (kid == PB200_K_LAYER_NORM)
+                long_row_kernel<1><<<grid, 1024, 0, s>>>((const float4*)p[0], (const float4*)p[1],
+                                                        (const float4*)p[2], (float4*)p[3], rows, n4, inv_n, eps);
+            else
+                long_row_kernel<2><<<grid, 1024, 0, s>>>((const float4*)p[0], nullptr, nullptr,
+                                                        (float4*)p[1], rows, n4, inv_n, eps);
+        }
+#undef PB200_ROW_CASE
+    }
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { set_err(err, "row kernel launch failed: %s", cudaGetErrorString(e)); return PB200_ERR_LAUNCH; }
+    return PB200_OK;
+}
+
+}  // namespace pb200

@@ -1,0 +1,85 @@
+"""bf16 GEMM for B200 on tcgen05 tensor cores: ``D = A @ B_T.T`` with fp32 accumulation.
+
+Drop-in for the reference entry points (examples/blackwell/gemm_highperf_blackwell.py):
+
+* ``build_gemm(M, N, K, *, arch, stages, grid_minor_dim, grid_tile_width)`` (:69-313):
+  1-SM MMA, one 128x256 output tile per CTA at a time;
+* ``build_gemm_2sm(M, N, K, *, arch, stages, grid_minor_dim, grid_tile_width)`` (:902-1246):
+  ``cta_group::2`` MMA, one 256x256 tile per 2-CTA cluster.
+
+Both take ``A[M,K]`` bf16 and ``B_T[N,K]`` bf16 (the caller passes
+``b.t().contiguous()``, as in the reference, :1264) and return ``D[M,N]`` f32.
+``out_dtype=bf16`` is an extension that rounds the result in the epilogue.
+"""
+from __future__ import annotations
+
+from ..._ids import F_OUT_BF16, K_GEMM_1SM, K_GEMM_2SM
+from ...kernel import NativeKernel
+from ...specs import Layout, Tile
+from ...types import PtxType, bf16, f32
+
+BM = 128
+BN = 256
+BK = 64
+STAGES = 4
+STAGES_2SM = 5
+GRID_MINOR_DIM = "n"
+GRID_TILE_WIDTH = 16
+
+
+def _out_flags(out_dtype: PtxType) -> int:
+    assert out_dtype in (f32, bf16), f"out_dtype must be f32 or bf16, got {out_dtype}"
+    return F_OUT_BF16 if out_dtype == bf16 else 0
+
+
+def build_gemm(M: int, N: int, K: int, *, arch: str = "sm_100a", stages: int = STAGES,
+               grid_minor_dim: str = GRID_MINOR_DIM, grid_tile_width: int = GRID_TILE_WIDTH,
+               out_dtype: PtxType = f32) -> NativeKernel:
+    """Kernel ``k(A[M,K] bf16, B_T[N,K] bf16) -> D[M,N]``.
+
+    ``stages`` and ``grid_minor_dim`` are accepted and validated as in the
+    reference; the native kernel sizes its own shared-memory ring and always
+    rasterises M-fastest inside a band.  ``grid_tile_width`` is the number of
+    M-tiles per raster band.
+    """
+    assert arch.startswith("sm_100"), "Blackwell GEMM is only implemented for sm_100*"
+    assert M % BM == 0, f"M={M} must be divisible by {BM}"
+    assert N % BN == 0, f"N={N} must be divisible by {BN}"
+    assert K % BK == 0, f"K={K} must be divisible by {BK}"
+    assert stages >= 2, "Blackwell GEMM requires at least two stages"
+    assert grid_tile_width >= 1, "grid_tile_width must be at least 1"
+    assert grid_minor_dim.lower() in {"m", "n"}, "grid_minor_dim must be 'm' or 'n'"
+    return NativeKernel(
+        "blackwell_gemm", K_GEMM_1SM, (M, N, K, grid_tile_width),
+        in_specs=(Tile(M, K, bf16, Layout.TMA_128B, tma_box=(BM, BK)),
+                  Tile(N, K, bf16, Layout.TMA_128B, tma_box=(BN, BK))),
+        out_specs=(Tile(M, N, out_dtype, Layout.ROW),),
+        flags=_out_flags(out_dtype), arch=arch,
+        meta={"stages": stages, "grid_minor_dim": grid_minor_dim, "grid_tile_width": grid_tile_width},
+    )
+
+
+def build_gemm_2sm(M: int, N: int, K: int, *, arch: str = "sm_100a", stages: int = STAGES_2SM,
+                   grid_minor_dim: str = GRID_MINOR_DIM, grid_tile_width: int = GRID_TILE_WIDTH,
+                   out_dtype: PtxType = f32) -> NativeKernel:
+    """2-SM variant: same call convention, ``M`` must divide by 256."""
+    assert arch.startswith("sm_100")
+    assert M % (2 * BM) == 0, f"M={M} must be divisible by {2 * BM} for 2SM"
+    assert N % BN == 0, f"N={N} must be divisible by {BN}"
+    assert K % BK == 0, f"K={K} must be divisible by {BK}"
+    assert stages >= 2, "2SM Blackwell GEMM requires at least two stages"
+    assert grid_tile_width >= 1, "grid_tile_width must be at least 1"
+    assert grid_minor_dim.lower() in {"m", "n"}, "grid_minor_dim must be 'm' or 'n'"
+    return NativeKernel(
+        "blackwell_gemm_2sm", K_GEMM_2SM, (M, N, K, grid_tile_width),
+        in_specs=(Tile(M, K, bf16, Layout.TMA_128B, tma_box=(BM, BK)),
+                  Tile(N, K, bf16, Layout.TMA_128B, tma_box=(BN // 2, BK))),
+        out_specs=(Tile(M, N, out_dtype, Layout.ROW),),
+        flags=_out_flags(out_dtype), arch=arch,
+        meta={"stages": stages, "grid_minor_dim": grid_minor_dim, "grid_tile_width": grid_tile_width},
+    )
+
+
+def gemm_flops(M: int, N: int, K: int) -> int:
+    """benchmarks/bench_blackwell_gemm.py:56."""
+    return 2 * M * N * K

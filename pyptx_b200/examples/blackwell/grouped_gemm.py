@@ -1,0 +1,48 @@
+"""Grouped (MoE) bf16 GEMM for B200: ``C[g] = A[g] @ B[g]`` for ``g < G``.
+
+Drop-in for ``build_grouped_gemm(G, M, N, K, *, arch="sm_100a")``
+(examples/blackwell/grouped_gemm.py:61-289).  Operands are stacked along the
+row axis: ``A[G*M, K]`` bf16, ``B_T[G*N, K]`` bf16 (each expert's weight
+transposed to K-major, :302-303), result ``C[G*M, N]`` f32.
+"""
+from __future__ import annotations
+
+from ..._ids import F_OUT_BF16, K_GROUPED_GEMM
+from ...kernel import NativeKernel
+from ...specs import Layout, Tile
+from ...types import PtxType, bf16, f32
+
+BM = 128
+BK = 64
+
+
+def _pick_bn(N: int) -> int:
+    """Widest supported N tile that divides N (the reference uses min(N, 256), :51-58)."""
+    for bn in (256, 128, 64):
+        if N % bn == 0:
+            return bn
+    raise AssertionError(f"N={N} must be divisible by 64")
+
+
+def build_grouped_gemm(G: int, M: int, N: int, K: int, *, arch: str = "sm_100a",
+                       out_dtype: PtxType = f32) -> NativeKernel:
+    """Kernel ``k(A[G*M,K] bf16, B_T[G*N,K] bf16) -> C[G*M,N]``."""
+    assert arch.startswith("sm_100"), "Blackwell grouped GEMM is only implemented for sm_100*"
+    assert G >= 1, "G must be at least 1"
+    assert M % BM == 0, f"M={M} must be divisible by {BM}"
+    assert K % BK == 0, f"K={K} must be divisible by {BK}"
+    bn = _pick_bn(N)
+    assert out_dtype in (f32, bf16), f"out_dtype must be f32 or bf16, got {out_dtype}"
+    return NativeKernel(
+        "grouped_gemm_bw", K_GROUPED_GEMM, (G, M, N, K),
+        in_specs=(Tile(G * M, K, bf16, Layout.TMA_128B, tma_box=(BM, BK)),
+                  Tile(G * N, K, bf16, Layout.TMA_128B, tma_box=(bn, BK))),
+        out_specs=(Tile(G * M, N, out_dtype, Layout.ROW),),
+        flags=F_OUT_BF16 if out_dtype == bf16 else 0, arch=arch,
+        meta={"block_n": bn},
+    )
+
+
+def grouped_gemm_flops(G: int, M: int, N: int, K: int) -> int:
+    """benchmarks/bench_blackwell_kernels.py:141."""
+    return 2 * G * M * N * K

@@ -1,0 +1,6 @@
+"""``examples.hopper.layer_norm`` import path of the reference (examples/hopper/layer_norm.py), kept so that
+callers written against it resolve; the kernel behind it is the sm_100a one and any
+other ``arch`` is rejected."""
+from ..blackwell.layer_norm import build_layer_norm  # noqa: F401
+
+__all__ = ["build_layer_norm"]

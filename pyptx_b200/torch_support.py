@@ -1,0 +1,252 @@
+"""PyTorch launch path for :class:`pyptx_b200.kernel.NativeKernel`.
+
+Mirrors the reference's torch integration (pyptx/torch_support.py):
+
+* eager launch -- ``call_kernel_via_torch`` (:171-271): outputs from
+  ``torch.empty`` on the first input's device, a ``void*[]`` of inputs then
+  outputs, the current CUDA stream as an integer, one call into the C ABI;
+* ``torch.compile`` -- one ``torch.library.custom_op`` per handle with schema
+  ``(Tensor[] inputs) -> Tensor[]`` and a ``register_fake`` that only sizes the
+  outputs (:347-438);
+* CUDA graphs -- the launch is stream-ordered, never synchronises and only
+  allocates through torch's caching allocator, so it can be captured;
+* autograd -- ``differentiable_kernel`` pairs a forward and a backward kernel
+  (:446-519).
+
+Unlike the reference, the inputs are checked at call time (device, dtype,
+contiguity, alignment) and a ``TypeError`` / ``ValueError`` is raised before
+anything is enqueued.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Any, Sequence
+
+from . import _native
+
+_TORCH = None
+
+
+def _torch():
+    global _TORCH
+    if _TORCH is None:
+        import torch
+        _TORCH = torch
+    return _TORCH
+
+
+def is_torch_tensor(obj: Any) -> bool:
+    try:
+        return isinstance(obj, _torch().Tensor)
+    except ImportError:
+        return False
+
+
+def any_torch_tensors(inputs: Sequence[Any]) -> bool:
+    return any(is_torch_tensor(x) for x in inputs)
+
+
+_PTX_TO_TORCH_NAME = {
+    "f16": "float16", "bf16": "bfloat16", "f32": "float32", "f64": "float64",
+    "s8": "int8", "s16": "int16", "s32": "int32", "s64": "int64",
+    "u8": "uint8", "b8": "uint8", "b16": "uint16", "b32": "uint32", "b64": "uint64",
+    "pred": "bool",
+}
+
+
+def _ptx_type_to_torch_dtype(dtype):
+    """Map a ``PtxType`` to a ``torch.dtype`` (pyptx/torch_support.py:278-301)."""
+    name = _PTX_TO_TORCH_NAME.get(dtype.name)
+    if name is None or not hasattr(_torch(), name):
+        raise TypeError(f"Cannot map PtxType {dtype.name} to a torch.dtype")
+    return getattr(_torch(), name)
+
+
+def _torch_dtype_to_ptx_type_name(torch_dtype) -> str:
+    """Inverse mapping, used to check input dtypes (pyptx/torch_support.py:304-323)."""
+    torch = _torch()
+    table = {
+        torch.float16: "f16", torch.bfloat16: "bf16", torch.float32: "f32", torch.float64: "f64",
+        torch.int8: "s8", torch.int16: "s16", torch.int32: "s32", torch.int64: "s64",
+        torch.uint8: "u8", torch.bool: "pred",
+    }
+    if torch_dtype not in table:
+        raise TypeError(f"Cannot map torch dtype {torch_dtype} to a pyptx type")
+    return table[torch_dtype]
+
+
+def extract_input_shapes(inputs) -> list[tuple[int, ...]]:
+    return [tuple(t.shape) for t in inputs]
+
+
+# ---------------------------------------------------------------------------
+# Eager launch
+# ---------------------------------------------------------------------------
+
+class _Launcher:
+    """Per-kernel cached state for the eager path: ctypes objects are reused so a
+    steady-state call does no Python allocation beyond the output tensors."""
+
+    def __init__(self, kernel) -> None:
+        self.lib = _native.load()
+        self.handle = ctypes.c_int64(kernel.handle)
+        self.n_in = len(kernel.in_specs)
+        self.n = self.n_in + len(kernel.out_specs)
+        self.ptrs = (ctypes.c_void_p * self.n)()
+        self.ptrs_ref = ctypes.cast(self.ptrs, ctypes.c_void_p)
+        self.err = ctypes.create_string_buffer(_native.ERR_LEN)
+        self.in_dtypes = [_ptx_type_to_torch_dtype(s.dtype) for s in kernel.in_specs]
+        self.out_dtypes = [_ptx_type_to_torch_dtype(s.dtype) for s in kernel.out_specs]
+        self.static_out_shapes = None
+        if not any(s.symbolic_dims for s in kernel.out_specs):
+            self.static_out_shapes = kernel.out_shapes({})
+        self.in_shapes = [s.shape if not s.symbolic_dims else None for s in kernel.in_specs]
+
+
+def _check_inputs(kernel, launcher: _Launcher, inputs) -> dict[str, int]:
+    torch = _torch()
+    dev = inputs[0].device
+    if dev.type != "cuda":
+        raise ValueError(
+            f"Kernel {kernel.__name__}: inputs must be CUDA tensors, got device {dev} "
+            f"(there is no CPU path)")
+    needs_env = False
+    for i, (t, want_dt, want_shape) in enumerate(zip(inputs, launcher.in_dtypes, launcher.in_shapes)):
+        if not isinstance(t, torch.Tensor):
+            raise TypeError(f"Kernel {kernel.__name__}: input {i} is {type(t).__name__}, not a torch.Tensor")
+        if t.device != dev:
+            raise ValueError(f"Kernel {kernel.__name__}: input {i} is on {t.device}, input 0 on {dev}")
+        if t.dtype != want_dt:
+            raise TypeError(f"Kernel {kernel.__name__}: input {i} has dtype {t.dtype}, spec wants {want_dt}")
+        if not t.is_contiguous():
+            raise ValueError(f"Kernel {kernel.__name__}: input {i} is not contiguous")
+        if want_shape is None:
+            needs_env = True
+        elif tuple(t.shape) != want_shape:
+            # Same wording as Tile.extract_env so messages match the reference's.
+            kernel.in_specs[i].extract_env(tuple(t.shape))
+    if needs_env:
+        return kernel.bind_shapes([tuple(t.shape) for t in inputs])
+    return {}
+
+
+def call_kernel_via_torch(kernel, inputs: Sequence[Any]):
+    """Enqueue ``kernel`` on the current stream of the inputs' device; returns a list of outputs."""
+    torch = _torch()
+    if not inputs:
+        raise ValueError("pyptx_b200: a kernel call requires at least one input")
+    launcher = kernel._launcher
+    if launcher is None:
+        launcher = kernel._launcher = _Launcher(kernel)
+    env = _check_inputs(kernel, launcher, inputs)
+    dev = inputs[0].device
+    shapes = launcher.static_out_shapes or kernel.out_shapes(env)
+    outs = [torch.empty(shp, dtype=dt, device=dev) for shp, dt in zip(shapes, launcher.out_dtypes)]
+    ptrs = launcher.ptrs
+    for i, t in enumerate(inputs):
+        ptrs[i] = t.data_ptr()
+    for i, t in enumerate(outs):
+        ptrs[launcher.n_in + i] = t.data_ptr()
+    if torch.cuda.current_device() != dev.index:
+        with torch.cuda.device(dev):
+            stream = torch.cuda.current_stream(dev).cuda_stream
+            rc = launcher.lib.pb200_launch_raw(launcher.handle, stream, launcher.ptrs_ref, launcher.n, launcher.err)
+    else:
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        rc = launcher.lib.pb200_launch_raw(launcher.handle, stream, launcher.ptrs_ref, launcher.n, launcher.err)
+    if rc != 0:
+        msg = launcher.err.value.decode("utf-8", errors="replace")
+        raise RuntimeError(f"pyptx_b200: pb200_launch_raw failed (code {rc}): {msg}")
+    return outs
+
+
+# ---------------------------------------------------------------------------
+# torch.compile: one custom_op per handle
+# ---------------------------------------------------------------------------
+
+_REGISTERED_OPS: dict[int, Any] = {}
+
+
+def get_or_register_torch_op(kernel):
+    """Return the ``torch.library.custom_op`` wrapping ``kernel`` (registered once per handle)."""
+    op = _REGISTERED_OPS.get(kernel.handle)
+    if op is not None:
+        return op
+    torch = _torch()
+    op_name = f"pyptx_b200::kernel_{kernel.handle}"
+
+    @torch.library.custom_op(op_name, mutates_args=(), schema="(Tensor[] inputs) -> Tensor[]")
+    def native_op(inputs):
+        return call_kernel_via_torch(kernel, list(inputs))
+
+    @native_op.register_fake
+    def _fake(inputs):
+        dev = inputs[0].device if inputs else torch.device("cuda")
+        env = kernel.bind_shapes([tuple(t.shape) for t in inputs])
+        return [torch.empty(spec.resolve_shape(env), dtype=_ptx_type_to_torch_dtype(spec.dtype), device=dev)
+                for spec in kernel.out_specs]
+
+    _REGISTERED_OPS[kernel.handle] = native_op
+    return native_op
+
+
+def call_kernel(kernel, inputs: Sequence[Any]):
+    """Dispatch used by ``NativeKernel.__call__``: the registered op while Dynamo
+    is tracing, the direct launch otherwise; one output -> tensor, several -> tuple."""
+    torch = _torch()
+    if torch.compiler.is_compiling():
+        outs = get_or_register_torch_op(kernel)(list(inputs))
+    else:
+        outs = call_kernel_via_torch(kernel, inputs)
+    return outs[0] if len(outs) == 1 else tuple(outs)
+
+
+def call_kernel_via_torch_compile(kernel, inputs: Sequence[Any]):
+    """Always go through the registered custom op (what ``torch.compile`` sees)."""
+    outs = get_or_register_torch_op(kernel)(list(inputs))
+    return outs[0] if len(outs) == 1 else tuple(outs)
+
+
+# ---------------------------------------------------------------------------
+# Autograd
+# ---------------------------------------------------------------------------
+
+def differentiable_kernel(forward_kernel, backward_kernel, *,
+                          save_for_backward: Sequence[int] | None = None,
+                          num_grad_inputs: int | None = None):
+    """Wrap a forward / backward kernel pair in a ``torch.autograd.Function``.
+
+    ``backward_kernel`` is called with ``(*saved_inputs, *grad_outputs)`` and
+    returns one gradient per differentiable input; missing trailing gradients
+    are filled with ``None`` (pyptx/torch_support.py:446-519).
+    """
+    torch = _torch()
+    saved_idx = None if save_for_backward is None else list(save_for_backward)
+
+    class _Fn(torch.autograd.Function):
+        @staticmethod
+        def forward(ctx, *inputs):
+            keep = inputs if saved_idx is None else tuple(inputs[i] for i in saved_idx)
+            ctx.save_for_backward(*keep)
+            ctx.n_inputs = len(inputs)
+            with torch.no_grad():
+                return forward_kernel(*inputs)
+
+        @staticmethod
+        def backward(ctx, *grad_outputs):
+            with torch.no_grad():
+                grads = backward_kernel(*ctx.saved_tensors, *grad_outputs)
+            if not isinstance(grads, tuple):
+                grads = (grads,)
+            n = ctx.n_inputs if num_grad_inputs is None else num_grad_inputs
+            grads = tuple(grads) + (None,) * max(0, n - len(grads))
+            return grads[:n] + (None,) * max(0, ctx.n_inputs - n)
+
+    def wrapper(*inputs):
+        return _Fn.apply(*inputs)
+
+    wrapper.__name__ = getattr(forward_kernel, "__name__", "kernel")
+    wrapper.__doc__ = f"Differentiable kernel ({wrapper.__name__})"
+    wrapper.forward_kernel = forward_kernel
+    wrapper.backward_kernel = backward_kernel
+    return wrapper

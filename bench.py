@@ -1,0 +1,372 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: bf16 GEMM TFLOPS at 8192^3 (headline) plus the row kernels' HBM GB/s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--variant 1sm|2sm]
+
+A step is one D = A @ B_T.T at M = N = K = 8192 (bf16 in, fp32 accumulate, f32 out) through the
+public ``build_gemm`` / ``build_gemm_2sm`` entry point.  With N > 1 (one process per GPU under
+``torch.distributed.run``) every rank owns one 8192-row block of A and of D with B_T replicated --
+M-sharding, no collective on the data path -- so the job is a (N*8192) x 8192 x 8192 product and
+scaling is weak.  One JSON line is printed by rank 0.
+
+``--impl reference`` times the reference's CPU path for the same product (its torch formula
+``a.float() @ b.float()``, the expression its GEMM example checks against) on the host cores, on a
+bounded row block per step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+S = 8192                       # headline size
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+CPU_SAMPLE_ROWS = 512          # rows of A per CPU step: 2*512*8192*8192 = 68.7 GFLOP
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return {k: float(p[k]) for k in FALLBACK_PEAKS}, "measured"
+    except Exception:  # noqa: BLE001 - absent or malformed file -> stated fallback
+        return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int) -> None:
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+        self.thread = None
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+
+        def pump():
+            for line in self.proc.stdout:
+                self.lines.append(line.strip())
+
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1])); mx.append(float(parts[2])); power.append(float(parts[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        # "under load" = samples in the upper half of the observed power range
+        lo, hi = min(power), max(power)
+        loaded = [c for c, p in zip(sm, power) if p >= lo + 0.5 * (hi - lo)] or sm
+        return {"sm_mhz": statistics.median(loaded), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm), "power_w_max": hi}
+
+
+def time_cuda(fn, steps: int, warmup: int, torch) -> float:
+    """Milliseconds per call of ``fn`` over ``steps`` back-to-back calls, CUDA events on the current stream."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        fn()
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) / steps
+
+
+def cpu_gemm_tflops(torch, a_bf16, bt_bf16, rows: int, repeats: int, warmup: int = 1):
+    """The oracle's GEMM formula on ``rows`` rows of A with every host thread torch uses."""
+    from oracle import formulas
+    a = a_bf16[:rows]
+    for _ in range(warmup):
+        formulas.gemm_ref(a, bt_bf16)
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        formulas.gemm_ref(a, bt_bf16)
+        times.append(time.perf_counter() - t0)
+    flops = 2.0 * rows * bt_bf16.shape[0] * bt_bf16.shape[1]
+    return flops / min(times) / 1e12, sum(times), times
+
+
+def run_reference(args) -> None:
+    """Reference arm: the reference's CPU path for the headline product, on rank 0 only."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    from oracle import inputs, formulas
+    torch.manual_seed(0)
+    threads = torch.get_num_threads()
+    a, bt = inputs.gemm_inputs(CPU_SAMPLE_ROWS, S, S)
+    for _ in range(args.warmup):
+        formulas.gemm_ref(a, bt)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        formulas.gemm_ref(a, bt)
+    dt = time.perf_counter() - t0
+    flops = 2.0 * CPU_SAMPLE_ROWS * S * S * args.steps
+    value = flops / dt / 1e12
+    sample = (f"{CPU_SAMPLE_ROWS} of {S} rows of A per step (1/{S // CPU_SAMPLE_ROWS} of the 8192^3 product), "
+              f"torch CPU a.float() @ b.float(), {threads} threads")
+    print(json.dumps({
+        "impl": "reference", "metric": "bf16 GEMM TFLOPS @8192^3", "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "gemm_bf16_8192x8192x8192_f32out", "cpu_sample_rows": CPU_SAMPLE_ROWS},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample,
+                         "host_cpus": os.cpu_count()},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def row_kernel_table(torch, peaks, steps: int, warmup: int) -> dict:
+    """GB/s of the four row kernels at 2048 x 8192 f32, rotating over buffer sets whose total
+    footprint exceeds L2 several times so that every launch streams from HBM."""
+    from pyptx_b200.examples.blackwell.layer_norm import build_layer_norm, layer_norm_bytes
+    from pyptx_b200.examples.blackwell.rms_norm import build_rms_norm, rms_norm_bytes
+    from pyptx_b200.examples.blackwell.softmax import build_softmax, softmax_bytes
+    from pyptx_b200.examples.blackwell.swiglu import build_fused_silu_mul, swiglu_bytes
+    B, N, SETS = 2048, 8192, 6
+    xs = [torch.randn(B, N, device="cuda") for _ in range(SETS)]
+    us = [torch.randn(B, N, device="cuda") for _ in range(SETS)]
+    w = torch.randn(N, device="cuda") * 0.02 + 1.0
+    b = torch.randn(N, device="cuda") * 0.02
+    table = {}
+    cases = {
+        "rms_norm": (build_rms_norm(B, N), lambda k, i: k(xs[i], w), rms_norm_bytes(B, N)),
+        "layer_norm": (build_layer_norm(B, N), lambda k, i: k(xs[i], w, b), layer_norm_bytes(B, N)),
+        "swiglu": (build_fused_silu_mul(B, N), lambda k, i: k(xs[i], us[i]), swiglu_bytes(B, N)),
+        "softmax": (build_softmax(B, N), lambda k, i: k(xs[i]), softmax_bytes(B, N)),
+    }
+    for name, (k, call, nbytes) in cases.items():
+        counter = [0]
+
+        def fn():
+            call(k, counter[0] % SETS)
+            counter[0] += 1
+
+        ms = time_cuda(fn, steps, warmup, torch)
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        table[name] = {"ms": ms, "GB/s": gbs, "bytes": nbytes, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
+                       "frac_of_8TBps": gbs / 8000.0}
+    return table
+
+
+def run_ours(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the kernels have no CPU path")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    from oracle import inputs
+    from pyptx_b200 import _native
+    from pyptx_b200.examples.blackwell.gemm_highperf_blackwell import build_gemm, build_gemm_2sm
+
+    peaks, peak_kind = load_peaks()
+    builders = {"1sm": build_gemm, "2sm": build_gemm_2sm}
+    kernel = builders[args.variant](S, S, S)
+
+    # Each rank's M-block of A; B_T replicated.  Seeded on the CPU so the oracle sees the same bits.
+    a_host, bt_host = inputs.gemm_inputs(S, S, S)
+    if rank:
+        a_host = a_host.roll(rank * 17, 0)
+    a_pin, bt_pin = a_host.pin_memory(), bt_host.pin_memory()
+    a, bt = a_pin.cuda(non_blocking=True), bt_pin.cuda(non_blocking=True)
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing -------------------------------------------------------------
+    out_holder = [None]
+
+    def step():
+        out_holder[0] = kernel(a, bt)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        step()
+    stop.record()
+    barrier()
+    ms_total = start.elapsed_time(stop)
+    clocks = sampler.stop() if rank == 0 else None
+    _native.device_status()
+    if world > 1:
+        t = torch.tensor([ms_total], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_per_step = ms_total / args.steps
+    flops_per_rank = 2.0 * S * S * S
+    value = flops_per_rank * world / (ms_per_step * 1e-3) / 1e12
+    kernel_tflops = flops_per_rank / (ms_per_step * 1e-3) / 1e12
+
+    # sanity of the timed output (sampled rows against the oracle happens in the tests; here: finite + nonzero)
+    d = out_holder[0]
+    checksum = float(d[::1024, ::1024].double().abs().sum().item())
+    if not (checksum > 0.0 and checksum == checksum):
+        raise SystemExit("bench.py: timed GEMM produced an empty or non-finite result")
+
+    # ---- end to end: pinned host -> device, kernel, device -> pinned host -----------------------
+    d_pin = torch.empty(S, S, dtype=torch.float32).pin_memory()
+    e2e_steps = max(2, min(args.steps, 5))
+
+    def e2e_step():
+        a_d = a_pin.cuda(non_blocking=True)
+        bt_d = bt_pin.cuda(non_blocking=True)
+        d_pin.copy_(kernel(a_d, bt_d), non_blocking=True)
+
+    e2e_step()
+    barrier()
+    start.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    stop.record()
+    barrier()
+    e2e_ms = start.elapsed_time(stop) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = flops_per_rank * world / (e2e_ms * 1e-3) / 1e12
+    h2d = a_pin.numel() * 2 + bt_pin.numel() * 2
+    d2h = d_pin.numel() * 4
+
+    extras, cpu_baseline = None, None
+    if rank == 0 and world == 1:
+        # ---- context numbers: other variant, cuBLAS, smaller sizes, grouped, row kernels ----------------
+        extras = {}
+        other = "2sm" if args.variant == "1sm" else "1sm"
+        for name in (args.variant, other):
+            for size in (2048, 4096, 8192):
+                k = builders[name](size, size, size)
+                x, y = a[:size, :size].contiguous(), bt[:size, :size].contiguous()
+                ms = time_cuda(lambda: k(x, y), 20, 5, torch)
+                extras[f"gemm_{name}_{size}_tflops"] = 2.0 * size ** 3 / (ms * 1e-3) / 1e12
+        for size in (2048, 4096, 8192):
+            x, y = a[:size, :size].contiguous(), bt[:size, :size].t().contiguous()
+            ms = time_cuda(lambda: torch.matmul(x, y), 20, 5, torch)
+            extras[f"cublas_{size}_tflops"] = 2.0 * size ** 3 / (ms * 1e-3) / 1e12
+        try:
+            from pyptx_b200.examples.blackwell.grouped_gemm import build_grouped_gemm
+            for G in (8, 4):
+                ga, gb = inputs.grouped_gemm_inputs(G, 2048, 256, 2048)
+                ga, gb = ga.cuda(), gb.cuda()
+                k = build_grouped_gemm(G, 2048, 256, 2048)
+                ms = time_cuda(lambda: k(ga, gb), 50, 10, torch)
+                extras[f"grouped_G{G}_tflops"] = 2.0 * G * 2048 * 256 * 2048 / (ms * 1e-3) / 1e12
+        except Exception as exc:  # noqa: BLE001 - context only
+            extras["grouped_error"] = str(exc)[:200]
+        extras["row_kernels_2048x8192_f32"] = row_kernel_table(torch, peaks, 200, 20)
+        _native.device_status()
+        # ---- CPU baseline: the oracle formula on a bounded row block -----------------------------
+        tflops, spent, _ = cpu_gemm_tflops(torch, a_host, bt_host, CPU_SAMPLE_ROWS, repeats=3)
+        cpu_baseline = {
+            "value": tflops, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+            "host_cpus": os.cpu_count(),
+            "sample": (f"{CPU_SAMPLE_ROWS} of {S} rows of A (1/{S // CPU_SAMPLE_ROWS} of the product), best of 3, "
+                       f"torch CPU a.float() @ b.float(); {spent:.1f} s of CPU work"),
+        }
+
+    if rank == 0:
+        peak = peaks["bf16_tflops"]
+        line = {
+            "metric": "bf16 GEMM TFLOPS @8192^3", "value": value, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": value / world / 1240.0,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"gemm_bf16_8192x8192x8192_f32out_{args.variant}",
+                       "per_gpu": "M=N=K=8192, A,B~N(0,1)/sqrt(K) seeded, B_T replicated, M-block per rank",
+                       "l2": "operands (256 MiB) + output (256 MiB) exceed the 126 MB L2",
+                       "vs_baseline_ref": "reference README.md:54: its 1-SM kernel 1240 TFLOPS at 8192^3 on B200 (per GPU)"},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms, "steps": e2e_steps},
+            "gpu_launches": args.steps,
+            "roofline": {"bound": "tensor", "achieved": kernel_tflops, "peak": peak, "unit": "TFLOP/s",
+                         "frac": kernel_tflops / peak, "traffic": None, "peak_kind": f"{peak_kind} burst cuBLAS bf16",
+                         "frac_of_nominal_2250": kernel_tflops / 2250.0},
+            "cpu_baseline": cpu_baseline,
+        }
+        if extras is not None:
+            line["kernels"] = extras
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--variant", choices=["1sm", "2sm"], default="1sm")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -147,6 +147,20 @@ PB200_API int    pb200_destroy(int64_t handle);
  * (pyptx/ptx.py:2311-2337). */
 PB200_API int pb200_device_status(char* err_out);
 
+/* Host-side evaluation of the encodings the matrix kernels use, exported so
+ * that tests can pin them to the reference's known answers.
+ *   pb200_encode_idesc      tcgen05 instruction descriptor, kind::f16, f32 accumulate
+ *                           (pyptx/ptx.py:3312-3366; tests/test_typed_wrappers.py:407-425)
+ *   pb200_encode_smem_desc  shared-memory matrix descriptor; layout 0/2/4/6 = none/128B/64B/32B
+ *                           (pyptx/ptx.py:3368-3459; tests/test_typed_wrappers.py:427-438)
+ *   pb200_swizzle128        byte offset -> swizzled byte offset, Swizzle<3,4,3>
+ *                           (pyptx/smem.py:476-492) */
+PB200_API uint32_t pb200_encode_idesc(int32_t m, int32_t n, int32_t bf16_inputs,
+                                      int32_t a_mn_major, int32_t b_mn_major);
+PB200_API uint64_t pb200_encode_smem_desc(uint32_t smem_addr, uint32_t leading_bytes,
+                                          uint32_t stride_bytes, uint32_t layout);
+PB200_API uint32_t pb200_swizzle128(uint32_t byte_offset);
+
 /* Library version and the architecture the kernels were compiled for. */
 PB200_API const char* pb200_version(void);
 PB200_API const char* pb200_arch(void);

@@ -1,0 +1,85 @@
+"""fp32 CPU formulas -- the numerical oracle.  TEST INFRASTRUCTURE, NOT PRODUCT CODE.
+
+Each function restates the torch expression the reference compares its kernel
+against (file:line given per function) and runs it with torch on the host in
+float32.  bf16 inputs are widened to float32 first, so matrix products are
+fp32-accumulated results of the bf16-rounded operands.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+
+def rms_norm_ref(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """examples/blackwell/rms_norm.py:62-63 (torch case); examples/hopper/rms_norm.py:189-192."""
+    x = x.float()
+    ms = (x * x).mean(dim=-1, keepdim=True)
+    return x * torch.rsqrt(ms + eps) * w.float()
+
+
+def layer_norm_ref(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
+    """examples/hopper/layer_norm.py:232-236; tests/test_torch_dispatch.py:65-67
+    (equivalent to F.layer_norm, examples/blackwell/layer_norm.py:74)."""
+    x = x.float()
+    mean = x.mean(dim=-1, keepdim=True)
+    var = ((x - mean) ** 2).mean(dim=-1, keepdim=True)
+    return (x - mean) * torch.rsqrt(var + eps) * w.float() + b.float()
+
+
+def swiglu_ref(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """examples/blackwell/swiglu.py:66; examples/hopper/swiglu.py:163-164."""
+    return torch.nn.functional.silu(gate.float()) * up.float()
+
+
+def softmax_ref(x: torch.Tensor) -> torch.Tensor:
+    """examples/hopper/softmax.py:189-193 and :224."""
+    return torch.softmax(x.float(), dim=-1)
+
+
+def gemm_ref(a: torch.Tensor, b_t: torch.Tensor) -> torch.Tensor:
+    """``a.float() @ b.float()`` (examples/blackwell/gemm_highperf_blackwell.py:1268) with
+    the kernel's operand convention: ``b_t`` is ``b.t().contiguous()`` (:1264)."""
+    return a.float() @ b_t.float().t()
+
+
+def grouped_gemm_ref(a2: torch.Tensor, b_t2: torch.Tensor, G: int) -> torch.Tensor:
+    """``einsum("gmk,gkn->gmn")`` in fp32 (examples/blackwell/grouped_gemm.py:306) on the
+    stacked operands ``a2[G*M,K]`` and ``b_t2[G*N,K]`` (:302-303); returns ``[G*M, N]``."""
+    gm, k = a2.shape
+    gn = b_t2.shape[0]
+    m, n = gm // G, gn // G
+    a3 = a2.float().reshape(G, m, k)
+    b3 = b_t2.float().reshape(G, n, k).transpose(1, 2)
+    return torch.einsum("gmk,gkn->gmn", a3, b3).reshape(G * m, n)
+
+
+def attention_ref(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool = False,
+                  sm_scale: float | None = None) -> torch.Tensor:
+    """``softmax(q k^T * scale) v`` in fp32 per leading index
+    (examples/hopper/experimental/flash_attention_hopper.py:479).  ``q[..., M, d]``,
+    ``k[..., N, d]``, ``v[..., N, d]``.  ``causal`` adds the lower-triangular mask
+    before the softmax (query i sees keys j <= i + N - M); the reference has no
+    causal case."""
+    q, k, v = q.float(), k.float(), v.float()
+    d = q.shape[-1]
+    scale = (1.0 / math.sqrt(d)) if sm_scale is None else sm_scale
+    s = q @ k.transpose(-1, -2) * scale
+    if causal:
+        m, n = s.shape[-2], s.shape[-1]
+        mask = torch.ones(m, n, dtype=torch.bool).tril(diagonal=n - m)
+        s = s.masked_fill(~mask, float("-inf"))
+    return torch.softmax(s, dim=-1) @ v
+
+
+def rel_fro(out: torch.Tensor, ref: torch.Tensor) -> float:
+    """Relative Frobenius error ``|out-ref|_F / |ref|_F`` in float64."""
+    o, r = out.double().cpu(), ref.double().cpu()
+    return float((o - r).norm() / r.norm().clamp_min(1e-300))
+
+
+def max_scaled_err(out: torch.Tensor, ref: torch.Tensor) -> float:
+    """``max |out-ref| / max(|ref|, 1)``, the elementwise companion of ``rel_fro``."""
+    o, r = out.double().cpu(), ref.double().cpu()
+    return float(((o - r).abs() / r.abs().clamp_min(1.0)).max())

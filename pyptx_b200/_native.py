@@ -35,6 +35,7 @@ EXPORTED_SYMBOLS = (
     "pb200_create", "pb200_launch_raw", "pb200_geometry_of", "pb200_has_handle",
     "pb200_registry_size", "pb200_clear_registry", "pb200_destroy",
     "pb200_device_status", "pb200_version", "pb200_arch",
+    "pb200_encode_idesc", "pb200_encode_smem_desc", "pb200_swizzle128",
 )
 
 
@@ -175,6 +176,12 @@ def load():
         lib.pb200_version.argtypes = []
         lib.pb200_arch.restype = c.c_char_p
         lib.pb200_arch.argtypes = []
+        lib.pb200_encode_idesc.restype = c.c_uint32
+        lib.pb200_encode_idesc.argtypes = [c.c_int32] * 5
+        lib.pb200_encode_smem_desc.restype = c.c_uint64
+        lib.pb200_encode_smem_desc.argtypes = [c.c_uint32] * 4
+        lib.pb200_swizzle128.restype = c.c_uint32
+        lib.pb200_swizzle128.argtypes = [c.c_uint32]
         _LIB = lib
     return _LIB
 

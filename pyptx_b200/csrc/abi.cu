@@ -9,6 +9,7 @@
 // under a plain mutex, pyptx_launch.cc:330-343).  Error text goes to the
 // caller's buffer, never to shared state.
 #include "common.cuh"
+#include "ptx.cuh"
 
 #include <atomic>
 #include <cstdarg>
@@ -208,6 +209,14 @@ PB200_API int pb200_device_status(char* err_out) {
     set_err(err_out, "device wait gave up: kernel %d, wait site %d, block %d", host[1], host[2], host[3]);
     return PB200_ERR_DEVICE_TIMEOUT;
 }
+
+PB200_API uint32_t pb200_encode_idesc(int32_t m, int32_t n, int32_t bf16_inputs, int32_t a_mn_major, int32_t b_mn_major) {
+    return ptx::make_idesc_f16(m, n, bf16_inputs != 0, a_mn_major != 0, b_mn_major != 0);
+}
+PB200_API uint64_t pb200_encode_smem_desc(uint32_t smem_addr, uint32_t leading_bytes, uint32_t stride_bytes, uint32_t layout) {
+    return ptx::make_smem_desc(smem_addr, leading_bytes, stride_bytes, layout);
+}
+PB200_API uint32_t pb200_swizzle128(uint32_t byte_offset) { return ptx::swizzle128(byte_offset); }
 
 PB200_API const char* pb200_version(void) { return "0.1.0"; }
 PB200_API const char* pb200_arch(void) { return "sm_100a"; }

@@ -1,0 +1,230 @@
+"""GPU parity of the tcgen05 GEMMs (1-SM, 2-SM, grouped) against the fp32-accumulated CPU
+oracle: known-answer patterns that pin the tensor-core operand layout (the ideas of the
+reference's examples/blackwell/tcgen05_suite.py:55-241), the golden vectors, the
+reference's shape lists (gemm_highperf_blackwell.py:1337-1354, grouped_gemm.py:343-352)
+and the benchmark configurations."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import formulas, inputs
+from pyptx_b200 import _ids
+from pyptx_b200.examples.blackwell.gemm_highperf_blackwell import build_gemm, build_gemm_2sm
+from pyptx_b200.examples.blackwell.grouped_gemm import build_grouped_gemm
+from pyptx_b200.kernel import NativeKernel
+from pyptx_b200.types import bf16
+from tests.gpu_util import check_bf16_matmul
+
+pytestmark = pytest.mark.gpu
+
+BUILDERS = {"1sm": build_gemm, "2sm": build_gemm_2sm}
+
+
+def _bf16(a: np.ndarray) -> torch.Tensor:
+    return torch.from_numpy(a.copy()).view(torch.bfloat16)
+
+
+def _min_m(kind):
+    return 256 if kind == "2sm" else 128
+
+
+@pytest.fixture(scope="module")
+def mats(golden_dir):
+    return np.load(os.path.join(golden_dir, "matmul_refs.npz"))
+
+
+# ---- known answers ---------------------------------------------------------------
+
+@pytest.mark.parametrize("kind", ["1sm", "2sm"])
+@pytest.mark.parametrize("K", [64, 128, 256, 320, 1024])
+def test_ones_gives_k(kind, K):
+    """ones x ones = K in every element: exact in bf16 inputs / fp32 accumulate."""
+    M, N = _min_m(kind), 256
+    a = torch.ones(M, K, dtype=torch.bfloat16, device="cuda")
+    bt = torch.ones(N, K, dtype=torch.bfloat16, device="cuda")
+    d = BUILDERS[kind](M, N, K)(a, bt)
+    assert d.dtype == torch.float32 and d.shape == (M, N)
+    assert torch.equal(d.cpu(), torch.full((M, N), float(K)))
+
+
+@pytest.mark.parametrize("kind", ["1sm", "2sm"])
+def test_row_and_column_coded_operands(kind):
+    """A[i,:] = i+1 on one k, B = e_k  ->  D[i,j] pins row/column/k placement exactly."""
+    M, N, K = 2 * _min_m(kind), 512, 128
+    a = torch.zeros(M, K)
+    bt = torch.zeros(N, K)
+    a[:, 3] = torch.arange(1, M + 1, dtype=torch.float32) % 251      # exactly representable in bf16
+    bt[:, 3] = torch.arange(1, N + 1, dtype=torch.float32) % 127
+    a[:, 77] = 1.0
+    bt[:, 77] = 2.0
+    ref = a @ bt.t()
+    d = BUILDERS[kind](M, N, K)(a.to(torch.bfloat16).cuda(), bt.to(torch.bfloat16).cuda())
+    assert torch.equal(d.cpu(), ref)
+
+
+@pytest.mark.parametrize("kind", ["1sm", "2sm"])
+def test_k_lane_map(kind):
+    """Each k contributes with its own weight: D = sum_k 2^-(k%8) * (k//8+1) pattern, exact."""
+    M, N, K = _min_m(kind), 256, 64
+    a = torch.zeros(M, K)
+    bt = torch.zeros(N, K)
+    for k in range(K):
+        a[:, k] = 2.0 ** -(k % 8)
+        bt[:, k] = float(k // 8 + 1)
+    ref = a @ bt.t()
+    d = BUILDERS[kind](M, N, K)(a.to(torch.bfloat16).cuda(), bt.to(torch.bfloat16).cuda())
+    assert torch.equal(d.cpu(), ref)
+
+
+@pytest.mark.parametrize("kind", ["1sm", "2sm"])
+def test_identity_selects_rows(kind):
+    """A = I (K = M): D = B, bit-exact; exercises every 128-byte swizzle row of both operands."""
+    M = K = 256
+    N = 256
+    g = torch.Generator().manual_seed(7)
+    b = torch.randn(K, N, generator=g).to(torch.bfloat16)
+    a = torch.eye(M, K).to(torch.bfloat16)
+    d = BUILDERS[kind](M, N, K)(a.cuda(), b.t().contiguous().cuda())
+    assert torch.equal(d.cpu(), b.float())
+
+
+# ---- golden vectors and the reference's shape lists ----------------------------------
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 128)])
+def test_golden_gemm(mats, M, N, K):
+    a, bt = _bf16(mats[f"gemm_{M}_{N}_{K}_a"]), _bf16(mats[f"gemm_{M}_{N}_{K}_bt"])
+    d = build_gemm(M, N, K)(a.cuda(), bt.cuda()).cpu()
+    ref = torch.from_numpy(mats[f"gemm_{M}_{N}_{K}_d"])
+    check_bf16_matmul(d, ref, 1e-5)   # same bf16 inputs, fp32 accumulate: only summation order differs
+    assert torch.allclose(d, ref, atol=5e-2, rtol=5e-2)  # the reference's own criterion (:1270)
+
+
+REF_GEMM_SHAPES = [(128, 256, 64), (128, 256, 128), (256, 256, 256), (256, 512, 256), (512, 512, 512),
+                   (1024, 1024, 512), (384, 768, 192), (2048, 2048, 2048)]
+
+
+@pytest.mark.parametrize("kind", ["1sm", "2sm"])
+@pytest.mark.parametrize("M,N,K", REF_GEMM_SHAPES)
+def test_gemm_shapes(kind, M, N, K):
+    if M % _min_m(kind):
+        pytest.skip("M not divisible by the 2-SM tile")
+    a, bt = inputs.gemm_inputs(M, N, K)
+    d = BUILDERS[kind](M, N, K)(a.cuda(), bt.cuda()).cpu()
+    check_bf16_matmul(d, formulas.gemm_ref(a, bt), 1e-4)
+
+
+@pytest.mark.parametrize("kind", ["1sm", "2sm"])
+def test_pipeline_wraparound_and_many_tiles(kind):
+    """K-tiles = stages-1, stages, stages+1, 2*stages+1 and more tiles than SMs: phase bits of the
+    shared-memory ring and of the double-buffered accumulator must stay consistent."""
+    for K in (192, 256, 320, 384, 448, 576, 832):
+        a, bt = inputs.gemm_inputs(256, 256, K)
+        d = BUILDERS[kind](256, 256, K)(a.cuda(), bt.cuda()).cpu()
+        check_bf16_matmul(d, formulas.gemm_ref(a, bt), 1e-4)
+    M, N, K = 4096, 4096 + 256, 128          # 544 / 272 tiles: > 3 per SM, odd count per SM
+    a, bt = inputs.gemm_inputs(M, N, K)
+    d = BUILDERS[kind](M, N, K)(a.cuda(), bt.cuda()).cpu()
+    check_bf16_matmul(d, formulas.gemm_ref(a, bt), 1e-4)
+
+
+@pytest.mark.parametrize("kind", ["1sm", "2sm"])
+@pytest.mark.parametrize("width", [1, 3, 16, 64])
+def test_raster_band_width(kind, width):
+    M, N, K = 1280, 768, 128
+    a, bt = inputs.gemm_inputs(M, N, K)
+    d = BUILDERS[kind](M, N, K, grid_tile_width=width)(a.cuda(), bt.cuda()).cpu()
+    check_bf16_matmul(d, formulas.gemm_ref(a, bt), 1e-4)
+
+
+@pytest.mark.parametrize("kind", ["1sm", "2sm"])
+def test_bf16_output(kind):
+    M, N, K = 512, 512, 256
+    a, bt = inputs.gemm_inputs(M, N, K)
+    d = BUILDERS[kind](M, N, K, out_dtype=bf16)(a.cuda(), bt.cuda())
+    assert d.dtype == torch.bfloat16
+    ref = formulas.gemm_ref(a, bt)
+    assert torch.equal(d.cpu(), ref.to(torch.bfloat16)) or formulas.rel_fro(d.float().cpu(), ref) < 4e-3
+    check_bf16_matmul(d.cpu(), ref)
+
+
+@pytest.mark.parametrize("kind_id", [_ids.K_GEMM_1SM, _ids.K_GEMM_2SM])
+def test_direct_store_epilogue_agrees(kind_id):
+    """The register-to-global epilogue (a debugging variant) and the TMA-store epilogue give
+    identical bits."""
+    from pyptx_b200.specs import Tile
+    from pyptx_b200.types import f32
+    M, N, K = 512, 768, 256
+    a, bt = inputs.gemm_inputs(M, N, K)
+    specs = dict(in_specs=(Tile(M, K, bf16), Tile(N, K, bf16)), out_specs=(Tile(M, N, f32),))
+    tma = NativeKernel("gemm_tma", kind_id, (M, N, K), **specs)(a.cuda(), bt.cuda())
+    direct = NativeKernel("gemm_direct", kind_id, (M, N, K), flags=1 << 16, **specs)(a.cuda(), bt.cuda())
+    assert torch.equal(tma, direct)
+
+
+@pytest.mark.parametrize("kind", ["1sm", "2sm"])
+@pytest.mark.parametrize("S", [2048, 4096])
+def test_benchmark_sizes(kind, S):
+    a, bt = inputs.gemm_inputs(S, S, S)
+    d = BUILDERS[kind](S, S, S)(a.cuda(), bt.cuda()).cpu()
+    check_bf16_matmul(d, formulas.gemm_ref(a, bt))
+
+
+@pytest.mark.parametrize("kind", ["1sm", "2sm"])
+def test_8192_cubed_properties(kind):
+    """Full benchmark size.  The fp32 CPU product of 8192^3 takes too long for a unit test, so
+    the oracle is evaluated on sampled row and column blocks, and linearity D(A1+A2) = D(A1)+D(A2)
+    (exact for operands chosen so that no bf16 rounding occurs) covers the whole output."""
+    S = 8192
+    a, bt = inputs.gemm_inputs(S, S, S)
+    k = BUILDERS[kind](S, S, S)
+    d = k(a.cuda(), bt.cuda())
+    for r0 in (0, 3968, 8064):
+        ref = formulas.gemm_ref(a[r0:r0 + 128], bt)
+        check_bf16_matmul(d[r0:r0 + 128].cpu(), ref, 1e-4)
+    for c0 in (256, 7936):
+        ref = formulas.gemm_ref(a, bt[c0:c0 + 64])
+        check_bf16_matmul(d[:, c0:c0 + 64].cpu(), ref, 1e-4)
+    ones = torch.ones(S, S, dtype=torch.bfloat16, device="cuda")
+    dk = k(ones, ones)
+    assert bool((dk == float(S)).all())
+    del d, dk
+
+
+# ---- grouped ---------------------------------------------------------------------
+
+@pytest.mark.parametrize("G,M,N,K", [(2, 128, 64, 64), (2, 128, 128, 128)])
+def test_golden_grouped(mats, G, M, N, K):
+    a, bt = _bf16(mats[f"grouped_{G}_{M}_{N}_{K}_a"]), _bf16(mats[f"grouped_{G}_{M}_{N}_{K}_bt"])
+    c = build_grouped_gemm(G, M, N, K)(a.cuda(), bt.cuda()).cpu()
+    ref = torch.from_numpy(mats[f"grouped_{G}_{M}_{N}_{K}_c"])
+    check_bf16_matmul(c, ref, 1e-5)
+    assert torch.allclose(c, ref, atol=5e-3, rtol=5e-3)   # the reference's own criterion (:308)
+
+
+@pytest.mark.parametrize("G,M,N,K", [(1, 128, 64, 64), (4, 128, 128, 128), (8, 512, 128, 512), (8, 1024, 128, 1024),
+                                     (3, 256, 192, 320), (4, 2048, 256, 2048), (8, 2048, 256, 2048),
+                                     (16, 128, 512, 64)])
+def test_grouped_shapes(G, M, N, K):
+    a, bt = inputs.grouped_gemm_inputs(G, M, N, K)
+    c = build_grouped_gemm(G, M, N, K)(a.cuda(), bt.cuda()).cpu()
+    check_bf16_matmul(c, formulas.grouped_gemm_ref(a, bt, G), 1e-4)
+
+
+def test_grouped_experts_do_not_mix():
+    """Expert g's output depends only on expert g's operands."""
+    G, M, N, K = 4, 256, 256, 128
+    a, bt = inputs.grouped_gemm_inputs(G, M, N, K)
+    k = build_grouped_gemm(G, M, N, K)
+    base = k(a.cuda(), bt.cuda()).cpu()
+    a2 = a.clone()
+    a2[2 * M:3 * M] = 0
+    out = k(a2.cuda(), bt.cuda()).cpu()
+    assert torch.equal(out[:2 * M], base[:2 * M]) and torch.equal(out[3 * M:], base[3 * M:])
+    assert torch.count_nonzero(out[2 * M:3 * M]) == 0
+
+
+def test_no_device_wait_gave_up():
+    from pyptx_b200 import _native
+    _native.device_status()

@@ -1,7 +1,487 @@
-// Flash-attention forward for sm_100a (placeholder until the tcgen05 kernel lands).
+// Flash-attention forward for sm_100a on tcgen05 tensor cores.
+//   O[bh, i, :] = softmax_j(scale * Q[bh, i, :] . K[bh, j, :]  (+ causal mask)) . V[bh, j, :]
+// bf16 operands, fp32 scores / statistics / accumulator, P rounded to bf16 before the
+// second product -- the arithmetic of the reference's algorithm
+// (examples/hopper/experimental/flash_attention_hopper.py:158-256: scores, running max,
+// alpha rescale, P -> bf16, acc += P V, final 1/l), re-designed for Blackwell, with the
+// batch*head dimension, head_dim 128 and the causal mask the reference lacks.
+//
+// One CTA owns 256 query rows of one (batch, head) as two 128-row tiles that ping-pong:
+// while the softmax warps of one tile work, the tensor core runs the other tile's MMAs.
+//   warp 0      TMA producer: Q once, then K and V tiles of 128 keys through 2-3 stage rings
+//   warp 1      MMA issuer (single thread): S_t = Q_t K^T into TMEM, O_t += P_t V
+//   warps 4-7   softmax for tile 0 (one query row per thread, TMEM lane = row)
+//   warps 8-11  softmax for tile 1
+// TMEM (512 columns): S0 | S1 | O0 | O1, 128 columns each.  P overwrites the first 64
+// columns of its S in place (two bf16 per column) and is consumed by the MMA directly
+// from TMEM, so P never touches shared memory.  A template switch keeps P in swizzled
+// shared memory instead (head_dim 64 only) as a cross-check of the TMEM-operand path.
+// V (keys x head_dim, head_dim contiguous) and, when the caller passes the reference's
+// transposed K (head_dim x keys), K are consumed as MN-major B operands.
+// The accumulator is rescaled lazily: the running reference maximum only moves when the
+// true maximum has grown by more than 2^8, which keeps P within bf16/fp32 range and makes
+// the TMEM round trip of O rare; the final division by l makes the result independent of it.
+// Every mbarrier wait is bounded and reports through the status word.
 #include "common.cuh"
+#include "ptx.cuh"
+
+#include <cuda_bf16.h>
+
+#include <atomic>
+#include <cmath>
 
 namespace pb200 {
-int plan_attention(Record&, char* err) { set_err(err, "flash attention is not built yet"); return PB200_ERR_BAD_KERNEL; }
-int launch_attention(const Record&, cudaStream_t, void**, char* err) { set_err(err, "flash attention is not built yet"); return PB200_ERR_BAD_KERNEL; }
+namespace {
+
+using namespace ptx;
+
+constexpr int kQTile = 128;       // query rows per tile (TMEM lanes)
+constexpr int kKvTile = 128;      // keys per K/V tile
+constexpr int kFmhaThreads = 384; // 12 warps
+constexpr uint32_t kDebugPSmem = 1u << 17;   // create flag: keep P in shared memory (head_dim 64)
+constexpr float kRescaleThreshold = 8.0f;    // log2 units
+
+struct FmhaParams {
+    int bh;            // batch * heads
+    int s_q;
+    int s_kv;
+    int causal;
+    int k_transposed;
+    float scale_log2;  // sm_scale * log2(e)
+    int causal_offset; // s_kv - s_q: query i sees keys j <= i + offset
+};
+
+template <int HD, bool P_SMEM>
+struct FmhaSmem {
+    static constexpr int kStages = HD == 64 ? 3 : 2;
+    static constexpr int kQBytes = kQTile * HD * 2;          // per tile
+    static constexpr int kKvBytes = kKvTile * HD * 2;        // per stage, K or V
+    static constexpr int kPBytes = P_SMEM ? kQTile * kKvTile * 2 : 0;   // per tile
+    static constexpr int kOffQ = 0;
+    static constexpr int kOffK = kOffQ + 2 * kQBytes;
+    static constexpr int kOffV = kOffK + kStages * kKvBytes;
+    static constexpr int kOffP = kOffV + kStages * kKvBytes;
+    static constexpr int kOffBar = kOffP + 2 * kPBytes;
+    static constexpr int kTotal = kOffBar + 512 + 1024;
+    static_assert(kTotal <= 227 * 1024, "shared memory budget exceeded");
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <int HD, typename OutT, bool P_SMEM>
+__global__ void __launch_bounds__(kFmhaThreads, 1)
+fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
+                const __grid_constant__ CUtensorMap tmap_k,
+                const __grid_constant__ CUtensorMap tmap_v,
+                OutT* __restrict__ out, FmhaParams prm, int* status) {
+    using L = FmhaSmem<HD, P_SMEM>;
+    constexpr int kStages = L::kStages;
+    constexpr int kDBlocks = HD / 64;                  // 64-element (128-byte) blocks along head_dim
+    constexpr uint32_t kIdescS = make_idesc_f16(kQTile, kKvTile, true, 0, 0);
+    constexpr uint32_t kIdescS_T = make_idesc_f16(kQTile, kKvTile, true, 0, 1);   // K given transposed
+    constexpr uint32_t kIdescPV = make_idesc_f16(kQTile, HD, true, 0, 1);         // V is MN-major
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t s_q = base + L::kOffQ, s_k = base + L::kOffK, s_v = base + L::kOffV, s_p = base + L::kOffP;
+    const uint32_t bars = base + L::kOffBar;
+    const uint32_t bar_q = bars;                        // [1]
+    const uint32_t bar_kfull = bars + 8;                // [kStages]
+    const uint32_t bar_kempty = bar_kfull + 8 * kStages;
+    const uint32_t bar_vfull = bar_kempty + 8 * kStages;
+    const uint32_t bar_vempty = bar_vfull + 8 * kStages;
+    const uint32_t bar_sfull = bar_vempty + 8 * kStages;   // [2]
+    const uint32_t bar_pfull = bar_sfull + 16;             // [2]
+    const uint32_t bar_ofull = bar_pfull + 16;             // [2]
+    const uint32_t s_tmem_slot = bar_ofull + 16;
+    const uint32_t s_abort = s_tmem_slot + 8;
+    volatile uint32_t* tmem_slot_gen = (volatile uint32_t*)(gen + (s_tmem_slot - base));
+    volatile int* abort_gen = (volatile int*)(gen + (s_abort - base));
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int n_qblocks = (int)gridDim.x;
+    // Heaviest causal blocks (largest row index) first.
+    const int qblock = n_qblocks - 1 - (int)blockIdx.x;
+    const int bh = (int)blockIdx.y;
+    const int q0 = qblock * 2 * kQTile;
+    const bool has_t1 = q0 + kQTile < prm.s_q;
+    // Number of K/V tiles each query tile visits.
+    int n_kv[2];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        int n = prm.s_kv / kKvTile;
+        if (prm.causal) {
+            const int last_key = q0 + t * kQTile + kQTile - 1 + prm.causal_offset;   // of the tile's last row
+            n = min(n, max(last_key / kKvTile + 1, 1));
+        }
+        n_kv[t] = n;
+    }
+    if (!has_t1) n_kv[1] = 0;
+    const int n_iter = max(n_kv[0], n_kv[1]);
+
+    WaitCtx ctx{status, abort_gen, PB200_K_FLASH_ATTN};
+
+    if (threadIdx.x == 0) {
+        *abort_gen = 0;
+        mbar_init(bar_q, 1);
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(bar_kfull + 8 * s, 1); mbar_init(bar_kempty + 8 * s, 1);
+            mbar_init(bar_vfull + 8 * s, 1); mbar_init(bar_vempty + 8 * s, 1);
+        }
+        for (int t = 0; t < 2; ++t) {
+            mbar_init(bar_sfull + 8 * t, 1);
+            mbar_init(bar_pfull + 8 * t, 4);     // one arrival per softmax warp
+            mbar_init(bar_ofull + 8 * t, 1);
+        }
+        fence_mbarrier_init();
+        fence_proxy_async_smem();
+        prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
+    }
+    if (warp == 1) {
+        tmem_alloc<1>(s_tmem_slot, 512);
+        tmem_relinquish<1>();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot_gen;
+    const uint32_t tmem_s[2] = {tmem_base, tmem_base + 128u};
+    const uint32_t tmem_o[2] = {tmem_base + 256u, tmem_base + 384u};
+
+    if (warp == 0) {
+        // ------------------------------- TMA producer -------------------------------
+        if (lane == 0) {
+            const int n_tiles = has_t1 ? 2 : 1;
+            mbar_arrive_expect_tx(bar_q, (uint32_t)(n_tiles * L::kQBytes));
+            for (int t = 0; t < n_tiles; ++t)
+                for (int db = 0; db < kDBlocks; ++db)
+                    tma_load_3d(s_q + t * L::kQBytes + db * (kQTile * 128), &tmap_q, bar_q, db * 64, q0 + t * kQTile, bh);
+            int stage = 0; uint32_t phase = 0;
+            bool ok = true;
+            for (int j = 0; j < n_iter && ok; ++j) {
+                if (!(ok = mbar_wait(bar_kempty + 8 * stage, phase ^ 1u, ctx, 11))) break;
+                mbar_arrive_expect_tx(bar_kfull + 8 * stage, (uint32_t)L::kKvBytes);
+                if (!prm.k_transposed) {
+                    for (int db = 0; db < kDBlocks; ++db)
+                        tma_load_3d(s_k + stage * L::kKvBytes + db * (kKvTile * 128), &tmap_k, bar_kfull + 8 * stage,
+                                    db * 64, j * kKvTile, bh);
+                } else {
+                    // K_t[bh][HD][s_kv]: two boxes of 64 keys x HD rows
+                    for (int nb = 0; nb < kKvTile / 64; ++nb)
+                        tma_load_3d(s_k + stage * L::kKvBytes + nb * (HD * 128), &tmap_k, bar_kfull + 8 * stage,
+                                    j * kKvTile + nb * 64, 0, bh);
+                }
+                if (!(ok = mbar_wait(bar_vempty + 8 * stage, phase ^ 1u, ctx, 12))) break;
+                mbar_arrive_expect_tx(bar_vfull + 8 * stage, (uint32_t)L::kKvBytes);
+                for (int db = 0; db < kDBlocks; ++db)
+                    tma_load_3d(s_v + stage * L::kKvBytes + db * (kKvTile * 128), &tmap_v, bar_vfull + 8 * stage,
+                                db * 64, j * kKvTile, bh);
+                if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------- MMA issuer ---------------------------------
+        if (lane == 0) {
+            bool ok = mbar_wait(bar_q, 0, ctx, 21);
+            // S_t(j) = Q_t . K(j)^T : HD/16 MMAs of K = 16.
+            auto issue_s = [&](int t, int kstage) {
+                const uint32_t qa = s_q + t * L::kQBytes;
+                const uint32_t kb = s_k + kstage * L::kKvBytes;
+#pragma unroll
+                for (int k = 0; k < HD / 16; ++k) {
+                    const uint64_t da = make_desc_kmajor_sw128(qa + (k >> 2) * (kQTile * 128) + (k & 3) * 32);
+                    uint64_t db;
+                    if (!prm.k_transposed)
+                        db = make_desc_kmajor_sw128(kb + (k >> 2) * (kKvTile * 128) + (k & 3) * 32);
+                    else
+                        db = make_smem_desc(kb + k * 2048, HD * 128, 1024, 2);
+                    umma_f16_ss<1>(tmem_s[t], da, db, prm.k_transposed ? kIdescS_T : kIdescS, k != 0 ? 1u : 0u);
+                }
+            };
+            // O_t += P_t . V(j) : 128/16 MMAs of K = 16.
+            auto issue_pv = [&](int t, int vstage, bool first) {
+                const uint32_t vb = s_v + vstage * L::kKvBytes;
+#pragma unroll
+                for (int k = 0; k < kKvTile / 16; ++k) {
+                    const uint64_t db = make_smem_desc(vb + k * 2048, kKvTile * 128, 1024, 2);
+                    const uint32_t acc = (first && k == 0) ? 0u : 1u;
+                    if (P_SMEM) {
+                        const uint64_t da = make_desc_kmajor_sw128(s_p + t * L::kPBytes + (k >> 2) * (kQTile * 128) + (k & 3) * 32);
+                        umma_f16_ss<1>(tmem_o[t], da, db, kIdescPV, acc);
+                    } else {
+                        umma_f16_ts(tmem_o[t], tmem_s[t] + (uint32_t)(k * 8), db, kIdescPV, acc);
+                    }
+                }
+            };
+            int kstage = 0; uint32_t kphase = 0;     // ring position of K(j+1) being consumed by S
+            int vstage = 0; uint32_t vphase = 0;     // ring position of V(j)
+            if (ok && n_iter > 0) {
+                ok = mbar_wait(bar_kfull + 8 * kstage, kphase, ctx, 22);
+                if (ok) {
+                    tc_fence_after_sync();
+                    issue_s(0, kstage); umma_commit<1>(bar_sfull + 0);
+                    if (n_kv[1] > 0) { issue_s(1, kstage); umma_commit<1>(bar_sfull + 8); }
+                    umma_commit<1>(bar_kempty + 8 * kstage);
+                    if (++kstage == kStages) { kstage = 0; kphase ^= 1u; }
+                }
+            }
+            for (int j = 0; j < n_iter && ok; ++j) {
+                const uint32_t jpar = (uint32_t)j & 1u;
+                const bool more = j + 1 < n_iter;
+                if (!(ok = mbar_wait(bar_vfull + 8 * vstage, vphase, ctx, 23))) break;
+                if (more && !(ok = mbar_wait(bar_kfull + 8 * kstage, kphase, ctx, 24))) break;
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+                    if (j < n_kv[t]) {
+                        if (!(ok = mbar_wait(bar_pfull + 8 * t, jpar, ctx, 25 + t))) break;
+                        tc_fence_after_sync();
+                        issue_pv(t, vstage, j == 0);
+                        if (j + 1 < n_kv[t]) { issue_s(t, kstage); umma_commit<1>(bar_sfull + 8 * t); }
+                        else umma_commit<1>(bar_ofull + 8 * t);
+                    }
+                }
+                if (!ok) break;
+                umma_commit<1>(bar_vempty + 8 * vstage);
+                if (++vstage == kStages) { vstage = 0; vphase ^= 1u; }
+                if (more) {
+                    umma_commit<1>(bar_kempty + 8 * kstage);
+                    if (++kstage == kStages) { kstage = 0; kphase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp >= 4) {
+        // ------------------------------- softmax + epilogue --------------------------
+        const int t = (warp - 4) >> 2;                   // query tile of this warp group
+        const int q = warp & 3;                          // TMEM lane quarter
+        const int row_in_tile = q * 32 + lane;
+        const int row = q0 + t * kQTile + row_in_tile;   // query index inside this (batch, head)
+        const uint32_t lane_off = (uint32_t)(q * 32) << 16;
+        const uint32_t ts = tmem_s[t] + lane_off;
+        const uint32_t to = tmem_o[t] + lane_off;
+        const int n = n_kv[t];
+        float m_used = -INFINITY;     // reference maximum currently baked into O and l (log2 units)
+        float l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n && ok; ++j) {
+            ok = mbar_wait(bar_sfull + 8 * t, (uint32_t)j & 1u, ctx, 31 + t);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const int key0 = j * kKvTile;
+            const int last_visible = row + prm.causal_offset;           // largest key index this row may see
+            const bool diag = prm.causal && (key0 + kKvTile - 1 > q0 + t * kQTile + q * 32 + prm.causal_offset);
+            // pass 1: row maximum of the raw scores
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < kKvTile / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(ts + (uint32_t)(c * 32), v);
+                tmem_ld_wait();
+                if (diag) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (key0 + c * 32 + i <= last_visible) mx = fmaxf(mx, __uint_as_float(v[i]));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+                }
+            }
+            const float m_new = fmaxf(m_used, mx * prm.scale_log2);
+            if (j == 0) {
+                m_used = m_new;
+            } else if (__any_sync(0xffffffffu, m_new - m_used > kRescaleThreshold)) {
+                const float alpha = fast_exp2(m_used - m_new);     // 1 for lanes whose maximum did not move
+                m_used = m_new;
+                l *= alpha;
+#pragma unroll 1
+                for (int c = 0; c < HD / 32; ++c) {
+                    uint32_t o[32];
+                    tmem_ld_32x32b_x32(to + (uint32_t)(c * 32), o);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    tmem_st_32x32b_x32(to + (uint32_t)(c * 32), o);
+                }
+                tmem_st_wait();
+            }
+            // pass 2: P = exp2(S * scale - m_used), row sum, bf16 P to TMEM (or shared memory)
+            float sum = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < kKvTile / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(ts + (uint32_t)(c * 32), v);
+                tmem_ld_wait();
+                uint32_t packed[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    float p0 = fast_exp2(fmaf(__uint_as_float(v[2 * i]), prm.scale_log2, -m_used));
+                    float p1 = fast_exp2(fmaf(__uint_as_float(v[2 * i + 1]), prm.scale_log2, -m_used));
+                    if (diag) {
+                        if (key0 + c * 32 + 2 * i > last_visible) p0 = 0.f;
+                        if (key0 + c * 32 + 2 * i + 1 > last_visible) p1 = 0.f;
+                    }
+                    sum += p0 + p1;
+                    __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);    // .x = p0 in the low half
+                    packed[i] = *reinterpret_cast<uint32_t*>(&b);
+                }
+                if (P_SMEM) {
+                    // K-major SWIZZLE_128B image: 64-key blocks of [128 rows][128 bytes]
+                    const uint32_t rowp = s_p + t * L::kPBytes + (uint32_t)(c >> 1) * (kQTile * 128) + (uint32_t)row_in_tile * 128u;
+#pragma unroll
+                    for (int jj = 0; jj < 4; ++jj) {
+                        const uint32_t chunk = (uint32_t)((c & 1) * 4 + jj);
+                        st_shared_v4(rowp + ((chunk ^ (uint32_t)(row_in_tile & 7)) << 4),
+                                     packed[4 * jj], packed[4 * jj + 1], packed[4 * jj + 2], packed[4 * jj + 3]);
+                    }
+                } else {
+                    tmem_st_32x32b_x16(ts + (uint32_t)(c * 16), packed);
+                }
+            }
+            l += sum;
+            if (P_SMEM) fence_proxy_async_smem(); else tmem_st_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_pfull + 8 * t);
+        }
+        // epilogue: O / l -> global, one row per thread
+        if (ok && n > 0) {
+            ok = mbar_wait(bar_ofull + 8 * t, 0, ctx, 41 + t);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok && n > 0) {
+            tc_fence_after_sync();
+            const float inv = 1.0f / l;
+            OutT* dst = out + ((size_t)bh * prm.s_q + row) * HD;
+#pragma unroll 1
+            for (int c = 0; c < HD / 32; ++c) {
+                uint32_t o[32];
+                tmem_ld_32x32b_x32(to + (uint32_t)(c * 32), o);
+                tmem_ld_wait();
+                if (sizeof(OutT) == 4) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        reinterpret_cast<float4*>(dst + c * 32)[i] =
+                            make_float4(__uint_as_float(o[4 * i]) * inv, __uint_as_float(o[4 * i + 1]) * inv,
+                                        __uint_as_float(o[4 * i + 2]) * inv, __uint_as_float(o[4 * i + 3]) * inv);
+                } else {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv);
+                        pk[i] = *reinterpret_cast<uint32_t*>(&b);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        reinterpret_cast<uint4*>(dst + c * 32)[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+                }
+            }
+        }
+    }
+
+    // ------------------------------- teardown ---------------------------------------
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after_sync();
+        tmem_dealloc<1>(tmem_base, 512);
+    }
+}
+
+template <int HD, typename OutT, bool P_SMEM>
+int launch_fmha(const Record& r, cudaStream_t stream, void** p, char* err) {
+    using L = FmhaSmem<HD, P_SMEM>;
+    auto kernel = fmha_fwd_kernel<HD, OutT, P_SMEM>;
+    static std::atomic<uint64_t> attr_set{0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!(attr_set.load(std::memory_order_relaxed) & (1ull << (dev & 63)))) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
+        if (e != cudaSuccess) { set_err(err, "cudaFuncSetAttribute(smem=%d): %s", L::kTotal, cudaGetErrorString(e)); return PB200_ERR_LAUNCH; }
+        attr_set.fetch_or(1ull << (dev & 63), std::memory_order_relaxed);
+    }
+    const int64_t BH = r.dims[0], SQ = r.dims[1], SKV = r.dims[2];
+    const bool kt = (r.flags & PB200_F_K_TRANSPOSED) != 0;
+    CUtensorMap tq, tk, tv;
+    {
+        uint64_t dims[3] = {(uint64_t)HD, (uint64_t)SQ, (uint64_t)BH};
+        uint64_t str[2] = {(uint64_t)HD * 2, (uint64_t)SQ * HD * 2};
+        uint32_t box[3] = {64, kQTile, 1};
+        int rc = make_tensor_map(&tq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, p[0], dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, err);
+        if (rc) return rc;
+    }
+    if (!kt) {
+        uint64_t dims[3] = {(uint64_t)HD, (uint64_t)SKV, (uint64_t)BH};
+        uint64_t str[2] = {(uint64_t)HD * 2, (uint64_t)SKV * HD * 2};
+        uint32_t box[3] = {64, kKvTile, 1};
+        int rc = make_tensor_map(&tk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, p[1], dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, err);
+        if (rc) return rc;
+    } else {
+        uint64_t dims[3] = {(uint64_t)SKV, (uint64_t)HD, (uint64_t)BH};
+        uint64_t str[2] = {(uint64_t)SKV * 2, (uint64_t)SKV * HD * 2};
+        uint32_t box[3] = {64, (uint32_t)HD, 1};
+        int rc = make_tensor_map(&tk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, p[1], dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, err);
+        if (rc) return rc;
+    }
+    {
+        uint64_t dims[3] = {(uint64_t)HD, (uint64_t)SKV, (uint64_t)BH};
+        uint64_t str[2] = {(uint64_t)HD * 2, (uint64_t)SKV * HD * 2};
+        uint32_t box[3] = {64, kKvTile, 1};
+        int rc = make_tensor_map(&tv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, p[2], dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, err);
+        if (rc) return rc;
+    }
+    FmhaParams prm;
+    prm.bh = (int)BH; prm.s_q = (int)SQ; prm.s_kv = (int)SKV;
+    prm.causal = (r.flags & PB200_F_CAUSAL) ? 1 : 0;
+    prm.k_transposed = kt ? 1 : 0;
+    prm.scale_log2 = (float)(r.fparams[0] * 1.4426950408889634);
+    prm.causal_offset = (int)(SKV - SQ);
+    dim3 grid(r.geom.grid[0], r.geom.grid[1], 1);
+    kernel<<<grid, kFmhaThreads, L::kTotal, stream>>>(tq, tk, tv, (OutT*)p[3], prm, device_status_ptr());
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { set_err(err, "attention launch failed (HD=%d smem=%d): %s", HD, L::kTotal, cudaGetErrorString(e)); return PB200_ERR_LAUNCH; }
+    return PB200_OK;
+}
+
+}  // namespace
+
+// dims = {batch*heads, S_q, S_kv, head_dim}; fparams = {sm_scale} (0 -> 1/sqrt(head_dim))
+int plan_attention(Record& r, char* err) {
+    if (r.n_dims != 4) { set_err(err, "attention needs dims = {batch*heads, S_q, S_kv, head_dim}, got %d dims", r.n_dims); return PB200_ERR_BAD_SHAPE; }
+    const int64_t BH = r.dims[0], SQ = r.dims[1], SKV = r.dims[2], HD = r.dims[3];
+    if (BH < 1 || SQ < 1 || SKV < 1) { set_err(err, "batch*heads, S_q, S_kv must be positive"); return PB200_ERR_BAD_SHAPE; }
+    if (HD != 64 && HD != 128) { set_err(err, "head_dim=%lld must be 64 or 128", (long long)HD); return PB200_ERR_BAD_SHAPE; }
+    if (SQ % kQTile != 0) { set_err(err, "S_q=%lld must be divisible by %d", (long long)SQ, kQTile); return PB200_ERR_BAD_SHAPE; }
+    if (SKV % kKvTile != 0) { set_err(err, "S_kv=%lld must be divisible by %d", (long long)SKV, kKvTile); return PB200_ERR_BAD_SHAPE; }
+    if ((r.flags & PB200_F_CAUSAL) && SKV < SQ) { set_err(err, "causal attention needs S_kv >= S_q"); return PB200_ERR_BAD_SHAPE; }
+    if (BH > 65535) { set_err(err, "batch*heads=%lld exceeds 65535", (long long)BH); return PB200_ERR_BAD_SHAPE; }
+    if ((r.flags & kDebugPSmem) && HD != 64) { set_err(err, "the shared-memory P variant exists for head_dim 64 only"); return PB200_ERR_BAD_SHAPE; }
+    if (r.n_fparams < 1 || r.fparams[0] == 0.0) { r.fparams[0] = 1.0 / std::sqrt((double)HD); r.n_fparams = 1; }
+    pb200_geometry& g = r.geom;
+    g.grid[0] = (uint32_t)((SQ + 2 * kQTile - 1) / (2 * kQTile)); g.grid[1] = (uint32_t)BH; g.grid[2] = 1;
+    g.block[0] = kFmhaThreads; g.block[1] = g.block[2] = 1;
+    g.cluster[0] = g.cluster[1] = g.cluster[2] = 1;
+    g.smem_bytes = HD == 64 ? ((r.flags & kDebugPSmem) ? FmhaSmem<64, true>::kTotal : FmhaSmem<64, false>::kTotal)
+                            : FmhaSmem<128, false>::kTotal;
+    g.n_inputs = 3; g.n_outputs = 1;
+    return PB200_OK;
+}
+
+int launch_attention(const Record& r, cudaStream_t stream, void** p, char* err) {
+    const int64_t HD = r.dims[3];
+    const bool bf16_out = (r.flags & PB200_F_OUT_BF16) != 0;
+    const bool p_smem = (r.flags & kDebugPSmem) != 0;
+    if (HD == 64) {
+        if (p_smem) return bf16_out ? launch_fmha<64, __nv_bfloat16, true>(r, stream, p, err) : launch_fmha<64, float, true>(r, stream, p, err);
+        return bf16_out ? launch_fmha<64, __nv_bfloat16, false>(r, stream, p, err) : launch_fmha<64, float, false>(r, stream, p, err);
+    }
+    return bf16_out ? launch_fmha<128, __nv_bfloat16, false>(r, stream, p, err) : launch_fmha<128, float, false>(r, stream, p, err);
+}
+
 }  // namespace pb200

@@ -19,7 +19,6 @@ import argparse
 import json
 import os
 import statistics
-import subprocess
 import sys
 import threading
 import time
@@ -44,63 +43,67 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clock, power and throttle reasons through NVML (read-only queries) from a
+    thread while the timed region runs; about one sample per millisecond."""
 
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown"}
 
-    def __init__(self, gpu_index: int) -> None:
-        self.gpu_index = gpu_index
-        self.proc = None
-        self.lines: list[str] = []
+    def __init__(self, torch, device_index: int) -> None:
+        self.samples: list[tuple[float, int, float, int]] = []
+        self.stop_flag = threading.Event()
         self.thread = None
+        self.error = None
+        self.sm_max = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            try:
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:  # noqa: BLE001 - older bindings take str
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(uuid)
+            self.nvml = pynvml
+            self.sm_max = int(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        except Exception as exc:  # noqa: BLE001 - clocks are reported as unavailable
+            self.nvml = None
+            self.error = f"NVML unavailable: {exc}"[:120]
+
+    def _loop(self) -> None:
+        n = self.nvml
+        while not self.stop_flag.is_set():
+            try:
+                clk = int(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM))
+                pw = n.nvmlDeviceGetPowerUsage(self.handle) / 1000.0
+                rs = int(n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
+                self.samples.append((time.perf_counter(), clk, pw, rs))
+            except Exception as exc:  # noqa: BLE001
+                self.error = f"NVML query failed: {exc}"[:120]
+                return
+            time.sleep(0.0005)
 
     def start(self) -> None:
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
+        if self.nvml is None:
             return
-
-        def pump():
-            for line in self.proc.stdout:
-                self.lines.append(line.strip())
-
-        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread = threading.Thread(target=self._loop, daemon=True)
         self.thread.start()
 
-    def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, mx, power, reasons = [], [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 9:
-                continue
-            try:
-                sm.append(float(parts[1])); mx.append(float(parts[2])); power.append(float(parts[3]))
-            except ValueError:
-                continue
-            for name, val in zip(names, parts[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        # "under load" = samples in the upper half of the observed power range
-        lo, hi = min(power), max(power)
-        loaded = [c for c, p in zip(sm, power) if p >= lo + 0.5 * (hi - lo)] or sm
-        return {"sm_mhz": statistics.median(loaded), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
-                "samples": len(sm), "power_w_max": hi}
+    def stop(self, t_begin: float, t_end: float) -> dict:
+        """Summary of the samples taken between the two ``perf_counter`` instants."""
+        if self.nvml is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [self.error or "NVML unavailable"]}
+        self.stop_flag.set()
+        self.thread.join(timeout=2)
+        inside = [s for s in self.samples if t_begin <= s[0] <= t_end] or self.samples[-3:]
+        if not inside:
+            return {"sm_mhz": None, "sm_max_mhz": self.sm_max, "reasons": [self.error or "no samples"]}
+        bits = 0
+        for s in inside:
+            bits |= s[3]
+        reasons = sorted(name for bit, name in self.REASONS.items() if bits & bit)
+        return {"sm_mhz": statistics.median(s[1] for s in inside), "sm_max_mhz": self.sm_max, "reasons": reasons,
+                "samples": len(inside), "power_w_max": max(s[2] for s in inside)}
 
 
 def time_cuda(fn, steps: int, warmup: int, torch) -> float:
@@ -239,17 +242,19 @@ def run_ours(args) -> None:
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
+    sampler = ClockSampler(torch, local_rank) if rank == 0 else None
+    if sampler:
         sampler.start()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_begin = time.perf_counter()
     start.record()
     for _ in range(args.steps):
         step()
     stop.record()
     barrier()
+    t_end = time.perf_counter()
     ms_total = start.elapsed_time(stop)
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(t_begin, t_end) if sampler else None
     _native.device_status()
     if world > 1:
         t = torch.tensor([ms_total], device="cuda")
@@ -360,7 +365,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--variant", choices=["1sm", "2sm"], default="1sm")
+    ap.add_argument("--variant", choices=["1sm", "2sm"], default="2sm")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

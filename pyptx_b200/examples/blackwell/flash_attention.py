@@ -1,0 +1,66 @@
+"""Flash-attention forward for B200 (tcgen05), batched over batch x heads.
+
+``O = softmax(Q K^T * sm_scale [+ causal mask]) V`` with bf16 operands, fp32 scores and
+statistics.  The algorithm is the reference's
+(examples/hopper/experimental/flash_attention_hopper.py:44-465: online softmax over K/V
+tiles, P rounded to bf16 before the second product); that kernel is sm_90a-only, single
+head, non-causal and limited to head_dim <= 64, so this entry point adds the batch and head
+dimensions, head_dim 128 and the causal mask.  ``build_flash_attention_hopper`` in
+``pyptx_b200.examples.hopper.experimental.flash_attention_hopper`` keeps the reference's
+single-head call signature on top of the same kernel.
+"""
+from __future__ import annotations
+
+import math
+
+from ..._ids import F_CAUSAL, F_K_TRANSPOSED, F_OUT_BF16, K_FLASH_ATTN
+from ...kernel import NativeKernel
+from ...specs import Layout, Tile
+from ...types import PtxType, bf16, f32
+
+BLOCK_M = 128   # query rows per tile (two tiles per CTA)
+BLOCK_N = 128   # keys per K/V tile
+HEAD_DIMS = (64, 128)
+
+
+def _check(seq_q: int, seq_kv: int, head_dim: int, causal: bool) -> None:
+    assert head_dim in HEAD_DIMS, f"head_dim={head_dim} must be one of {HEAD_DIMS}"
+    assert seq_q >= BLOCK_M and seq_q % BLOCK_M == 0, f"M_q={seq_q} must be a positive multiple of {BLOCK_M}"
+    assert seq_kv >= BLOCK_N and seq_kv % BLOCK_N == 0, f"N_seq={seq_kv} must be a positive multiple of {BLOCK_N}"
+    assert not causal or seq_kv >= seq_q, "causal attention needs N_seq >= M_q"
+
+
+def build_flash_attention(batch: int, heads: int, seq_q: int, seq_kv: int | None = None,
+                          head_dim: int = 64, *, causal: bool = False, sm_scale: float | None = None,
+                          out_dtype: PtxType = bf16, arch: str = "sm_100a",
+                          _debug_flags: int = 0) -> NativeKernel:
+    """Kernel ``k(Q[B,H,Sq,d], K[B,H,Skv,d], V[B,H,Skv,d]) -> O[B,H,Sq,d]`` (bf16 in).
+
+    ``causal`` lets query ``i`` see keys ``j <= i + (Skv - Sq)``.  ``sm_scale`` defaults to
+    ``1/sqrt(head_dim)``.  ``out_dtype`` is bf16 (default) or f32.
+    """
+    assert arch.startswith("sm_100"), "Blackwell attention is only implemented for sm_100*"
+    seq_kv = seq_q if seq_kv is None else seq_kv
+    _check(seq_q, seq_kv, head_dim, causal)
+    assert batch >= 1 and heads >= 1 and batch * heads <= 65535, "batch*heads must be in [1, 65535]"
+    assert out_dtype in (f32, bf16), f"out_dtype must be f32 or bf16, got {out_dtype}"
+    scale = 1.0 / math.sqrt(head_dim) if sm_scale is None else float(sm_scale)
+    flags = (F_CAUSAL if causal else 0) | (F_OUT_BF16 if out_dtype == bf16 else 0) | _debug_flags
+    return NativeKernel(
+        "flash_attn_fwd", K_FLASH_ATTN, (batch * heads, seq_q, seq_kv, head_dim),
+        in_specs=(Tile(batch, heads, seq_q, head_dim, bf16, Layout.TMA_128B, tma_box=(BLOCK_M, 64)),
+                  Tile(batch, heads, seq_kv, head_dim, bf16, Layout.TMA_128B, tma_box=(BLOCK_N, 64)),
+                  Tile(batch, heads, seq_kv, head_dim, bf16, Layout.TMA_128B, tma_box=(BLOCK_N, 64))),
+        out_specs=(Tile(batch, heads, seq_q, head_dim, out_dtype, Layout.ROW),),
+        fparams=(scale,), flags=flags, arch=arch,
+        meta={"causal": causal, "sm_scale": scale, "block_m": BLOCK_M, "block_n": BLOCK_N},
+    )
+
+
+def attention_flops(batch: int, heads: int, seq_q: int, seq_kv: int, head_dim: int, causal: bool = False) -> float:
+    """4*B*H*Sq*Skv*d for the two products; half of it under the causal mask."""
+    f = 4.0 * batch * heads * seq_q * seq_kv * head_dim
+    return f / 2 if causal else f
+
+
+__all__ = ["build_flash_attention", "attention_flops", "F_K_TRANSPOSED"]

@@ -199,6 +199,73 @@ def row_kernel_table(torch, peaks, steps: int, warmup: int) -> dict:
     return table
 
 
+def run_case(args) -> None:
+    """``--case NAME``: launch one kernel of the library ``warmup + steps`` times on its benchmark
+    configuration and print its device time.  This is the small, single-kernel command that the
+    ncu summaries under profiles/ were captured from."""
+    import torch
+    from oracle import inputs
+    from pyptx_b200 import _native
+    from pyptx_b200.examples.blackwell.flash_attention import attention_flops, build_flash_attention
+    from pyptx_b200.examples.blackwell.gemm_highperf_blackwell import build_gemm, build_gemm_2sm
+    from pyptx_b200.examples.blackwell.grouped_gemm import build_grouped_gemm
+    from pyptx_b200.examples.blackwell.layer_norm import build_layer_norm, layer_norm_bytes
+    from pyptx_b200.examples.blackwell.rms_norm import build_rms_norm, rms_norm_bytes
+    from pyptx_b200.examples.blackwell.softmax import build_softmax, softmax_bytes
+    from pyptx_b200.examples.blackwell.swiglu import build_fused_silu_mul, swiglu_bytes
+
+    torch.cuda.set_device(0)
+    name, size = args.case, args.size
+    B, N = 2048, 8192
+    work, unit = 0.0, "GB/s"
+    if name in ("gemm_1sm", "gemm_2sm"):
+        a, bt = inputs.gemm_inputs(size, size, size)
+        k = (build_gemm if name == "gemm_1sm" else build_gemm_2sm)(size, size, size)
+        ops = (a.cuda(), bt.cuda()); work, unit = 2.0 * size ** 3, "TFLOP/s"
+    elif name == "grouped":
+        a, bt = inputs.grouped_gemm_inputs(8, 2048, 256, 2048)
+        k = build_grouped_gemm(8, 2048, 256, 2048)
+        ops = (a.cuda(), bt.cuda()); work, unit = 2.0 * 8 * 2048 * 256 * 2048, "TFLOP/s"
+    elif name.startswith("attention"):
+        d = 64 if "64" in name else 128
+        causal = "causal" in name
+        q, kk, v = inputs.attention_inputs(64, size, size, d)
+        k = build_flash_attention(4, 16, size, size, d, causal=causal)
+        ops = tuple(t.view(4, 16, size, d).cuda() for t in (q, kk, v))
+        work, unit = attention_flops(4, 16, size, size, d, causal), "TFLOP/s"
+    elif name == "rms_norm":
+        k, ops, work = build_rms_norm(B, N), tuple(t.cuda() for t in inputs.rms_norm_inputs(B, N)), rms_norm_bytes(B, N)
+    elif name == "layer_norm":
+        k, ops, work = build_layer_norm(B, N), tuple(t.cuda() for t in inputs.layer_norm_inputs(B, N)), layer_norm_bytes(B, N)
+    elif name == "swiglu":
+        k, ops, work = build_fused_silu_mul(B, N), tuple(t.cuda() for t in inputs.swiglu_inputs(B, N)), swiglu_bytes(B, N)
+    elif name == "softmax":
+        k, ops, work = build_softmax(B, N), tuple(t.cuda() for t in inputs.softmax_inputs(B, N)), softmax_bytes(B, N)
+    else:
+        raise SystemExit(f"unknown --case {name}")
+    flush = torch.empty(1 << 30, dtype=torch.uint8, device="cuda")   # 8x L2; also long enough to hide the host-side launch
+
+    def fn():
+        flush.zero_()
+        k(*ops)
+
+    for _ in range(args.warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(args.steps):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); k(*ops); e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    _native.device_status()
+    ms = statistics.median(times)
+    rate = work / (ms * 1e-3) / (1e12 if unit == "TFLOP/s" else 1e9)
+    print(json.dumps({"case": name, "size": size, "ms": ms, "rate": rate, "unit": unit, "steps": args.steps,
+                      "l2": "1 GiB buffer written between launches"}))
+
+
 def run_ours(args) -> None:
     import torch
     import torch.distributed as dist
@@ -297,7 +364,11 @@ def run_ours(args) -> None:
     d2h = d_pin.numel() * 4
 
     extras, cpu_baseline = None, None
-    if rank == 0 and world == 1:
+    if rank == 0 and world == 1 and args.no_extras:
+        tflops, spent, _ = cpu_gemm_tflops(torch, a_host, bt_host, CPU_SAMPLE_ROWS, repeats=1)
+        cpu_baseline = {"value": tflops, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                        "host_cpus": os.cpu_count(), "sample": f"{CPU_SAMPLE_ROWS} of {S} rows of A, one pass"}
+    elif rank == 0 and world == 1:
         # ---- context numbers: other variant, cuBLAS, smaller sizes, grouped, row kernels ----------------
         extras = {}
         other = "2sm" if args.variant == "1sm" else "1sm"
@@ -321,6 +392,22 @@ def run_ours(args) -> None:
                 extras[f"grouped_G{G}_tflops"] = 2.0 * G * 2048 * 256 * 2048 / (ms * 1e-3) / 1e12
         except Exception as exc:  # noqa: BLE001 - context only
             extras["grouped_error"] = str(exc)[:200]
+        try:
+            from pyptx_b200.examples.blackwell.flash_attention import attention_flops, build_flash_attention
+            import torch.nn.functional as F
+            for d in (64, 128):
+                q, kk, v = (t.view(4, 16, 4096, d).cuda() for t in inputs.attention_inputs(64, 4096, 4096, d))
+                for causal in (False, True):
+                    k = build_flash_attention(4, 16, 4096, 4096, d, causal=causal)
+                    fl = attention_flops(4, 16, 4096, 4096, d, causal)
+                    tag = f"attention_d{d}_{'causal' if causal else 'full'}"
+                    ms = time_cuda(lambda: k(q, kk, v), 20, 5, torch)
+                    extras[tag + "_tflops"] = fl / (ms * 1e-3) / 1e12
+                    ms = time_cuda(lambda: F.scaled_dot_product_attention(q, kk, v, is_causal=causal), 20, 5, torch)
+                    extras[tag + "_torch_sdpa_tflops"] = fl / (ms * 1e-3) / 1e12
+                del q, kk, v
+        except Exception as exc:  # noqa: BLE001 - context only
+            extras["attention_error"] = str(exc)[:200]
         extras["row_kernels_2048x8192_f32"] = row_kernel_table(torch, peaks, 200, 20)
         _native.device_status()
         # ---- CPU baseline: the oracle formula on a bounded row block -----------------------------
@@ -348,7 +435,10 @@ def run_ours(args) -> None:
                     "ms_per_step": e2e_ms, "steps": e2e_steps},
             "gpu_launches": args.steps,
             "roofline": {"bound": "tensor", "achieved": kernel_tflops, "peak": peak, "unit": "TFLOP/s",
-                         "frac": kernel_tflops / peak, "traffic": None, "peak_kind": f"{peak_kind} burst cuBLAS bf16",
+                         "frac": kernel_tflops / peak,
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this size
+                         # (ncu capture summarised in profiles/gemm_2sm_8192.md)
+                         "traffic": 1508349440 if args.variant == "2sm" else None, "peak_kind": f"{peak_kind} burst cuBLAS bf16",
                          "frac_of_nominal_2250": kernel_tflops / 2250.0},
             "cpu_baseline": cpu_baseline,
         }
@@ -366,8 +456,15 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--variant", choices=["1sm", "2sm"], default="2sm")
+    ap.add_argument("--no-extras", action="store_true", help="skip the context table (other kernels, cuBLAS)")
+    ap.add_argument("--case", default=None,
+                    help="run ONE kernel only: gemm_1sm gemm_2sm grouped attention_d64 attention_d128[_causal] "
+                         "rms_norm layer_norm swiglu softmax")
+    ap.add_argument("--size", type=int, default=8192, help="M=N=K (gemm cases) or sequence length (attention cases)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.case:
+        run_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -124,6 +124,75 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
     return LIB_PATH
 
 
+TORCH_EXT_NAME = "_pb200_torch_ext"
+TORCH_EXT_PATH = os.path.join(LIB_DIR, TORCH_EXT_NAME + ".so")
+TORCH_EXT_SRC = os.path.join(CSRC_DIR, "torch_ext.cpp")
+
+
+def build_torch_ext(force: bool = False) -> str:
+    """Compile ``csrc/torch_ext.cpp`` (pybind11 fast path) in-tree with g++ against the installed
+    torch; counterpart of the reference's JIT build of its extension
+    (pyptx/torch_support.py:128-149), done ahead of time so that it travels with the tree."""
+    if (not force and os.path.isfile(TORCH_EXT_PATH)
+            and os.path.getmtime(TORCH_EXT_PATH) >= os.path.getmtime(TORCH_EXT_SRC)):
+        return TORCH_EXT_PATH
+    import sysconfig
+    import warnings
+
+    import torch
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        from torch.utils import cpp_extension as ce
+        inc, libdirs = ce.include_paths(), ce.library_paths()
+    os.makedirs(LIB_DIR, exist_ok=True)
+    tmp = TORCH_EXT_PATH + ".tmp"
+    cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", TORCH_EXT_SRC, "-o", tmp,
+           f"-DTORCH_EXTENSION_NAME={TORCH_EXT_NAME}", "-DTORCH_API_INCLUDE_EXTENSION_H",
+           f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
+           "-I" + sysconfig.get_paths()["include"]]
+    cmd += ["-I" + i for i in inc if os.path.isdir(i) and "cuda" not in i]
+    libdirs = [d for d in libdirs if os.path.isdir(d) and "cuda" not in d]
+    cmd += ["-L" + d for d in libdirs]
+    cmd += ["-lc10", "-ltorch", "-ltorch_cpu", "-ltorch_python", "-ldl"]
+    cmd += ["-Wl,-rpath," + d for d in libdirs]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"pyptx_b200: building the torch extension failed:\n{r.stderr[-2000:]}")
+    os.replace(tmp, TORCH_EXT_PATH)
+    return TORCH_EXT_PATH
+
+
+_TORCH_EXT = None
+_TORCH_EXT_TRIED = False
+
+
+def load_torch_ext():
+    """The pybind11 extension module with the C-ABI library attached, or ``None`` when it has
+    not been built (the ctypes path is then used; both end in the same ``pb200_launch_raw``).
+    ``PYPTX_B200_NO_TORCH_EXT=1`` forces the ctypes path."""
+    global _TORCH_EXT, _TORCH_EXT_TRIED
+    if _TORCH_EXT_TRIED:
+        return _TORCH_EXT
+    with _LOCK:
+        if _TORCH_EXT_TRIED:
+            return _TORCH_EXT
+        ext = None
+        if os.environ.get("PYPTX_B200_NO_TORCH_EXT") != "1" and os.path.isfile(TORCH_EXT_PATH):
+            import importlib.util
+
+            import torch  # noqa: F401 - libtorch must be loaded before the extension
+            try:
+                spec = importlib.util.spec_from_file_location(TORCH_EXT_NAME, TORCH_EXT_PATH)
+                ext = importlib.util.module_from_spec(spec)
+                spec.loader.exec_module(ext)
+                ext.load_shim(LIB_PATH)
+            except Exception:  # noqa: BLE001 - an unusable extension falls back to ctypes, same C ABI
+                ext = None
+        _TORCH_EXT = ext
+        _TORCH_EXT_TRIED = True
+    return _TORCH_EXT
+
+
 _LIB = None
 _LOCK = threading.Lock()
 

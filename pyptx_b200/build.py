@@ -10,3 +10,4 @@ if __name__ == "__main__":
     ap.add_argument("--ptxas-info", action="store_true", help="print registers / spills / shared memory per kernel")
     a = ap.parse_args()
     print(_native.build(force=a.force, verbose=a.verbose, ptxas_info=a.ptxas_info))
+    print(_native.build_torch_ext(force=a.force))

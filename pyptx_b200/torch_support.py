@@ -101,6 +101,13 @@ class _Launcher:
         if not any(s.symbolic_dims for s in kernel.out_specs):
             self.static_out_shapes = kernel.out_shapes({})
         self.in_shapes = [s.shape if not s.symbolic_dims else None for s in kernel.in_specs]
+        self.ext = _native.load_torch_ext()
+        # c10::ScalarType integers, as the reference passes them (pyptx/torch_support.py:209-214)
+        torch = _torch()
+        codes = {torch.uint8: 0, torch.int8: 1, torch.int16: 2, torch.int32: 3, torch.int64: 4,
+                 torch.float16: 5, torch.float32: 6, torch.float64: 7, torch.bool: 11, torch.bfloat16: 15}
+        self.out_dtype_codes = [codes[d] for d in self.out_dtypes]
+        self.handle_int = int(kernel.handle)
 
 
 def _check_inputs(kernel, launcher: _Launcher, inputs) -> dict[str, int]:
@@ -141,6 +148,14 @@ def call_kernel_via_torch(kernel, inputs: Sequence[Any]):
     env = _check_inputs(kernel, launcher, inputs)
     dev = inputs[0].device
     shapes = launcher.static_out_shapes or kernel.out_shapes(env)
+    if launcher.ext is not None:
+        # pybind11 fast path: output allocation and the C-ABI call happen in C++.
+        if torch.cuda.current_device() != dev.index:
+            with torch.cuda.device(dev):
+                return launcher.ext.launch_kernel(launcher.handle_int, torch.cuda.current_stream(dev).cuda_stream,
+                                                  list(inputs), [list(s) for s in shapes], launcher.out_dtype_codes)
+        return launcher.ext.launch_kernel(launcher.handle_int, torch.cuda.current_stream(dev).cuda_stream,
+                                          list(inputs), [list(s) for s in shapes], launcher.out_dtype_codes)
     outs = [torch.empty(shp, dtype=dt, device=dev) for shp, dt in zip(shapes, launcher.out_dtypes)]
     ptrs = launcher.ptrs
     for i, t in enumerate(inputs):

@@ -1,0 +1,203 @@
+"""The PyTorch launch path on a GPU: eager (pybind11 extension and ctypes), torch.compile through
+the registered custom op, CUDA-graph capture and replay, the autograd wrapper, stream ordering
+and call-time validation.  Mirrors the reference's tests/test_torch_dispatch.py:38-204."""
+import ctypes
+
+import pytest
+import torch
+
+from oracle import formulas, inputs
+from pyptx_b200 import _ids, _native, differentiable_kernel, torch_support
+from pyptx_b200.examples.blackwell.gemm_highperf_blackwell import build_gemm
+from pyptx_b200.examples.blackwell.layer_norm import build_layer_norm
+from pyptx_b200.examples.blackwell.rms_norm import build_rms_norm
+from pyptx_b200.examples.blackwell.softmax import build_softmax
+from pyptx_b200.examples.blackwell.swiglu import build_fused_silu_mul
+from tests.gpu_util import check_f32
+
+pytestmark = pytest.mark.gpu
+
+
+def test_native_library_is_the_loaded_path():
+    lib = _native.load()
+    assert lib.pb200_arch() == b"sm_100a"
+    assert _native.load_torch_ext() is not None, "the in-tree pybind11 extension should be built and loadable"
+
+
+def test_eager_ext_and_ctypes_paths_agree():
+    x, w = inputs.rms_norm_inputs(16, 512)
+    xc, wc = x.cuda(), w.cuda()
+    k = build_rms_norm(16, 512)
+    y_ext = k(xc, wc)
+    launcher = k._launcher
+    assert launcher.ext is not None
+    launcher.ext = None               # force the ctypes path on the same kernel object
+    try:
+        y_ct = k(xc, wc)
+    finally:
+        launcher.ext = _native.load_torch_ext()
+    assert torch.equal(y_ext, y_ct)
+    check_f32(y_ext.cpu(), formulas.rms_norm_ref(x, w))
+
+
+def test_raw_c_abi_call():
+    """pb200_launch_raw with raw pointers and the stream as an integer, as a non-Python host would call it."""
+    lib = _native.load()
+    x, w = inputs.rms_norm_inputs(8, 256)
+    xc, wc = x.cuda(), w.cuda()
+    y = torch.empty_like(xc)
+    h = _native.create_handle(_ids.K_RMS_NORM, (8, 256), (1e-6,))
+    ptrs = (ctypes.c_void_p * 3)(xc.data_ptr(), wc.data_ptr(), y.data_ptr())
+    err = ctypes.create_string_buffer(_native.ERR_LEN)
+    rc = lib.pb200_launch_raw(h, torch.cuda.current_stream().cuda_stream, ptrs, 3, err)
+    assert rc == 0, err.value
+    torch.cuda.synchronize()
+    check_f32(y.cpu(), formulas.rms_norm_ref(x, w))
+    assert lib.pb200_device_status(err) == 0
+    lib.pb200_destroy(h)
+
+
+def test_torch_compile_through_custom_op():
+    x, w = inputs.rms_norm_inputs(16, 512)
+    k = build_rms_norm(16, 512)
+
+    @torch.compile(fullgraph=True)
+    def f(a, b):
+        return k(a * 2.0, b) + 1.0
+
+    out = f(x.cuda(), w.cuda())
+    ref = formulas.rms_norm_ref(x * 2.0, w) + 1.0
+    check_f32(out.cpu(), ref)
+    assert k.handle in torch_support._REGISTERED_OPS
+
+
+def test_custom_op_fake_shapes():
+    k = build_gemm(256, 256, 128)
+    op = torch_support.get_or_register_torch_op(k)
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    with FakeTensorMode():
+        a = torch.empty(256, 128, dtype=torch.bfloat16, device="cuda")
+        b = torch.empty(256, 128, dtype=torch.bfloat16, device="cuda")
+        (d,) = op([a, b])
+        assert d.shape == (256, 256) and d.dtype == torch.float32 and d.device.type == "cuda"
+
+
+def test_compile_swiglu_layernorm_softmax():
+    g, u = inputs.swiglu_inputs(32, 1024)
+    x, w, b = inputs.layer_norm_inputs(32, 1024)
+    ks, kl, km = build_fused_silu_mul(32, 1024), build_layer_norm(32, 1024), build_softmax(32, 1024)
+
+    @torch.compile
+    def f(g, u, x, w, b):
+        return km(kl(ks(g, u) + x, w, b))
+
+    out = f(*(t.cuda() for t in (g, u, x, w, b))).cpu()
+    ref = formulas.softmax_ref(formulas.layer_norm_ref(formulas.swiglu_ref(g, u) + x, w, b))
+    check_f32(out, ref, tol=2e-5)
+
+
+def test_cuda_graph_capture_and_replay():
+    x, w = inputs.rms_norm_inputs(64, 2048)
+    a, bt = inputs.gemm_inputs(256, 256, 256)
+    k_rms, k_gemm = build_rms_norm(64, 2048), build_gemm(256, 256, 256)
+    xs, ws, as_, bts = x.cuda(), w.cuda(), a.cuda(), bt.cuda()
+    k_rms(xs, ws); k_gemm(as_, bts)            # warm-up outside capture (first-call set-up)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        y = k_rms(xs, ws)
+        d = k_gemm(as_, bts)
+    for scale in (1.0, 3.0):
+        xs.copy_((x * scale).cuda())
+        as_.copy_((a.float() * scale).to(torch.bfloat16).cuda())
+        graph.replay()
+        torch.cuda.synchronize()
+        check_f32(y.cpu(), formulas.rms_norm_ref(x * scale, w))
+        ref = formulas.gemm_ref((a.float() * scale).to(torch.bfloat16), bt)
+        assert formulas.rel_fro(d.cpu(), ref) < 1e-4
+    _native.device_status()
+
+
+def test_stream_ordering():
+    """The launch is enqueued on the caller's current stream: work queued before it on that
+    stream is visible, and no other stream is touched."""
+    k = build_rms_norm(64, 4096)
+    x, w = inputs.rms_norm_inputs(64, 4096)
+    s = torch.cuda.Stream()
+    wc = w.cuda()
+    torch.cuda.synchronize()
+    with torch.cuda.stream(s):
+        xs = torch.empty(64, 4096, device="cuda")
+        for _ in range(20):
+            xs.zero_()
+        xs.copy_(x.cuda(), non_blocking=True)
+        y = k(xs, wc)
+    s.synchronize()
+    check_f32(y.cpu(), formulas.rms_norm_ref(x, w))
+
+
+def test_differentiable_kernel_wrapper():
+    """Forward kernel + a backward callable through torch.autograd (the backward here is the
+    analytic SwiGLU gradient in torch; backward kernels are outside this library's scope)."""
+    M, F = 16, 256
+    fwd = build_fused_silu_mul(M, F)
+
+    def bwd(g, u, grad_out):
+        sig = torch.sigmoid(g)
+        return grad_out * u * (sig * (1 + g * (1 - sig))), grad_out * g * sig
+
+    op = differentiable_kernel(fwd, bwd)
+    g, u = (t.cuda().requires_grad_() for t in inputs.swiglu_inputs(M, F))
+    out = op(g, u)
+    out.sum().backward()
+    g2, u2 = (t.detach().clone().requires_grad_() for t in (g, u))
+    (torch.nn.functional.silu(g2) * u2).sum().backward()
+    torch.testing.assert_close(g.grad, g2.grad, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(u.grad, u2.grad, rtol=1e-4, atol=1e-5)
+    assert op.forward_kernel is fwd
+
+
+def test_call_time_validation():
+    k = build_rms_norm(16, 512)
+    x, w = (t.cuda() for t in inputs.rms_norm_inputs(16, 512))
+    with pytest.raises(TypeError, match="expected 2 input arrays, got 1"):
+        k(x)
+    with pytest.raises(ValueError, match="dim mismatch"):
+        k(x[:8].contiguous(), w)
+    with pytest.raises(TypeError, match="dtype"):
+        k(x.double(), w)
+    with pytest.raises(ValueError, match="not contiguous"):
+        k(x.t().contiguous().t(), w)
+    with pytest.raises(ValueError, match="CUDA tensors"):
+        k(x.cpu(), w.cpu())
+    with pytest.raises(TypeError):
+        k([1, 2], w)
+    kg = build_gemm(128, 256, 64)
+    with pytest.raises(TypeError, match="dtype"):
+        kg(torch.zeros(128, 64, device="cuda"), torch.zeros(256, 64, device="cuda"))
+
+
+def test_misaligned_view_is_rejected_by_the_c_abi():
+    k = build_rms_norm(4, 64)
+    base = torch.zeros(4 * 64 + 1, device="cuda")
+    x = base[1:].view(4, 64)                      # 4-byte offset: not 16-byte aligned
+    with pytest.raises(RuntimeError, match="code -10"):
+        k(x, torch.ones(64, device="cuda"))
+
+
+def test_dispatch_overhead_is_reported(capsys):
+    """Host-side cost of one eager call (not asserted tightly; the figure is printed for the log)."""
+    import time
+    k = build_rms_norm(4, 64)
+    x, w = torch.zeros(4, 64, device="cuda"), torch.ones(64, device="cuda")
+    for _ in range(200):
+        k(x, w)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    n = 2000
+    for _ in range(n):
+        k(x, w)
+    host_us = (time.perf_counter() - t0) / n * 1e6
+    torch.cuda.synchronize()
+    print(f"eager dispatch: {host_us:.1f} us per call (ext={'yes' if k._launcher.ext else 'no'})")
+    assert host_us < 200

@@ -18,7 +18,8 @@ _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC_DIR = os.path.join(_PKG_DIR, "csrc")
 INCLUDE_DIR = os.path.join(os.path.dirname(_PKG_DIR), "include")
 LIB_DIR = os.path.join(_PKG_DIR, "_lib")
-LIB_PATH = os.path.join(LIB_DIR, "libpyptx_b200.so")
+# PYPTX_B200_LIB points at a library built elsewhere (e.g. an installed copy); default: in-tree.
+LIB_PATH = os.environ.get("PYPTX_B200_LIB") or os.path.join(LIB_DIR, "libpyptx_b200.so")
 
 ERR_LEN = 128
 

@@ -9,6 +9,7 @@ handle of the C-ABI library instead of a traced-and-JIT-compiled PTX module.
 """
 from __future__ import annotations
 
+import sys
 from typing import Any, Sequence
 
 from . import _native
@@ -45,6 +46,12 @@ class NativeKernel:
                 f"{name}: spec count ({len(self._in_specs)} in, {len(self._out_specs)} out) disagrees "
                 f"with the native kernel ({g.n_inputs} in, {g.n_outputs} out)")
         self._launcher = None  # built on first call (imports torch)
+        # The torch.compile route needs its custom op to exist before Dynamo starts tracing a
+        # call, so it is registered here whenever torch is already imported.
+        self._op = None
+        if "torch" in sys.modules:
+            from . import torch_support
+            self._op = torch_support.get_or_register_torch_op(self)
 
     # -- attribute surface of the reference's Kernel -------------------------
     @property
@@ -107,6 +114,4 @@ class NativeKernel:
         if len(inputs) != len(self._in_specs):
             raise TypeError(
                 f"Kernel {self._name} expected {len(self._in_specs)} input arrays, got {len(inputs)}")
-        if not torch_support.any_torch_tensors(inputs):
-            raise TypeError(f"Kernel {self._name} takes torch.Tensor inputs (the JAX path is not built)")
         return torch_support.call_kernel(self, inputs)

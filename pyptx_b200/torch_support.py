@@ -142,6 +142,8 @@ def call_kernel_via_torch(kernel, inputs: Sequence[Any]):
     torch = _torch()
     if not inputs:
         raise ValueError("pyptx_b200: a kernel call requires at least one input")
+    if not isinstance(inputs[0], torch.Tensor):
+        raise TypeError(f"Kernel {kernel.__name__} takes torch.Tensor inputs (the JAX path is not built)")
     launcher = kernel._launcher
     if launcher is None:
         launcher = kernel._launcher = _Launcher(kernel)
@@ -202,6 +204,7 @@ def get_or_register_torch_op(kernel):
                 for spec in kernel.out_specs]
 
     _REGISTERED_OPS[kernel.handle] = native_op
+    kernel._op = native_op
     return native_op
 
 
@@ -210,7 +213,12 @@ def call_kernel(kernel, inputs: Sequence[Any]):
     is tracing, the direct launch otherwise; one output -> tensor, several -> tuple."""
     torch = _torch()
     if torch.compiler.is_compiling():
-        outs = get_or_register_torch_op(kernel)(list(inputs))
+        op = kernel._op
+        if op is None:
+            raise RuntimeError(
+                f"Kernel {kernel.__name__} was built before torch was imported; call "
+                "pyptx_b200.torch_support.get_or_register_torch_op(kernel) once before torch.compile traces it")
+        outs = op(list(inputs))
     else:
         outs = call_kernel_via_torch(kernel, inputs)
     return outs[0] if len(outs) == 1 else tuple(outs)

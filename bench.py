@@ -32,6 +32,13 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 CPU_SAMPLE_ROWS = 512          # rows of A per CPU step: 2*512*8192*8192 = 68.7 GFLOP
 
 
+def host_cores() -> int:
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
@@ -120,6 +127,48 @@ def time_cuda(fn, steps: int, warmup: int, torch) -> float:
     return start.elapsed_time(stop) / steps
 
 
+def time_graph(fn, iters: int, torch, repeats: int = 3) -> float:
+    """Milliseconds per call of ``fn`` with ``iters`` calls captured in one CUDA graph and replayed:
+    device time without per-launch host dispatch, which matters for kernels of 20-30 us."""
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        fn()
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(iters):
+                fn()
+    graph.replay()
+    torch.cuda.synchronize()
+    best = float("inf")
+    for _ in range(repeats):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1) / iters)
+    return best
+
+
+def pyptx_reference_kernels() -> dict:
+    """The reference's own sm_100a kernels on this GPU (baseline/run_pyptx.py), when staged."""
+    script = os.path.join(ROOT, "baseline", "run_pyptx.py")
+    if not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "pyptx")):
+        return {"unavailable": "baseline/_ref not staged"}
+    import subprocess
+    try:
+        r = subprocess.run([sys.executable, script], capture_output=True, text=True, timeout=420)
+        line = r.stdout.strip().splitlines()[-1] if r.stdout.strip() else ""
+        return json.loads(line) if line.startswith("{") else {"error": (r.stderr or "no output")[-300:]}
+    except Exception as exc:  # noqa: BLE001 - context only
+        return {"error": str(exc)[:300]}
+
+
 def cpu_gemm_tflops(torch, a_bf16, bt_bf16, rows: int, repeats: int, warmup: int = 1):
     """The oracle's GEMM formula on ``rows`` rows of A with every host thread torch uses."""
     from oracle import formulas
@@ -143,6 +192,8 @@ def run_reference(args) -> None:
     import torch
     from oracle import inputs, formulas
     torch.manual_seed(0)
+    # torch.distributed.run exports OMP_NUM_THREADS=1; the CPU arm is meant to use every host core.
+    torch.set_num_threads(host_cores())
     threads = torch.get_num_threads()
     a, bt = inputs.gemm_inputs(CPU_SAMPLE_ROWS, S, S)
     for _ in range(args.warmup):
@@ -192,10 +243,13 @@ def row_kernel_table(torch, peaks, steps: int, warmup: int) -> dict:
             call(k, counter[0] % SETS)
             counter[0] += 1
 
-        ms = time_cuda(fn, steps, warmup, torch)
+        ms_eager = time_cuda(fn, steps, warmup, torch)
+        counter[0] = 0
+        ms = time_graph(fn, 24, torch)       # 24 launches = 4 passes over the 6 buffer sets
         gbs = nbytes / (ms * 1e-3) / 1e9
         table[name] = {"ms": ms, "GB/s": gbs, "bytes": nbytes, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
-                       "frac_of_8TBps": gbs / 8000.0}
+                       "frac_of_8TBps": gbs / 8000.0, "timing": "cuda-graph replay, 6 rotating buffer sets",
+                       "ms_eager_loop": ms_eager}
     return table
 
 
@@ -365,6 +419,7 @@ def run_ours(args) -> None:
 
     extras, cpu_baseline = None, None
     if rank == 0 and world == 1 and args.no_extras:
+        torch.set_num_threads(host_cores())
         tflops, spent, _ = cpu_gemm_tflops(torch, a_host, bt_host, CPU_SAMPLE_ROWS, repeats=1)
         cpu_baseline = {"value": tflops, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
                         "host_cpus": os.cpu_count(), "sample": f"{CPU_SAMPLE_ROWS} of {S} rows of A, one pass"}
@@ -388,7 +443,7 @@ def run_ours(args) -> None:
                 ga, gb = inputs.grouped_gemm_inputs(G, 2048, 256, 2048)
                 ga, gb = ga.cuda(), gb.cuda()
                 k = build_grouped_gemm(G, 2048, 256, 2048)
-                ms = time_cuda(lambda: k(ga, gb), 50, 10, torch)
+                ms = time_graph(lambda: k(ga, gb), 20, torch)
                 extras[f"grouped_G{G}_tflops"] = 2.0 * G * 2048 * 256 * 2048 / (ms * 1e-3) / 1e12
         except Exception as exc:  # noqa: BLE001 - context only
             extras["grouped_error"] = str(exc)[:200]
@@ -411,6 +466,7 @@ def run_ours(args) -> None:
         extras["row_kernels_2048x8192_f32"] = row_kernel_table(torch, peaks, 200, 20)
         _native.device_status()
         # ---- CPU baseline: the oracle formula on a bounded row block -----------------------------
+        torch.set_num_threads(host_cores())
         tflops, spent, _ = cpu_gemm_tflops(torch, a_host, bt_host, CPU_SAMPLE_ROWS, repeats=3)
         cpu_baseline = {
             "value": tflops, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
@@ -444,6 +500,12 @@ def run_ours(args) -> None:
         }
         if extras is not None:
             line["kernels"] = extras
+            if not args.no_pyptx:
+                # Last, after every number of this library is in hand: the reference's own sm_100a
+                # kernels in child processes (their device waits are unbounded, hence the time limits).
+                del a, bt
+                torch.cuda.empty_cache()
+                extras["pyptx_reference_kernels"] = pyptx_reference_kernels()
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -456,6 +518,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--variant", choices=["1sm", "2sm"], default="2sm")
+    ap.add_argument("--no-pyptx", action="store_true",
+                    help="do not run the reference's own sm_100a kernels (baseline/_ref) for the context table")
     ap.add_argument("--no-extras", action="store_true", help="skip the context table (other kernels, cuBLAS)")
     ap.add_argument("--case", default=None,
                     help="run ONE kernel only: gemm_1sm gemm_2sm grouped attention_d64 attention_d128[_causal] "

@@ -239,8 +239,13 @@ def row_kernel_table(torch, peaks, steps: int, warmup: int) -> dict:
     for name, (k, call, nbytes) in cases.items():
         counter = [0]
 
+        # Outputs are kept in rotating slots as well: an output that is freed at once would be
+        # handed the same 64 MiB block every launch and its writes would stay in L2.
+        outs = [None] * SETS
+
         def fn():
-            call(k, counter[0] % SETS)
+            i = counter[0] % SETS
+            outs[i] = call(k, i)
             counter[0] += 1
 
         ms_eager = time_cuda(fn, steps, warmup, torch)

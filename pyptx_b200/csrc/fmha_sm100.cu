@@ -12,6 +12,8 @@
 //   warp 1      MMA issuer (single thread): S_t = Q_t K^T into TMEM, O_t += P_t V
 //   warps 4-7   softmax for tile 0 (one query row per thread, TMEM lane = row)
 //   warps 8-11  softmax for tile 1
+// The first warpgroup gives registers back (setmaxnreg 64) so that the softmax warpgroups can
+// hold a whole 128-element score row per thread (setmaxnreg 208).
 // TMEM (512 columns): S0 | S1 | O0 | O1, 128 columns each.  P overwrites the first 64
 // columns of its S in place (two bf16 per column) and is consumed by the MMA directly
 // from TMEM, so P never touches shared memory.  A template switch keeps P in swizzled
@@ -37,7 +39,7 @@ using namespace ptx;
 
 constexpr int kQTile = 128;       // query rows per tile (TMEM lanes)
 constexpr int kKvTile = 128;      // keys per K/V tile
-constexpr int kFmhaThreads = 384; // 12 warps
+constexpr int kFmhaThreads = 384; // 3 warpgroups: {TMA, MMA, 2 idle}, softmax tile 0, softmax tile 1
 constexpr uint32_t kDebugPSmem = 1u << 17;   // create flag: keep P in shared memory (head_dim 64)
 constexpr float kRescaleThreshold = 8.0f;    // log2 units
 
@@ -189,34 +191,38 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         // ------------------------------- MMA issuer ---------------------------------
         if (lane == 0) {
             bool ok = mbar_wait(bar_q, 0, ctx, 21);
+            // The issuing thread is the serial resource of this kernel: a 128x128x16 MMA retires
+            // every 64 clocks, so descriptors are built once here and each MMA costs two 64-bit
+            // adds.  Offsets are in descriptor units (16 bytes).
+            const bool kt = prm.k_transposed != 0;
+            const uint32_t idesc_s = kt ? kIdescS_T : kIdescS;
+            const uint64_t q_desc[2] = {make_desc_kmajor_sw128(s_q), make_desc_kmajor_sw128(s_q + L::kQBytes)};
+            const uint64_t k_desc0 = kt ? make_smem_desc(s_k, HD * 128, 1024, 2) : make_desc_kmajor_sw128(s_k);
+            const uint64_t v_desc0 = make_smem_desc(s_v, kKvTile * 128, 1024, 2);
+            const uint64_t p_desc[2] = {make_desc_kmajor_sw128(s_p), make_desc_kmajor_sw128(s_p + L::kPBytes)};
+            uint32_t k_step[HD / 16];     // K-major: 32 bytes per step inside a 64-wide block; transposed: 16 rows
+#pragma unroll
+            for (int k = 0; k < HD / 16; ++k)
+                k_step[k] = kt ? (uint32_t)(k * 128) : (uint32_t)((k >> 2) * (kKvTile * 8) + (k & 3) * 2);
             // S_t(j) = Q_t . K(j)^T : HD/16 MMAs of K = 16.
             auto issue_s = [&](int t, int kstage) {
-                const uint32_t qa = s_q + t * L::kQBytes;
-                const uint32_t kb = s_k + kstage * L::kKvBytes;
+                const uint64_t kd = k_desc0 + (uint64_t)(kstage * (L::kKvBytes >> 4));
 #pragma unroll
-                for (int k = 0; k < HD / 16; ++k) {
-                    const uint64_t da = make_desc_kmajor_sw128(qa + (k >> 2) * (kQTile * 128) + (k & 3) * 32);
-                    uint64_t db;
-                    if (!prm.k_transposed)
-                        db = make_desc_kmajor_sw128(kb + (k >> 2) * (kKvTile * 128) + (k & 3) * 32);
-                    else
-                        db = make_smem_desc(kb + k * 2048, HD * 128, 1024, 2);
-                    umma_f16_ss<1>(tmem_s[t], da, db, prm.k_transposed ? kIdescS_T : kIdescS, k != 0 ? 1u : 0u);
-                }
+                for (int k = 0; k < HD / 16; ++k)
+                    umma_f16_ss<1>(tmem_s[t], q_desc[t] + (uint64_t)((k >> 2) * (kQTile * 8) + (k & 3) * 2),
+                                   kd + k_step[k], idesc_s, k != 0 ? 1u : 0u);
             };
             // O_t += P_t . V(j) : 128/16 MMAs of K = 16.
             auto issue_pv = [&](int t, int vstage, bool first) {
-                const uint32_t vb = s_v + vstage * L::kKvBytes;
+                const uint64_t vd = v_desc0 + (uint64_t)(vstage * (L::kKvBytes >> 4));
 #pragma unroll
                 for (int k = 0; k < kKvTile / 16; ++k) {
-                    const uint64_t db = make_smem_desc(vb + k * 2048, kKvTile * 128, 1024, 2);
                     const uint32_t acc = (first && k == 0) ? 0u : 1u;
-                    if (P_SMEM) {
-                        const uint64_t da = make_desc_kmajor_sw128(s_p + t * L::kPBytes + (k >> 2) * (kQTile * 128) + (k & 3) * 32);
-                        umma_f16_ss<1>(tmem_o[t], da, db, kIdescPV, acc);
-                    } else {
-                        umma_f16_ts(tmem_o[t], tmem_s[t] + (uint32_t)(k * 8), db, kIdescPV, acc);
-                    }
+                    if (P_SMEM)
+                        umma_f16_ss<1>(tmem_o[t], p_desc[t] + (uint64_t)((k >> 2) * (kQTile * 8) + (k & 3) * 2),
+                                       vd + (uint64_t)(k * 128), kIdescPV, acc);
+                    else
+                        umma_f16_ts(tmem_o[t], tmem_s[t] + (uint32_t)(k * 8), vd + (uint64_t)(k * 128), kIdescPV, acc);
                 }
             };
             int kstage = 0; uint32_t kphase = 0;     // ring position of K(j+1) being consumed by S
@@ -276,22 +282,24 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
             const int key0 = j * kKvTile;
             const int last_visible = row + prm.causal_offset;           // largest key index this row may see
             const bool diag = prm.causal && (key0 + kKvTile - 1 > q0 + t * kQTile + q * 32 + prm.causal_offset);
-            // pass 1: row maximum of the raw scores
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < kKvTile / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld_32x32b_x32(ts + (uint32_t)(c * 32), v);
-                tmem_ld_wait();
-                if (diag) {
+            // The whole score row (128 fp32) comes out of TMEM once: four loads in flight, one wait.
+            uint32_t sc[kKvTile];
 #pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (key0 + c * 32 + i <= last_visible) mx = fmaxf(mx, __uint_as_float(v[i]));
-                } else {
+            for (int c = 0; c < kKvTile / 32; ++c)
+                tmem_ld_32x32b_x32(ts + (uint32_t)(c * 32), *reinterpret_cast<uint32_t(*)[32]>(&sc[c * 32]));
+            tmem_ld_wait();
+            reg_fence(sc);
+            // row maximum of the raw scores (four independent chains)
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            if (diag) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
-                }
+                for (int i = 0; i < kKvTile; ++i)
+                    if (key0 + i <= last_visible) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sc[i]));
+            } else {
+#pragma unroll
+                for (int i = 0; i < kKvTile; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sc[i]));
             }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             const float m_new = fmaxf(m_used, mx * prm.scale_log2);
             if (j == 0) {
                 m_used = m_new;
@@ -310,39 +318,48 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 }
                 tmem_st_wait();
             }
-            // pass 2: P = exp2(S * scale - m_used), row sum, bf16 P to TMEM (or shared memory)
-            float sum = 0.f;
+            // P = exp2(S * scale - m_used): the scores are read again in two halves of 64 (two loads in
+            // flight per wait), exponentiated, summed and written back as bf16 P to TMEM (or shared memory).
+            const float neg_m = -m_used;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
-            for (int c = 0; c < kKvTile / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld_32x32b_x32(ts + (uint32_t)(c * 32), v);
+            for (int h = 0; h < 2; ++h) {
+                uint32_t v[64];
+                tmem_ld_32x32b_x32(ts + (uint32_t)(h * 64), *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+                tmem_ld_32x32b_x32(ts + (uint32_t)(h * 64 + 32), *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
                 tmem_ld_wait();
-                uint32_t packed[16];
+                reg_fence(v);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    float p0 = fast_exp2(fmaf(__uint_as_float(v[2 * i]), prm.scale_log2, -m_used));
-                    float p1 = fast_exp2(fmaf(__uint_as_float(v[2 * i + 1]), prm.scale_log2, -m_used));
-                    if (diag) {
-                        if (key0 + c * 32 + 2 * i > last_visible) p0 = 0.f;
-                        if (key0 + c * 32 + 2 * i + 1 > last_visible) p1 = 0.f;
-                    }
-                    sum += p0 + p1;
-                    __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);    // .x = p0 in the low half
-                    packed[i] = *reinterpret_cast<uint32_t*>(&b);
-                }
-                if (P_SMEM) {
-                    // K-major SWIZZLE_128B image: 64-key blocks of [128 rows][128 bytes]
-                    const uint32_t rowp = s_p + t * L::kPBytes + (uint32_t)(c >> 1) * (kQTile * 128) + (uint32_t)row_in_tile * 128u;
+                for (int cc = 0; cc < 2; ++cc) {
+                    const int c = h * 2 + cc;          // 32-key chunk index
+                    uint32_t packed[16];
 #pragma unroll
-                    for (int jj = 0; jj < 4; ++jj) {
-                        const uint32_t chunk = (uint32_t)((c & 1) * 4 + jj);
-                        st_shared_v4(rowp + ((chunk ^ (uint32_t)(row_in_tile & 7)) << 4),
-                                     packed[4 * jj], packed[4 * jj + 1], packed[4 * jj + 2], packed[4 * jj + 3]);
+                    for (int i = 0; i < 16; ++i) {
+                        float p0 = fast_exp2(fmaf(__uint_as_float(v[cc * 32 + 2 * i]), prm.scale_log2, neg_m));
+                        float p1 = fast_exp2(fmaf(__uint_as_float(v[cc * 32 + 2 * i + 1]), prm.scale_log2, neg_m));
+                        if (diag) {
+                            if (key0 + c * 32 + 2 * i > last_visible) p0 = 0.f;
+                            if (key0 + c * 32 + 2 * i + 1 > last_visible) p1 = 0.f;
+                        }
+                        sum4[i & 3] += p0 + p1;
+                        __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);    // .x = p0 in the low half
+                        packed[i] = *reinterpret_cast<uint32_t*>(&b);
                     }
-                } else {
-                    tmem_st_32x32b_x16(ts + (uint32_t)(c * 16), packed);
+                    if (P_SMEM) {
+                        // K-major SWIZZLE_128B image: 64-key blocks of [128 rows][128 bytes]
+                        const uint32_t rowp = s_p + t * L::kPBytes + (uint32_t)h * (kQTile * 128) + (uint32_t)row_in_tile * 128u;
+#pragma unroll
+                        for (int jj = 0; jj < 4; ++jj) {
+                            const uint32_t chunk = (uint32_t)(cc * 4 + jj);
+                            st_shared_v4(rowp + ((chunk ^ (uint32_t)(row_in_tile & 7)) << 4),
+                                         packed[4 * jj], packed[4 * jj + 1], packed[4 * jj + 2], packed[4 * jj + 3]);
+                        }
+                    } else {
+                        tmem_st_32x32b_x16(ts + (uint32_t)(c * 16), packed);
+                    }
                 }
             }
+            const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             l += sum;
             if (P_SMEM) fence_proxy_async_smem(); else tmem_st_wait();
             tc_fence_before_sync();

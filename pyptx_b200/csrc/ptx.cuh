@@ -90,6 +90,15 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
 __device__ __forceinline__ void fence_mbarrier_init() {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
+// Register reallocation between warpgroups (all four warps of a warpgroup execute it).
+template <int N>
+__device__ __forceinline__ void reg_alloc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" :: "n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_dealloc() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" :: "n"(N));
+}
 __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
     asm volatile("bar.sync %0, %1;" :: "r"(id), "r"(threads) : "memory");
 }
@@ -291,6 +300,13 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)
 }
 __device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// Ties registers filled by tcgen05.ld to a point after tmem_ld_wait(): the empty volatile asm
+// statements keep the compiler from scheduling a use of r[i] above the wait.
+template <int N>
+__device__ __forceinline__ void reg_fence(uint32_t (&r)[N]) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) asm volatile("" : "+r"(r[i]) :: "memory");
 }
 // registers -> TMEM, same 32x32b shape.
 __device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_t (&r)[16]) {

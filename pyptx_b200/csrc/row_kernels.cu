@@ -18,9 +18,10 @@
 // (examples/hopper/rms_norm.py:105-162, layer_norm.py:120-215,
 //  swiglu.py:100-140, softmax.py:100-170) with two deliberate changes that
 // tighten accuracy to 1e-5 relative of an fp32 CPU evaluation: full-precision
-// rsqrtf/expf/division instead of the .approx instructions, and a two-pass
-// variance (sum of squared deviations from the mean, taken over registers)
-// instead of E[x^2]-mean^2.
+// rsqrtf, division and (in SwiGLU) expf instead of the .approx instructions
+// (softmax keeps ex2.approx on an exactly computed x - max, whose error stays
+// near 1e-6), and a two-pass variance (sum of squared deviations from the mean,
+// taken over registers) instead of E[x^2]-mean^2.
 #include "common.cuh"
 
 namespace pb200 {
@@ -320,8 +321,14 @@ swiglu_kernel(const float4* __restrict__ gate, const float4* __restrict__ up,
 // ---------------------------------------------------------------------------
 struct RowConfig { int threads; int vpt; };
 
-RowConfig pick_row_config(int64_t n4) {
-    // Prefer 8 float4 per thread (32 KiB per 256-thread CTA in flight).
+// `threads` > 0 asks for that CTA size (a tuning override carried in dims[2]); the smallest
+// float4-per-thread count that covers the row is chosen for it.
+RowConfig pick_row_config(int64_t n4, int threads = 0) {
+    if (threads == 128 || threads == 256 || threads == 512 || threads == 1024) {
+        for (int vpt : {1, 2, 4, 8, 16})
+            if ((int64_t)threads * vpt >= n4) return {threads, vpt};
+    }
+    // Default: 8 float4 per thread (32 KiB per 256-thread CTA in flight).
     const RowConfig table[] = {
         {32, 1}, {32, 2}, {32, 4}, {64, 4}, {128, 4}, {128, 8}, {256, 8}, {512, 8}, {1024, 8},
     };
@@ -344,12 +351,17 @@ void launch_one(int kid, dim3 grid, cudaStream_t s, void** p, int rows, int n4, 
 }
 
 constexpr int kSwigluThreads = 256;
-constexpr int kSwigluUnroll = 4;
+constexpr int kSwigluUnroll = 2;
 
 }  // namespace
 
 int plan_row(Record& r, char* err) {
-    if (r.n_dims != 2) { set_err(err, "row kernel needs dims = {rows, cols}, got %d dims", r.n_dims); return PB200_ERR_BAD_SHAPE; }
+    // dims = {rows, cols} plus an optional tuning word: CTA size for the row kernels (128 / 256 /
+    // 512 / 1024), float4 pairs in flight per thread for SwiGLU (2 / 4 / 8; default 2).  0 or absent = default.
+    if (r.n_dims != 2 && r.n_dims != 3) { set_err(err, "row kernel needs dims = {rows, cols}, got %d dims", r.n_dims); return PB200_ERR_BAD_SHAPE; }
+    const int tune = r.n_dims == 3 ? (int)r.dims[2] : 0;
+    r.dims[7] = tune;
+    r.n_dims = 2;
     const int64_t rows = r.dims[0], n = r.dims[1];
     if (rows <= 0 || n <= 0) { set_err(err, "rows=%lld cols=%lld must be positive", (long long)rows, (long long)n); return PB200_ERR_BAD_SHAPE; }
     if (n % 4 != 0) { set_err(err, "cols=%lld must be divisible by 4 (128-bit vector access)", (long long)n); return PB200_ERR_BAD_SHAPE; }
@@ -361,14 +373,15 @@ int plan_row(Record& r, char* err) {
     g.n_outputs = 1;
     if (r.kernel_id == PB200_K_SWIGLU) {
         const int64_t total4 = rows * n / 4;
-        const int64_t tile = (int64_t)kSwigluThreads * kSwigluUnroll;
+        const int unroll = (tune == 4 || tune == 8) ? tune : kSwigluUnroll;
+        const int64_t tile = (int64_t)kSwigluThreads * unroll;
         int64_t ctas = (total4 + tile - 1) / tile;
         if (ctas > 0x7fffffffLL) ctas = 0x7fffffffLL;
         g.grid[0] = (uint32_t)ctas; g.block[0] = kSwigluThreads;
         g.n_inputs = 2;
         return PB200_OK;
     }
-    RowConfig c = pick_row_config(n / 4);
+    RowConfig c = pick_row_config(n / 4, tune);
     g.grid[0] = (uint32_t)rows; g.block[0] = (uint32_t)c.threads;
     g.smem_bytes = 2 * kWarp * sizeof(float);
     g.n_inputs = r.kernel_id == PB200_K_RMS_NORM ? 2 : r.kernel_id == PB200_K_LAYER_NORM ? 3 : 1;
@@ -383,16 +396,28 @@ int launch_row(const Record& r, cudaStream_t s, void** p, char* err) {
     const float eps = (float)r.fparams[0];
     dim3 grid(r.geom.grid[0]);
     if (r.kernel_id == PB200_K_SWIGLU) {
-        swiglu_kernel<kSwigluThreads, kSwigluUnroll><<<grid, kSwigluThreads, 0, s>>>(
-            (const float4*)p[0], (const float4*)p[1], (float4*)p[2], (size_t)rows * n4);
+        const int tune = (int)r.dims[7];
+        if (tune == 4)
+            swiglu_kernel<kSwigluThreads, 4><<<grid, kSwigluThreads, 0, s>>>(
+                (const float4*)p[0], (const float4*)p[1], (float4*)p[2], (size_t)rows * n4);
+        else if (tune == 8)
+            swiglu_kernel<kSwigluThreads, 8><<<grid, kSwigluThreads, 0, s>>>(
+                (const float4*)p[0], (const float4*)p[1], (float4*)p[2], (size_t)rows * n4);
+        else
+            swiglu_kernel<kSwigluThreads, kSwigluUnroll><<<grid, kSwigluThreads, 0, s>>>(
+                (const float4*)p[0], (const float4*)p[1], (float4*)p[2], (size_t)rows * n4);
     } else {
-        RowConfig c = pick_row_config(n4);
+        RowConfig c = pick_row_config(n4, (int)r.dims[7]);
         const int kid = r.kernel_id;
 #define PB200_ROW_CASE(T, V) \
         if (c.threads == T && c.vpt == V) launch_one<T, V>(kid, grid, s, p, rows, n4, inv_n, eps); else
         PB200_ROW_CASE(32, 1) PB200_ROW_CASE(32, 2) PB200_ROW_CASE(32, 4) PB200_ROW_CASE(64, 4)
         PB200_ROW_CASE(128, 4) PB200_ROW_CASE(128, 8) PB200_ROW_CASE(256, 8) PB200_ROW_CASE(512, 8)
         PB200_ROW_CASE(1024, 8)
+        PB200_ROW_CASE(128, 1) PB200_ROW_CASE(128, 2) PB200_ROW_CASE(128, 16)
+        PB200_ROW_CASE(256, 1) PB200_ROW_CASE(256, 2) PB200_ROW_CASE(256, 4) PB200_ROW_CASE(256, 16)
+        PB200_ROW_CASE(512, 1) PB200_ROW_CASE(512, 2) PB200_ROW_CASE(512, 4) PB200_ROW_CASE(512, 16)
+        PB200_ROW_CASE(1024, 1) PB200_ROW_CASE(1024, 2) PB200_ROW_CASE(1024, 4) PB200_ROW_CASE(1024, 16)
         {
             if (kid == PB200_K_RMS_NORM)
                 long_row_kernel<0><<<grid, 1024, 0, s>>>((const float4*)p[0], (const float4*)p[1], nullptr,

@@ -12,8 +12,6 @@
 //   warp 1      MMA issuer (single thread): S_t = Q_t K^T into TMEM, O_t += P_t V
 //   warps 4-7   softmax for tile 0 (one query row per thread, TMEM lane = row)
 //   warps 8-11  softmax for tile 1
-// The first warpgroup gives registers back (setmaxnreg 64) so that the softmax warpgroups can
-// hold a whole 128-element score row per thread (setmaxnreg 208).
 // TMEM (512 columns): S0 | S1 | O0 | O1, 128 columns each.  P overwrites the first 64
 // columns of its S in place (two bf16 per column) and is consumed by the MMA directly
 // from TMEM, so P never touches shared memory.  A template switch keeps P in swizzled
@@ -191,38 +189,45 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         // ------------------------------- MMA issuer ---------------------------------
         if (lane == 0) {
             bool ok = mbar_wait(bar_q, 0, ctx, 21);
-            // The issuing thread is the serial resource of this kernel: a 128x128x16 MMA retires
-            // every 64 clocks, so descriptors are built once here and each MMA costs two 64-bit
-            // adds.  Offsets are in descriptor units (16 bytes).
+            // The issuing thread is the serial resource of this kernel: it shares its scheduler with
+            // two busy softmax warps, and a 128x128x16 MMA retires every 64 clocks.  Descriptors are
+            // therefore built once; their high word is constant and every per-MMA change stays inside
+            // the 14-bit start-address field of the low word, so an MMA costs one 32-bit add per operand.
+            // One thread issues for both tiles on purpose: the fixed order PV0 S0 PV1 S1 keeps the two
+            // tiles half a period apart, so one tile's softmax always overlaps the other tile's MMAs.
             const bool kt = prm.k_transposed != 0;
             const uint32_t idesc_s = kt ? kIdescS_T : kIdescS;
-            const uint64_t q_desc[2] = {make_desc_kmajor_sw128(s_q), make_desc_kmajor_sw128(s_q + L::kQBytes)};
-            const uint64_t k_desc0 = kt ? make_smem_desc(s_k, HD * 128, 1024, 2) : make_desc_kmajor_sw128(s_k);
-            const uint64_t v_desc0 = make_smem_desc(s_v, kKvTile * 128, 1024, 2);
-            const uint64_t p_desc[2] = {make_desc_kmajor_sw128(s_p), make_desc_kmajor_sw128(s_p + L::kPBytes)};
+            const uint64_t qd0 = make_desc_kmajor_sw128(s_q), qd1 = make_desc_kmajor_sw128(s_q + L::kQBytes);
+            const uint64_t kd0 = kt ? make_smem_desc(s_k, HD * 128, 1024, 2) : make_desc_kmajor_sw128(s_k);
+            const uint64_t vd0 = make_smem_desc(s_v, kKvTile * 128, 1024, 2);
+            const uint64_t pd0 = make_desc_kmajor_sw128(s_p), pd1 = make_desc_kmajor_sw128(s_p + L::kPBytes);
+            const uint32_t q_lo[2] = {(uint32_t)qd0, (uint32_t)qd1}, q_hi = (uint32_t)(qd0 >> 32);
+            const uint32_t p_lo[2] = {(uint32_t)pd0, (uint32_t)pd1}, p_hi = (uint32_t)(pd0 >> 32);
+            const uint32_t k_lo0 = (uint32_t)kd0, k_hi = (uint32_t)(kd0 >> 32);
+            const uint32_t v_lo0 = (uint32_t)vd0, v_hi = (uint32_t)(vd0 >> 32);
             uint32_t k_step[HD / 16];     // K-major: 32 bytes per step inside a 64-wide block; transposed: 16 rows
 #pragma unroll
             for (int k = 0; k < HD / 16; ++k)
                 k_step[k] = kt ? (uint32_t)(k * 128) : (uint32_t)((k >> 2) * (kKvTile * 8) + (k & 3) * 2);
             // S_t(j) = Q_t . K(j)^T : HD/16 MMAs of K = 16.
             auto issue_s = [&](int t, int kstage) {
-                const uint64_t kd = k_desc0 + (uint64_t)(kstage * (L::kKvBytes >> 4));
+                const uint32_t kl = k_lo0 + (uint32_t)(kstage * (L::kKvBytes >> 4));
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k)
-                    umma_f16_ss<1>(tmem_s[t], q_desc[t] + (uint64_t)((k >> 2) * (kQTile * 8) + (k & 3) * 2),
-                                   kd + k_step[k], idesc_s, k != 0 ? 1u : 0u);
+                    umma_f16_ss_lohi(tmem_s[t], q_lo[t] + (uint32_t)((k >> 2) * (kQTile * 8) + (k & 3) * 2), q_hi,
+                                     kl + k_step[k], k_hi, idesc_s, k != 0 ? 1u : 0u);
             };
             // O_t += P_t . V(j) : 128/16 MMAs of K = 16.
             auto issue_pv = [&](int t, int vstage, bool first) {
-                const uint64_t vd = v_desc0 + (uint64_t)(vstage * (L::kKvBytes >> 4));
+                const uint32_t vl = v_lo0 + (uint32_t)(vstage * (L::kKvBytes >> 4));
 #pragma unroll
                 for (int k = 0; k < kKvTile / 16; ++k) {
                     const uint32_t acc = (first && k == 0) ? 0u : 1u;
                     if (P_SMEM)
-                        umma_f16_ss<1>(tmem_o[t], p_desc[t] + (uint64_t)((k >> 2) * (kQTile * 8) + (k & 3) * 2),
-                                       vd + (uint64_t)(k * 128), kIdescPV, acc);
+                        umma_f16_ss_lohi(tmem_o[t], p_lo[t] + (uint32_t)((k >> 2) * (kQTile * 8) + (k & 3) * 2), p_hi,
+                                         vl + (uint32_t)(k * 128), v_hi, kIdescPV, acc);
                     else
-                        umma_f16_ts(tmem_o[t], tmem_s[t] + (uint32_t)(k * 8), vd + (uint64_t)(k * 128), kIdescPV, acc);
+                        umma_f16_ts_lohi(tmem_o[t], tmem_s[t] + (uint32_t)(k * 8), vl + (uint32_t)(k * 128), v_hi, kIdescPV, acc);
                 }
             };
             int kstage = 0; uint32_t kphase = 0;     // ring position of K(j+1) being consumed by S

@@ -263,6 +263,23 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, ui
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
                  :: "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// The same two instructions with each 64-bit descriptor given as (low, high) words.  The fields
+// that change between MMAs (start address) live in the low word, so callers keep the high word
+// constant and advance the low word with one 32-bit add.
+__device__ __forceinline__ void umma_f16_ss_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                                 uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\n.reg .b64 da, db;\nsetp.ne.b32 p, %6, 0;\n"
+                 "mov.b64 da, {%1, %2};\nmov.b64 db, {%3, %4};\n"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}"
+                 :: "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_f16_ts_lohi(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
+                                                 uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\n.reg .b64 db;\nsetp.ne.b32 p, %5, 0;\n"
+                 "mov.b64 db, {%2, %3};\n"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n}"
+                 :: "r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
 // Makes `bar` (a shared::cluster address: this CTA's, or a peer's obtained
 // with map_to_cta) receive one arrival when all MMAs issued so far by this
 // thread have completed.  Implies tcgen05.fence::before_thread_sync.

@@ -255,6 +255,29 @@ def row_kernel_table(torch, peaks, steps: int, warmup: int) -> dict:
         table[name] = {"ms": ms, "GB/s": gbs, "bytes": nbytes, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
                        "frac_of_8TBps": gbs / 8000.0, "timing": "cuda-graph replay, 6 rotating buffer sets",
                        "ms_eager_loop": ms_eager}
+    # torch's own GPU kernels for the same formulas, same buffers, same method (what the
+    # reference's kernel benchmark prints next to its kernels, bench_blackwell_kernels.py:61-62, 85-86, 108-109)
+    F = torch.nn.functional
+    torch_refs = {
+        "rms_norm": lambda i: xs[i] * torch.rsqrt((xs[i] * xs[i]).mean(-1, keepdim=True) + 1e-6) * w,
+        "layer_norm": lambda i: F.layer_norm(xs[i], (N,), w, b, 1e-5),
+        "swiglu": lambda i: F.silu(xs[i]) * us[i],
+        "softmax": lambda i: torch.softmax(xs[i], -1),
+    }
+    for name, ref in torch_refs.items():
+        counter = [0]
+        outs = [None] * SETS
+
+        def fn():
+            i = counter[0] % SETS
+            outs[i] = ref(i)
+            counter[0] += 1
+
+        try:
+            ms = time_graph(fn, 24, torch)
+            table[name]["torch_gpu_GB/s"] = table[name]["bytes"] / (ms * 1e-3) / 1e9
+        except Exception as exc:  # noqa: BLE001 - context only
+            table[name]["torch_gpu_error"] = str(exc)[:120]
     return table
 
 
@@ -450,6 +473,10 @@ def run_ours(args) -> None:
                 k = build_grouped_gemm(G, 2048, 256, 2048)
                 ms = time_graph(lambda: k(ga, gb), 20, torch)
                 extras[f"grouped_G{G}_tflops"] = 2.0 * G * 2048 * 256 * 2048 / (ms * 1e-3) / 1e12
+                a3 = ga.view(G, 2048, 2048)
+                b3 = gb.view(G, 256, 2048).transpose(1, 2)
+                ms = time_graph(lambda: torch.bmm(a3, b3), 20, torch)
+                extras[f"grouped_G{G}_torch_bmm_bf16_tflops"] = 2.0 * G * 2048 * 256 * 2048 / (ms * 1e-3) / 1e12
         except Exception as exc:  # noqa: BLE001 - context only
             extras["grouped_error"] = str(exc)[:200]
         try:

@@ -1,0 +1,85 @@
+"""Sharded calls on real GPUs, one process per GPU (run under ``torch.distributed.run``; with a
+single process the same code paths run with world size 1).  Each rank computes its shard with
+the CUDA kernels; the gathered result must equal the CPU oracle on the unsharded problem."""
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+
+from oracle import formulas, inputs
+from pyptx_b200 import dist as pdist
+from pyptx_b200.examples.blackwell.flash_attention import build_flash_attention
+from pyptx_b200.examples.blackwell.gemm_highperf_blackwell import build_gemm, build_gemm_2sm
+from pyptx_b200.examples.blackwell.grouped_gemm import build_grouped_gemm
+from pyptx_b200.examples.blackwell.rms_norm import build_rms_norm
+from pyptx_b200.types import f32
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module", autouse=True)
+def process_group():
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1 and not dist.is_initialized():
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    yield
+    if dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def _wr():
+    return (dist.get_world_size(), dist.get_rank()) if dist.is_initialized() else (1, 0)
+
+
+def test_rows_sharded_and_gathered():
+    world, rank = _wr()
+    x, w = inputs.rms_norm_inputs(512, 2048)
+    ref = formulas.rms_norm_ref(x, w)
+    shard = pdist.shard_rows(build_rms_norm, 512, 2048, world=world, rank=rank)
+    y = shard(shard.slice(x).cuda().contiguous(), w.cuda())
+    assert formulas.rel_fro(y.cpu(), ref[shard.start:shard.stop]) < 1e-5
+    full = pdist.shard_rows(build_rms_norm, 512, 2048, world=world, rank=rank, gather=True)
+    yg = full(full.slice(x).cuda().contiguous(), w.cuda())
+    assert yg.shape == ref.shape and formulas.rel_fro(yg.cpu(), ref) < 1e-5
+
+
+@pytest.mark.parametrize("builder", [build_gemm, build_gemm_2sm])
+def test_gemm_m_sharded_b_replicated(builder):
+    world, rank = _wr()
+    M, N, K = 2048, 512, 256
+    a, bt = inputs.gemm_inputs(M, N, K)
+    ref = formulas.gemm_ref(a, bt)
+    shard = pdist.shard_gemm(builder, M, N, K, world=world, rank=rank, gather=True)
+    d = shard(shard.slice(a).cuda().contiguous(), bt.cuda())
+    assert d.shape == ref.shape and formulas.rel_fro(d.cpu(), ref) < 1e-4
+
+
+def test_grouped_experts_partitioned():
+    world, rank = _wr()
+    G, M, N, K = 8, 256, 256, 128
+    a, bt = inputs.grouped_gemm_inputs(G, M, N, K)
+    ref = formulas.grouped_gemm_ref(a, bt, G)
+    shard = pdist.shard_grouped_gemm(build_grouped_gemm, G, M, N, K, world=world, rank=rank, gather=True)
+    g0, g1 = shard.start // M, shard.stop // M
+    local_a = a[shard.start:shard.stop].cuda().contiguous()
+    local_b = bt[g0 * N:g1 * N].cuda().contiguous()
+    c = shard(local_a, local_b)
+    assert c.shape == ref.shape and formulas.rel_fro(c.cpu(), ref) < 1e-4
+
+
+def test_attention_batch_head_sharded():
+    world, rank = _wr()
+    B, H, S, d = 2, 8, 256, 64
+    q, k, v = inputs.attention_inputs(B * H, S, S, d)
+    ref = formulas.attention_ref(q, k, v, causal=True)
+    shard = pdist.shard_attention(build_flash_attention, B, H, S, S, d, world=world, rank=rank, gather=True,
+                                  causal=True, out_dtype=f32)
+    sl = slice(shard.start, shard.stop)
+    o = shard.kernel(q[sl][None].cuda().contiguous(), k[sl][None].cuda().contiguous(), v[sl][None].cuda().contiguous())
+    og = pdist.all_gather_rows(o[0], pdist.counts(B * H, world), rank) if world > 1 else o[0]
+    assert og.shape == ref.shape and formulas.rel_fro(og.cpu(), ref) < 1e-2

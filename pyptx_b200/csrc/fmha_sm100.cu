@@ -67,9 +67,32 @@ struct FmhaSmem {
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
+    // Not volatile on purpose: the compiler must be free to batch the FMAs of a chunk ahead of
+    // its exponentials; a volatile asm pins every ex2 behind its own FMA and serialises the chunk.
     float y;
-    asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+
+// max of three (one instruction on sm_100)
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// (a0, a1) * scale + bias on the packed-f32x2 path: one FFMA2 for two scores.
+__device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, float scale, float bias) {
+    asm("{\n.reg .b64 a, s, b, d;\n"
+        "mov.b64 a, {%2, %3};\nmov.b64 s, {%4, %4};\nmov.b64 b, {%5, %5};\n"
+        "fma.rn.f32x2 d, a, s, b;\nmov.b64 {%0, %1}, d;\n}"
+        : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(scale), "f"(bias));
+}
+// (acc0, acc1) += (p0, p1): one FADD2.
+__device__ __forceinline__ void add2(float& acc0, float& acc1, float p0, float p1) {
+    asm("{\n.reg .b64 a, p;\n"
+        "mov.b64 a, {%0, %1};\nmov.b64 p, {%2, %3};\n"
+        "add.rn.f32x2 a, a, p;\nmov.b64 {%0, %1}, a;\n}"
+        : "+f"(acc0), "+f"(acc1) : "f"(p0), "f"(p1));
 }
 
 template <int HD, typename OutT, bool P_SMEM>
@@ -294,7 +317,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 tmem_ld_32x32b_x32(ts + (uint32_t)(c * 32), *reinterpret_cast<uint32_t(*)[32]>(&sc[c * 32]));
             tmem_ld_wait();
             reg_fence(sc);
-            // row maximum of the raw scores (four independent chains)
+            // row maximum of the raw scores: four independent chains of 3-input max
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (diag) {
 #pragma unroll
@@ -302,7 +325,12 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     if (key0 + i <= last_visible) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sc[i]));
             } else {
 #pragma unroll
-                for (int i = 0; i < kKvTile; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sc[i]));
+                for (int i = 0; i < kKvTile; i += 8) {
+                    mx4[0] = fmax3(mx4[0], __uint_as_float(sc[i]), __uint_as_float(sc[i + 1]));
+                    mx4[1] = fmax3(mx4[1], __uint_as_float(sc[i + 2]), __uint_as_float(sc[i + 3]));
+                    mx4[2] = fmax3(mx4[2], __uint_as_float(sc[i + 4]), __uint_as_float(sc[i + 5]));
+                    mx4[3] = fmax3(mx4[3], __uint_as_float(sc[i + 6]), __uint_as_float(sc[i + 7]));
+                }
             }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             const float m_new = fmaxf(m_used, mx * prm.scale_log2);
@@ -338,17 +366,29 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 for (int cc = 0; cc < 2; ++cc) {
                     const int c = h * 2 + cc;          // 32-key chunk index
                     uint32_t packed[16];
+                    if (!diag) {
+                        // Common case, no mask: per pair of scores one FFMA2, two EX2, one FADD2, one pack.
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        float p0 = fast_exp2(fmaf(__uint_as_float(v[cc * 32 + 2 * i]), prm.scale_log2, neg_m));
-                        float p1 = fast_exp2(fmaf(__uint_as_float(v[cc * 32 + 2 * i + 1]), prm.scale_log2, neg_m));
-                        if (diag) {
+                        for (int i = 0; i < 16; ++i) {
+                            float t0, t1;
+                            fma2(t0, t1, __uint_as_float(v[cc * 32 + 2 * i]), __uint_as_float(v[cc * 32 + 2 * i + 1]),
+                                 prm.scale_log2, neg_m);
+                            const float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
+                            add2(sum4[2 * (i & 1)], sum4[2 * (i & 1) + 1], p0, p1);
+                            __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);    // .x = p0 in the low half
+                            packed[i] = *reinterpret_cast<uint32_t*>(&b);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            float p0 = fast_exp2(fmaf(__uint_as_float(v[cc * 32 + 2 * i]), prm.scale_log2, neg_m));
+                            float p1 = fast_exp2(fmaf(__uint_as_float(v[cc * 32 + 2 * i + 1]), prm.scale_log2, neg_m));
                             if (key0 + c * 32 + 2 * i > last_visible) p0 = 0.f;
                             if (key0 + c * 32 + 2 * i + 1 > last_visible) p1 = 0.f;
+                            sum4[i & 3] += p0 + p1;
+                            __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
+                            packed[i] = *reinterpret_cast<uint32_t*>(&b);
                         }
-                        sum4[i & 3] += p0 + p1;
-                        __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);    // .x = p0 in the low half
-                        packed[i] = *reinterpret_cast<uint32_t*>(&b);
                     }
                     if (P_SMEM) {
                         // K-major SWIZZLE_128B image: 64-key blocks of [128 rows][128 bytes]

@@ -40,6 +40,10 @@ constexpr int kKvTile = 128;      // keys per K/V tile
 constexpr int kFmhaThreads = 384; // 3 warpgroups: {TMA, MMA, 2 idle}, softmax tile 0, softmax tile 1
 constexpr uint32_t kDebugPSmem = 1u << 17;   // create flag: keep P in shared memory (head_dim 64)
 constexpr float kRescaleThreshold = 8.0f;    // log2 units
+#ifndef PB200_FMA_EXP_PAIRS
+#define PB200_FMA_EXP_PAIRS 3
+#endif
+constexpr int kFmaExpPairsOf8 = PB200_FMA_EXP_PAIRS;   // of every 8 score pairs, how many take the FMA-pipe exp2
 
 struct FmhaParams {
     int bh;            // batch * heads
@@ -86,6 +90,37 @@ __device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, f
         "mov.b64 a, {%2, %3};\nmov.b64 s, {%4, %4};\nmov.b64 b, {%5, %5};\n"
         "fma.rn.f32x2 d, a, s, b;\nmov.b64 {%0, %1}, d;\n}"
         : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(scale), "f"(bias));
+}
+// General packed forms: (d0, d1) = (a0, a1) * (b0, b1) + (c0, c1) and (d0, d1) = (a0, a1) + (b0, b1).
+__device__ __forceinline__ void fma2v(float& d0, float& d1, float a0, float a1, float b0, float b1, float c0, float c1) {
+    asm("{\n.reg .b64 a, b, c, d;\n"
+        "mov.b64 a, {%2, %3};\nmov.b64 b, {%4, %5};\nmov.b64 c, {%6, %7};\n"
+        "fma.rn.f32x2 d, a, b, c;\nmov.b64 {%0, %1}, d;\n}"
+        : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1), "f"(c0), "f"(c1));
+}
+__device__ __forceinline__ void add2v(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+    asm("{\n.reg .b64 a, b, d;\n"
+        "mov.b64 a, {%2, %3};\nmov.b64 b, {%4, %5};\n"
+        "add.rn.f32x2 d, a, b;\nmov.b64 {%0, %1}, d;\n}"
+        : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+// 2^x for two arguments on the FMA pipe instead of the MUFU unit, which is the scarcer resource
+// of this kernel (16 exponentials per clock per SM against 8192 MMA flops).  Round-to-nearest
+// split x = n + f with the 1.5*2^23 trick, cubic minimax for 2^f on [-0.5, 0.5] (relative error
+// 1.0e-4, far below the bf16 rounding of P), n added into the exponent field.  Needs x >= -126.
+__device__ __forceinline__ void exp2_fma_pair(float& r0, float& r1, float x0, float x1) {
+    constexpr float kMagic = 12582912.0f;
+    x0 = fmaxf(x0, -126.0f);
+    x1 = fmaxf(x1, -126.0f);
+    float t0, t1, n0, n1, f0, f1, p0, p1;
+    add2v(t0, t1, x0, x1, kMagic, kMagic);
+    add2v(n0, n1, t0, t1, -kMagic, -kMagic);
+    add2v(f0, f1, x0, x1, -n0, -n1);
+    fma2v(p0, p1, f0, f1, 0.05500892f, 0.05500892f, 0.24221097f, 0.24221097f);
+    fma2v(p0, p1, p0, p1, f0, f1, 0.69328290f, 0.69328290f);
+    fma2v(p0, p1, p0, p1, f0, f1, 1.0f, 1.0f);
+    r0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
+    r1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
 }
 // (acc0, acc1) += (p0, p1): one FADD2.
 __device__ __forceinline__ void add2(float& acc0, float& acc1, float p0, float p1) {
@@ -373,7 +408,9 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                             float t0, t1;
                             fma2(t0, t1, __uint_as_float(v[cc * 32 + 2 * i]), __uint_as_float(v[cc * 32 + 2 * i + 1]),
                                  prm.scale_log2, neg_m);
-                            const float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
+                            float p0, p1;
+                            if ((i & 7) < kFmaExpPairsOf8) exp2_fma_pair(p0, p1, t0, t1);   // compile-time choice per pair
+                            else { p0 = fast_exp2(t0); p1 = fast_exp2(t1); }
                             add2(sum4[2 * (i & 1)], sum4[2 * (i & 1) + 1], p0, p1);
                             __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);    // .x = p0 in the low half
                             packed[i] = *reinterpret_cast<uint32_t*>(&b);

@@ -48,6 +48,7 @@ using namespace ptx;
 constexpr int BM = 128;          // rows per CTA tile (TMEM lanes)
 constexpr int BK = 64;           // bf16 elements per k-tile = one 128-byte swizzle row
 constexpr int UMMA_K = 16;       // K per tcgen05.mma for 16-bit operands
+static_assert(BK / UMMA_K == 4, "the MMA issuer is written out for four MMAs per k-tile");
 constexpr int kThreads = 192;    // 6 warps
 constexpr int kEpiWarps = 4;
 constexpr int kStageRows = 32;   // rows per epilogue store box (one warp)
@@ -190,9 +191,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     } else if (warp == 1) {
         // ------------------------- MMA issuer ---------------------------
         if (lane == 0 && is_leader) {
+            // This thread is the serial resource of the kernel (it shares its scheduler with an
+            // epilogue warp, and four MMAs retire every 512 clocks), so its loop carries running
+            // barrier addresses and running descriptor low words instead of recomputing them; only
+            // the 14-bit start-address field of a descriptor ever changes, and that is in the low word.
             int stage = 0; uint32_t phase = 0;
-            const uint32_t empty_peer = CTA_GROUP == 2 ? map_to_cta(bar_empty, 1) : 0u;
+            const uint32_t empty_peer0 = CTA_GROUP == 2 ? map_to_cta(bar_empty, 1) : 0u;
             const uint32_t tfull_peer = CTA_GROUP == 2 ? map_to_cta(bar_tfull, 1) : 0u;
+            const uint64_t da0 = make_desc_kmajor_sw128(s_a), db0 = make_desc_kmajor_sw128(s_b);
+            const uint32_t a_hi = (uint32_t)(da0 >> 32), b_hi = (uint32_t)(db0 >> 32);
+            const uint32_t a_lo0 = (uint32_t)da0, b_lo0 = (uint32_t)db0;
+            uint32_t a_lo = a_lo0, b_lo = b_lo0;
+            uint32_t full_cur = bar_full, empty_cur = bar_empty, empty_peer = empty_peer0;
             bool ok = true;
             int local = 0;
             for (int t = unit; t < n_tiles && ok; t += n_units, ++local) {
@@ -202,18 +212,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
                 for (int kt = 0; kt < shape.k_tiles; ++kt) {
-                    if (!(ok = mbar_wait(bar_full + 8 * stage, phase, ctx, 3))) break;
+                    if (!(ok = mbar_wait(full_cur, phase, ctx, 3))) break;
                     tc_fence_after_sync();
-                    const uint64_t da = make_desc_kmajor_sw128(s_a + stage * Plan::kABytes);
-                    const uint64_t db = make_desc_kmajor_sw128(s_b + stage * Plan::kBBytes);
-#pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k) {
-                        // +32 bytes along K inside the 128-byte swizzle row = +2 in the encoded address.
-                        umma_f16_ss<CTA_GROUP>(d_tmem, da + 2 * k, db + 2 * k, kIdesc, (kt | k) != 0 ? 1u : 0u);
+                    // +32 bytes along K inside the 128-byte swizzle row = +2 in the encoded address.
+                    umma_f16_ss_lohi<CTA_GROUP>(d_tmem, a_lo, a_hi, b_lo, b_hi, kIdesc, kt != 0 ? 1u : 0u);
+                    umma_f16_ss_lohi<CTA_GROUP>(d_tmem, a_lo + 2, a_hi, b_lo + 2, b_hi, kIdesc, 1u);
+                    umma_f16_ss_lohi<CTA_GROUP>(d_tmem, a_lo + 4, a_hi, b_lo + 4, b_hi, kIdesc, 1u);
+                    umma_f16_ss_lohi<CTA_GROUP>(d_tmem, a_lo + 6, a_hi, b_lo + 6, b_hi, kIdesc, 1u);
+                    umma_commit<CTA_GROUP>(empty_cur);
+                    if (CTA_GROUP == 2) umma_commit<CTA_GROUP>(empty_peer);
+                    if (++stage == kStages) {
+                        stage = 0; phase ^= 1u;
+                        a_lo = a_lo0; b_lo = b_lo0; full_cur = bar_full; empty_cur = bar_empty; empty_peer = empty_peer0;
+                    } else {
+                        a_lo += Plan::kABytes >> 4; b_lo += Plan::kBBytes >> 4;
+                        full_cur += 8; empty_cur += 8; empty_peer += 8;
                     }
-                    umma_commit<CTA_GROUP>(bar_empty + 8 * stage);
-                    if (CTA_GROUP == 2) umma_commit<CTA_GROUP>(empty_peer + 8 * stage);
-                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
                 umma_commit<CTA_GROUP>(bar_tfull + 8 * buf);

@@ -266,12 +266,19 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, ui
 // The same two instructions with each 64-bit descriptor given as (low, high) words.  The fields
 // that change between MMAs (start address) live in the low word, so callers keep the high word
 // constant and advance the low word with one 32-bit add.
+template <int CTA_GROUP = 1>
 __device__ __forceinline__ void umma_f16_ss_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
                                                  uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n.reg .pred p;\n.reg .b64 da, db;\nsetp.ne.b32 p, %6, 0;\n"
-                 "mov.b64 da, {%1, %2};\nmov.b64 db, {%3, %4};\n"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}"
-                 :: "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+    if (CTA_GROUP == 1)
+        asm volatile("{\n.reg .pred p;\n.reg .b64 da, db;\nsetp.ne.b32 p, %6, 0;\n"
+                     "mov.b64 da, {%1, %2};\nmov.b64 db, {%3, %4};\n"
+                     "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}"
+                     :: "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+    else
+        asm volatile("{\n.reg .pred p;\n.reg .b64 da, db;\nsetp.ne.b32 p, %6, 0;\n"
+                     "mov.b64 da, {%1, %2};\nmov.b64 db, {%3, %4};\n"
+                     "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n}"
+                     :: "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void umma_f16_ts_lohi(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
                                                  uint32_t idesc, uint32_t accumulate) {

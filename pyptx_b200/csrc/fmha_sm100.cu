@@ -173,7 +173,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     int n_kv[2];
 #pragma unroll
     for (int t = 0; t < 2; ++t) {
-        int n = prm.s_kv / kKvTile;
+        int n = (prm.s_kv + kKvTile - 1) / kKvTile;     // the last tile may be partial: TMA fills it with zeros
         if (prm.causal) {
             const int last_key = q0 + t * kQTile + kQTile - 1 + prm.causal_offset;   // of the tile's last row
             n = min(n, max(last_key / kKvTile + 1, 1));
@@ -343,8 +343,11 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
             if (!ok) break;
             tc_fence_after_sync();
             const int key0 = j * kKvTile;
-            const int last_visible = row + prm.causal_offset;           // largest key index this row may see
-            const bool diag = prm.causal && (key0 + kKvTile - 1 > q0 + t * kQTile + q * 32 + prm.causal_offset);
+            // Largest key index this row may see: the causal bound and the end of the sequence.
+            const int last_visible = prm.causal ? min(row + prm.causal_offset, prm.s_kv - 1) : prm.s_kv - 1;
+            // Tiles that cross the diagonal (for any row of this warp) or the end of K/V take the masked path.
+            const bool diag = (prm.causal && (key0 + kKvTile - 1 > q0 + t * kQTile + q * 32 + prm.causal_offset)) ||
+                              (key0 + kKvTile > prm.s_kv);
             // The whole score row (128 fp32) comes out of TMEM once: four loads in flight, one wait.
             uint32_t sc[kKvTile];
 #pragma unroll
@@ -457,11 +460,13 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
             tc_fence_after_sync();
             const float inv = 1.0f / l;
             OutT* dst = out + ((size_t)bh * prm.s_q + row) * HD;
+            const bool row_exists = row < prm.s_q;          // a partial last query tile computes padding rows
 #pragma unroll 1
             for (int c = 0; c < HD / 32; ++c) {
                 uint32_t o[32];
                 tmem_ld_32x32b_x32(to + (uint32_t)(c * 32), o);
                 tmem_ld_wait();
+                if (!row_exists) continue;
                 if (sizeof(OutT) == 4) {
 #pragma unroll
                     for (int i = 0; i < 8; ++i)
@@ -556,8 +561,11 @@ int plan_attention(Record& r, char* err) {
     const int64_t BH = r.dims[0], SQ = r.dims[1], SKV = r.dims[2], HD = r.dims[3];
     if (BH < 1 || SQ < 1 || SKV < 1) { set_err(err, "batch*heads, S_q, S_kv must be positive"); return PB200_ERR_BAD_SHAPE; }
     if (HD != 64 && HD != 128) { set_err(err, "head_dim=%lld must be 64 or 128", (long long)HD); return PB200_ERR_BAD_SHAPE; }
-    if (SQ % kQTile != 0) { set_err(err, "S_q=%lld must be divisible by %d", (long long)SQ, kQTile); return PB200_ERR_BAD_SHAPE; }
-    if (SKV % kKvTile != 0) { set_err(err, "S_kv=%lld must be divisible by %d", (long long)SKV, kKvTile); return PB200_ERR_BAD_SHAPE; }
+    if ((r.flags & PB200_F_K_TRANSPOSED) && SKV % 8 != 0) {
+        set_err(err, "S_kv=%lld must be divisible by 8 when K is given transposed (16-byte row pitch)", (long long)SKV);
+        return PB200_ERR_BAD_SHAPE;
+    }
+    if (SQ > 0x7fffffffLL / 256 || SKV > 0x7fffffffLL / 256) { set_err(err, "sequence length too large"); return PB200_ERR_BAD_SHAPE; }
     if ((r.flags & PB200_F_CAUSAL) && SKV < SQ) { set_err(err, "causal attention needs S_kv >= S_q"); return PB200_ERR_BAD_SHAPE; }
     if (BH > 65535) { set_err(err, "batch*heads=%lld exceeds 65535", (long long)BH); return PB200_ERR_BAD_SHAPE; }
     if ((r.flags & kDebugPSmem) && HD != 64) { set_err(err, "the shared-memory P variant exists for head_dim 64 only"); return PB200_ERR_BAD_SHAPE; }

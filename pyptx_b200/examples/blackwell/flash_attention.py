@@ -25,8 +25,8 @@ HEAD_DIMS = (64, 128)
 
 def _check(seq_q: int, seq_kv: int, head_dim: int, causal: bool) -> None:
     assert head_dim in HEAD_DIMS, f"head_dim={head_dim} must be one of {HEAD_DIMS}"
-    assert seq_q >= BLOCK_M and seq_q % BLOCK_M == 0, f"M_q={seq_q} must be a positive multiple of {BLOCK_M}"
-    assert seq_kv >= BLOCK_N and seq_kv % BLOCK_N == 0, f"N_seq={seq_kv} must be a positive multiple of {BLOCK_N}"
+    assert seq_q >= 1, f"M_q={seq_q} must be positive"
+    assert seq_kv >= 1, f"N_seq={seq_kv} must be positive"
     assert not causal or seq_kv >= seq_q, "causal attention needs N_seq >= M_q"
 
 
@@ -37,7 +37,8 @@ def build_flash_attention(batch: int, heads: int, seq_q: int, seq_kv: int | None
     """Kernel ``k(Q[B,H,Sq,d], K[B,H,Skv,d], V[B,H,Skv,d]) -> O[B,H,Sq,d]`` (bf16 in).
 
     ``causal`` lets query ``i`` see keys ``j <= i + (Skv - Sq)``.  ``sm_scale`` defaults to
-    ``1/sqrt(head_dim)``.  ``out_dtype`` is bf16 (default) or f32.
+    ``1/sqrt(head_dim)``.  ``out_dtype`` is bf16 (default) or f32.  Sequence lengths need not be
+    multiples of the 128-wide tiles: partial tiles are zero-filled by TMA and masked.
     """
     assert arch.startswith("sm_100"), "Blackwell attention is only implemented for sm_100*"
     seq_kv = seq_q if seq_kv is None else seq_kv

@@ -122,6 +122,29 @@ def test_large_scores_rescale_path(causal):
     check_bf16_matmul(o, formulas.attention_ref(q, k, v, causal=causal, sm_scale=1.0))
 
 
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("Sq,Skv", [(1, 1), (5, 40), (100, 100), (129, 300), (200, 513), (257, 257), (383, 1000)])
+def test_ragged_sequence_lengths(Sq, Skv, d, causal):
+    """Lengths that are not multiples of the 128-wide tiles: zero-filled partial tiles + masks."""
+    q, k, v = _inputs(1, 3, Sq, Skv, d)
+    o = _run(q, k, v, causal=causal)
+    check_bf16_matmul(o, formulas.attention_ref(q, k, v, causal=causal))
+
+
+def test_ragged_single_head_reference_layout():
+    """The reference's call form with K transposed; N_seq a multiple of 8 but not of 64 or 128."""
+    M_q, N_seq, HD = 192, 200, 64
+    torch.manual_seed(1)
+    q = (torch.randn(M_q, HD) * 0.3).to(torch.bfloat16)
+    k = (torch.randn(N_seq, HD) * 0.3).to(torch.bfloat16)
+    v = (torch.randn(N_seq, HD) * 0.3).to(torch.bfloat16)
+    o = build_flash_attention_hopper(M_q, N_seq, HD)(q.cuda(), k.t().contiguous().cuda(), v.cuda()).cpu()
+    check_bf16_matmul(o, formulas.attention_ref(q, k, v))
+    with pytest.raises(AssertionError, match="divisible by 8"):
+        build_flash_attention_hopper(128, 100, 64)
+
+
 def test_bf16_output_and_scale():
     q, k, v = _inputs(2, 2, 256, 256, 128)
     o = _run(q, k, v, out_dtype=bf16, sm_scale=0.05)

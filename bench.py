@@ -477,6 +477,26 @@ def run_ours(args) -> None:
                 b3 = gb.view(G, 256, 2048).transpose(1, 2)
                 ms = time_graph(lambda: torch.bmm(a3, b3), 20, torch)
                 extras[f"grouped_G{G}_torch_bmm_bf16_tflops"] = 2.0 * G * 2048 * 256 * 2048 / (ms * 1e-3) / 1e12
+            # MoE up-projection + activation: one fused kernel against grouped GEMM followed by SwiGLU
+            from pyptx_b200.examples.blackwell.grouped_gemm import build_grouped_gemm_swiglu
+            from pyptx_b200.examples.blackwell.swiglu import build_fused_silu_mul
+            from pyptx_b200.types import bf16 as _bf16
+            G, M, F, K = 8, 2048, 1024, 2048
+            ga, gw = inputs.grouped_gemm_inputs(G, M, 2 * F, K)
+            ga, gw = ga.cuda(), gw.cuda()
+            fused = build_grouped_gemm_swiglu(G, M, F, K, out_dtype=_bf16)
+            two_a, two_b = build_grouped_gemm(G, M, 2 * F, K), build_fused_silu_mul(G * M, F, out_dtype=_bf16)
+
+            def two_kernels():
+                c = two_a(ga, gw)
+                return two_b(c[:, :F].contiguous(), c[:, F:].contiguous())
+
+            fl = 2.0 * G * M * 2 * F * K
+            ms = time_graph(lambda: fused(ga, gw), 10, torch)
+            extras["moe_up_swiglu_fused_G8_M2048_F1024_K2048_tflops"] = fl / (ms * 1e-3) / 1e12
+            ms2 = time_graph(two_kernels, 10, torch)
+            extras["moe_up_swiglu_two_kernels_tflops"] = fl / (ms2 * 1e-3) / 1e12
+            del ga, gw
         except Exception as exc:  # noqa: BLE001 - context only
             extras["grouped_error"] = str(exc)[:200]
         try:

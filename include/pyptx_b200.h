@@ -94,6 +94,14 @@ extern "C" {
  *            -> O[BH,M_q,d] f32 (or bf16)                                         */
 #define PB200_K_FLASH_ATTN     8
 
+/* Fused MoE up-projection: out[g] = silu(A[g] W_gate[g]^T) * (A[g] W_up[g]^T).  The two products it
+ * fuses are build_grouped_gemm (examples/blackwell/grouped_gemm.py:61-289) followed by
+ * build_fused_silu_mul (examples/blackwell/swiglu.py:32); the reference has no fused entry point.
+ *   dims = {G, M, F, K}      flags: PB200_F_OUT_BF16
+ *   buffers: A[G*M,K] bf16, W_T[G*2F,K] bf16 (per expert: F gate rows, then F up rows)
+ *            -> out[G*M,F] f32 (or bf16)                                            */
+#define PB200_K_GROUPED_GEMM_SWIGLU 9
+
 /* ---- create-time flags -------------------------------------------------- */
 #define PB200_F_OUT_BF16       (1ull << 0)  /* round the output to bf16            */
 #define PB200_F_CAUSAL         (1ull << 1)  /* attention: lower-triangular mask    */

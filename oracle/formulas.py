@@ -55,6 +55,15 @@ def grouped_gemm_ref(a2: torch.Tensor, b_t2: torch.Tensor, G: int) -> torch.Tens
     return torch.einsum("gmk,gkn->gmn", a3, b3).reshape(G * m, n)
 
 
+def grouped_gemm_swiglu_ref(a2: torch.Tensor, w_t2: torch.Tensor, G: int) -> torch.Tensor:
+    """The two reference ops composed: grouped GEMM (examples/blackwell/grouped_gemm.py:306) then
+    ``F.silu(gate) * up`` (examples/blackwell/swiglu.py:66).  ``w_t2[G*2F, K]`` holds, per expert,
+    F gate rows followed by F up rows; returns ``[G*M, F]`` in fp32."""
+    c = grouped_gemm_ref(a2, w_t2, G)                 # [G*M, 2F]
+    f = c.shape[1] // 2
+    return torch.nn.functional.silu(c[:, :f]) * c[:, f:]
+
+
 def attention_ref(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool = False,
                   sm_scale: float | None = None) -> torch.Tensor:
     """``softmax(q k^T * scale) v`` in fp32 per leading index

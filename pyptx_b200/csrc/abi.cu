@@ -43,7 +43,8 @@ bool is_row(int32_t k) {
     return k == PB200_K_RMS_NORM || k == PB200_K_LAYER_NORM || k == PB200_K_SWIGLU || k == PB200_K_SOFTMAX;
 }
 bool is_gemm(int32_t k) {
-    return k == PB200_K_GEMM_1SM || k == PB200_K_GEMM_2SM || k == PB200_K_GROUPED_GEMM;
+    return k == PB200_K_GEMM_1SM || k == PB200_K_GEMM_2SM || k == PB200_K_GROUPED_GEMM ||
+           k == PB200_K_GROUPED_GEMM_SWIGLU;
 }
 
 }  // namespace

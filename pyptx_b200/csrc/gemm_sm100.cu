@@ -64,6 +64,7 @@ struct GemmShape {
     int rows_per_group_b;   // N  (row offset of group g in B_T is g*N)
     int band;               // M-tiles per raster band
     int n_total;            // leading dimension of D (elements)
+    int up_row_off;         // EPI 1: row offset of an expert's "up" weights inside its block of B_T (= F)
 };
 
 template <int BN, int CTA_GROUP>
@@ -96,7 +97,10 @@ __device__ __forceinline__ void tile_coords(const GemmShape& s, int t, int& g, i
     tm = m0 + (r - tn * width);
 }
 
-template <int BN, int CTA_GROUP, typename OutT, bool DIRECT>
+// EPI = 0: D = accumulator.  EPI = 1 (grouped, 1-SM): the 256 accumulator columns of a tile are
+// 128 "gate" columns followed by the matching 128 "up" columns of one expert, and the kernel
+// writes silu(gate) * up (128 columns) -- the MoE up-projection with its activation fused.
+template <int BN, int CTA_GROUP, typename OutT, bool DIRECT, int EPI = 0>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const __grid_constant__ CUtensorMap tmap_b,
@@ -105,7 +109,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     using Plan = SmemPlan<BN, CTA_GROUP>;
     constexpr int kStages = Plan::kStages;
     constexpr int kChunkCols = 128 / (int)sizeof(OutT);     // columns per 128-byte store row
-    constexpr int kChunks = BN / kChunkCols;
+    constexpr int kOutCols = EPI == 1 ? BN / 2 : BN;        // output columns per tile
+    constexpr int kChunks = kOutCols / kChunkCols;
+    static_assert(EPI == 0 || (BN == 256 && CTA_GROUP == 1 && !DIRECT), "the fused SwiGLU epilogue is a 1-SM, 256-column, TMA-store variant");
     constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
     constexpr uint32_t kIdesc = make_idesc_f16(BM * CTA_GROUP, BN);
 
@@ -170,7 +176,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 int g, tm, tn;
                 tile_coords(shape, t, g, tm, tn);
                 const int row_a = g * shape.rows_per_group_a + (tm * CTA_GROUP + (int)cta_rank) * BM;
-                const int row_b = g * shape.rows_per_group_b + tn * BN + (int)cta_rank * Plan::kBRows;
+                const int row_b = EPI == 1 ? g * shape.rows_per_group_b + tn * (BN / 2)
+                                           : g * shape.rows_per_group_b + tn * BN + (int)cta_rank * Plan::kBRows;
                 for (int kt = 0; kt < shape.k_tiles; ++kt) {
                     if (!(ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, ctx, 1))) break;
                     const uint32_t dst_a = s_a + stage * Plan::kABytes;
@@ -178,7 +185,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     if (CTA_GROUP == 1) {
                         mbar_arrive_expect_tx(bar_full + 8 * stage, Plan::kTxBytes);
                         tma_load_2d(dst_a, &tmap_a, bar_full + 8 * stage, kt * BK, row_a);
-                        tma_load_2d(dst_b, &tmap_b, bar_full + 8 * stage, kt * BK, row_b);
+                        if (EPI == 1) {
+                            // 128 gate rows, then the 128 up rows of the same feature block
+                            tma_load_2d(dst_b, &tmap_b, bar_full + 8 * stage, kt * BK, row_b);
+                            tma_load_2d(dst_b + (BN / 2) * BK * 2, &tmap_b, bar_full + 8 * stage, kt * BK, row_b + shape.up_row_off);
+                        } else {
+                            tma_load_2d(dst_b, &tmap_b, bar_full + 8 * stage, kt * BK, row_b);
+                        }
                     } else {
                         if (is_leader) mbar_arrive_expect_tx(bar_full + 8 * stage, Plan::kTxBytes);
                         tma_load_2d_pair(dst_a, &tmap_a, full_leader + 8 * stage, kt * BK, row_a);
@@ -249,7 +262,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const int buf = local & 1;
             const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
             const int row0 = g * shape.rows_per_group_a + (tm * CTA_GROUP + (int)cta_rank) * BM + q * 32;
-            const int col0 = tn * BN;
+            const int col0 = tn * kOutCols;
             ok = mbar_wait(bar_tfull + 8 * buf, acc_phase, ctx, 4);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
@@ -258,7 +271,32 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll 1
             for (int c = 0; c < kChunks; ++c) {
                 uint32_t v[32];
-                if (sizeof(OutT) == 4) {
+                if (EPI == 1) {
+                    // silu(gate) * up on kChunkCols columns: gate at column x, up at column 128 + x
+#pragma unroll
+                    for (int h = 0; h < kChunkCols / 32; ++h) {
+                        uint32_t gt[32], up[32];
+                        tmem_ld_32x32b_x32(t_row + (uint32_t)(c * kChunkCols + h * 32), gt);
+                        tmem_ld_32x32b_x32(t_row + (uint32_t)(BN / 2 + c * kChunkCols + h * 32), up);
+                        tmem_ld_wait();
+                        if (sizeof(OutT) == 4) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                const float gg = __uint_as_float(gt[i]);
+                                v[i] = __float_as_uint(__fdividef(gg, 1.0f + __expf(-gg)) * __uint_as_float(up[i]));
+                            }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                const float g0 = __uint_as_float(gt[2 * i]), g1 = __uint_as_float(gt[2 * i + 1]);
+                                __nv_bfloat162 pk = __floats2bfloat162_rn(
+                                    __fdividef(g0, 1.0f + __expf(-g0)) * __uint_as_float(up[2 * i]),
+                                    __fdividef(g1, 1.0f + __expf(-g1)) * __uint_as_float(up[2 * i + 1]));
+                                v[h * 16 + i] = *reinterpret_cast<uint32_t*>(&pk);
+                            }
+                        }
+                    }
+                } else if (sizeof(OutT) == 4) {
                     tmem_ld_32x32b_x32(t_row + (uint32_t)(c * 32), v);
                     tmem_ld_wait();
                 } else {
@@ -331,10 +369,12 @@ int pick_bn(int64_t n) {
     return 0;
 }
 
-template <int BN, int CTA_GROUP, typename OutT, bool DIRECT>
+bool is_grouped(int32_t kid) { return kid == PB200_K_GROUPED_GEMM || kid == PB200_K_GROUPED_GEMM_SWIGLU; }
+
+template <int BN, int CTA_GROUP, typename OutT, bool DIRECT, int EPI = 0>
 int launch_variant(const Record& r, cudaStream_t stream, void** p, const GemmShape& shape, char* err) {
     using Plan = SmemPlan<BN, CTA_GROUP>;
-    auto kernel = gemm_kernel<BN, CTA_GROUP, OutT, DIRECT>;
+    auto kernel = gemm_kernel<BN, CTA_GROUP, OutT, DIRECT, EPI>;
     static std::atomic<uint64_t> attr_set{0};   // bit per device
     int dev = 0;
     cudaGetDevice(&dev);
@@ -343,8 +383,11 @@ int launch_variant(const Record& r, cudaStream_t stream, void** p, const GemmSha
         if (e != cudaSuccess) { set_err(err, "cudaFuncSetAttribute(smem=%d): %s", Plan::kTotal, cudaGetErrorString(e)); return PB200_ERR_LAUNCH; }
         attr_set.fetch_or(1ull << (dev & 63), std::memory_order_relaxed);
     }
-    const int64_t G = r.kernel_id == PB200_K_GROUPED_GEMM ? r.dims[0] : 1;
+    const int64_t G = is_grouped(r.kernel_id) ? r.dims[0] : 1;
     const int64_t M = r.dims[r.n_dims - 3], N = r.dims[r.n_dims - 2], K = r.dims[r.n_dims - 1];
+    // EPI 1: dims carry F; B_T holds 2F rows per expert (gate rows, then up rows), D has F columns.
+    const int64_t b_rows = EPI == 1 ? 2 * N : N;
+    const uint32_t b_box_rows = EPI == 1 ? (uint32_t)(BN / 2) : (uint32_t)Plan::kBRows;
     CUtensorMap ta, tb, td;
     {
         uint64_t dims[2] = {(uint64_t)K, (uint64_t)(G * M)};
@@ -354,9 +397,9 @@ int launch_variant(const Record& r, cudaStream_t stream, void** p, const GemmSha
         if (rc) return rc;
     }
     {
-        uint64_t dims[2] = {(uint64_t)K, (uint64_t)(G * N)};
+        uint64_t dims[2] = {(uint64_t)K, (uint64_t)(G * b_rows)};
         uint64_t str[1] = {(uint64_t)K * 2};
-        uint32_t box[2] = {BK, (uint32_t)Plan::kBRows};
+        uint32_t box[2] = {BK, b_box_rows};
         int rc = make_tensor_map(&tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p[1], dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, err);
         if (rc) return rc;
     }
@@ -393,15 +436,17 @@ int launch_variant(const Record& r, cudaStream_t stream, void** p, const GemmSha
 }
 
 GemmShape make_shape(const Record& r, int bn, int cta_group) {
-    const int64_t G = r.kernel_id == PB200_K_GROUPED_GEMM ? r.dims[0] : 1;
+    const int64_t G = is_grouped(r.kernel_id) ? r.dims[0] : 1;
     const int64_t M = r.dims[r.n_dims - 3], N = r.dims[r.n_dims - 2], K = r.dims[r.n_dims - 1];
+    const bool swiglu = r.kernel_id == PB200_K_GROUPED_GEMM_SWIGLU;
     GemmShape s;
     s.tiles_m = (int)(M / (BM * cta_group));
-    s.tiles_n = (int)(N / bn);
+    s.tiles_n = swiglu ? (int)(N / 128) : (int)(N / bn);
     s.k_tiles = (int)(K / BK);
     s.groups = (int)G;
     s.rows_per_group_a = (int)M;
-    s.rows_per_group_b = (int)N;
+    s.rows_per_group_b = swiglu ? (int)(2 * N) : (int)N;
+    s.up_row_off = swiglu ? (int)N : 0;
     int band = (int)r.dims[7];            // stored by plan_gemm
     s.band = band < 1 ? 1 : (band > s.tiles_m ? s.tiles_m : band);
     s.n_total = (int)N;
@@ -412,7 +457,8 @@ GemmShape make_shape(const Record& r, int bn, int cta_group) {
 
 // dims: {M,N,K} (+ optional band) for the dense kernels, {G,M,N,K} (+ optional band) for grouped.
 int plan_gemm(Record& r, char* err) {
-    const bool grouped = r.kernel_id == PB200_K_GROUPED_GEMM;
+    const bool grouped = is_grouped(r.kernel_id);
+    const bool swiglu = r.kernel_id == PB200_K_GROUPED_GEMM_SWIGLU;
     const int need = grouped ? 4 : 3;
     if (r.n_dims != need && r.n_dims != need + 1) {
         set_err(err, "gemm kernel %d needs %d dims (+1 optional raster band), got %d", r.kernel_id, need, r.n_dims);
@@ -428,13 +474,14 @@ int plan_gemm(Record& r, char* err) {
     if (G < 1 || M < 1 || N < 1 || K < 1) { set_err(err, "G, M, N, K must be positive"); return PB200_ERR_BAD_SHAPE; }
     if (M % (BM * cta_group) != 0) { set_err(err, "M=%lld must be divisible by %d", (long long)M, BM * cta_group); return PB200_ERR_BAD_SHAPE; }
     if (K % BK != 0) { set_err(err, "K=%lld must be divisible by %d", (long long)K, BK); return PB200_ERR_BAD_SHAPE; }
-    const int bn = pick_bn(N);
+    if (swiglu && N % 128 != 0) { set_err(err, "F=%lld must be divisible by 128", (long long)N); return PB200_ERR_BAD_SHAPE; }
+    const int bn = swiglu ? 256 : pick_bn(N);
     if (bn == 0 || (!grouped && bn != 256)) {
         set_err(err, "N=%lld must be divisible by %d", (long long)N, grouped ? 64 : 256);
         return PB200_ERR_BAD_SHAPE;
     }
     if (G * M > 0x7fffffffLL || G * N > 0x7fffffffLL || K > 0x7fffffffLL) { set_err(err, "extent exceeds 2^31-1"); return PB200_ERR_BAD_SHAPE; }
-    const int64_t tiles = G * (M / (BM * cta_group)) * (N / bn);
+    const int64_t tiles = G * (M / (BM * cta_group)) * (swiglu ? N / 128 : N / bn);
     int64_t units = sm_count() / cta_group;
     if (units > tiles) units = tiles;
     pb200_geometry& g = r.geom;
@@ -449,7 +496,8 @@ int plan_gemm(Record& r, char* err) {
 
 int launch_gemm(const Record& r, cudaStream_t stream, void** p, char* err) {
     const int64_t N = r.dims[r.n_dims - 2];
-    const int bn = pick_bn(N);
+    const bool swiglu = r.kernel_id == PB200_K_GROUPED_GEMM_SWIGLU;
+    const int bn = swiglu ? 256 : pick_bn(N);
     const int cta_group = r.kernel_id == PB200_K_GEMM_2SM ? 2 : 1;
     const bool bf16_out = (r.flags & PB200_F_OUT_BF16) != 0;
     const bool direct = (r.flags & kDebugDirectStore) != 0;
@@ -460,6 +508,9 @@ int launch_gemm(const Record& r, cudaStream_t stream, void** p, char* err) {
         if ((int64_t)rr.geom.grid[0] > units * cta_group) rr.geom.grid[0] = (uint32_t)(units * cta_group);
     }
     GemmShape shape = make_shape(rr, bn, cta_group);
+    if (swiglu)
+        return bf16_out ? launch_variant<256, 1, __nv_bfloat16, false, 1>(rr, stream, p, shape, err)
+                        : launch_variant<256, 1, float, false, 1>(rr, stream, p, shape, err);
 #define PB200_GEMM_CASE(BN_, CG_)                                                                       \
     if (bn == BN_ && cta_group == CG_) {                                                                \
         if (bf16_out) return direct ? launch_variant<BN_, CG_, __nv_bfloat16, true>(rr, stream, p, shape, err)  \

@@ -24,6 +24,8 @@
 // taken over registers) instead of E[x^2]-mean^2.
 #include "common.cuh"
 
+#include <cuda_bf16.h>
+
 namespace pb200 {
 namespace {
 
@@ -38,6 +40,19 @@ __device__ __forceinline__ float4 ld_stream(const float4* p) {
 __device__ __forceinline__ void st_stream(float4* p, const float4& v) {
     asm volatile("st.global.cs.v4.f32 [%0], {%1,%2,%3,%4};"
                  :: "l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+
+// Four results to element index 4*idx4 of an f32 or bf16 array (bf16 = the fused output cast).
+template <typename OutT>
+__device__ __forceinline__ void store4(void* base, size_t idx4, const float4& v) {
+    if (sizeof(OutT) == 4) {
+        st_stream(reinterpret_cast<float4*>(base) + idx4, v);
+    } else {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+        asm volatile("st.global.cs.v2.b32 [%0], {%1, %2};"
+                     :: "l"(reinterpret_cast<uint2*>(base) + idx4), "r"(*reinterpret_cast<uint32_t*>(&lo)),
+                        "r"(*reinterpret_cast<uint32_t*>(&hi)) : "memory");
+    }
 }
 
 constexpr float kLog2e = 1.4426950408889634f;
@@ -78,15 +93,15 @@ __device__ __forceinline__ float block_reduce(float v, float* slot) {
 // ---------------------------------------------------------------------------
 // RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w
 // ---------------------------------------------------------------------------
-template <int THREADS, int VPT>
+template <int THREADS, int VPT, typename OutT>
 __global__ void __launch_bounds__(THREADS)
 rms_norm_kernel(const float4* __restrict__ x, const float4* __restrict__ w,
-                float4* __restrict__ y, int rows, int n4, float inv_n, float eps) {
+                void* __restrict__ y, int rows, int n4, float inv_n, float eps) {
     __shared__ float red[2][kWarp];
     int flip = 0;
     for (int row = blockIdx.x; row < rows; row += gridDim.x) {
         const float4* xr = x + (size_t)row * n4;
-        float4* yr = y + (size_t)row * n4;
+        const size_t row4 = (size_t)row * n4;
         float4 v[VPT];
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
@@ -110,7 +125,7 @@ rms_norm_kernel(const float4* __restrict__ x, const float4* __restrict__ w,
                 o.y = v[i].y * rstd * g.y;
                 o.z = v[i].z * rstd * g.z;
                 o.w = v[i].w * rstd * g.w;
-                st_stream(yr + idx, o);
+                store4<OutT>(y, row4 + idx, o);
             }
         }
     }
@@ -119,15 +134,15 @@ rms_norm_kernel(const float4* __restrict__ x, const float4* __restrict__ w,
 // ---------------------------------------------------------------------------
 // LayerNorm: y = (x - mean) * rsqrt(var + eps) * w + b, var over registers
 // ---------------------------------------------------------------------------
-template <int THREADS, int VPT>
+template <int THREADS, int VPT, typename OutT>
 __global__ void __launch_bounds__(THREADS)
 layer_norm_kernel(const float4* __restrict__ x, const float4* __restrict__ w,
-                  const float4* __restrict__ b, float4* __restrict__ y,
+                  const float4* __restrict__ b, void* __restrict__ y,
                   int rows, int n4, float inv_n, float eps) {
     __shared__ float red[2][kWarp];
     for (int row = blockIdx.x; row < rows; row += gridDim.x) {
         const float4* xr = x + (size_t)row * n4;
-        float4* yr = y + (size_t)row * n4;
+        const size_t row4 = (size_t)row * n4;
         float4 v[VPT];
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
@@ -160,7 +175,7 @@ layer_norm_kernel(const float4* __restrict__ x, const float4* __restrict__ w,
                 o.y = (v[i].y - mean) * rstd * g.y + c.y;
                 o.z = (v[i].z - mean) * rstd * g.z + c.z;
                 o.w = (v[i].w - mean) * rstd * g.w + c.w;
-                st_stream(yr + idx, o);
+                store4<OutT>(y, row4 + idx, o);
             }
         }
     }
@@ -169,13 +184,13 @@ layer_norm_kernel(const float4* __restrict__ x, const float4* __restrict__ w,
 // ---------------------------------------------------------------------------
 // Softmax: y = exp(x - max) / sum(exp(x - max))
 // ---------------------------------------------------------------------------
-template <int THREADS, int VPT>
+template <int THREADS, int VPT, typename OutT>
 __global__ void __launch_bounds__(THREADS)
-softmax_kernel(const float4* __restrict__ x, float4* __restrict__ y, int rows, int n4) {
+softmax_kernel(const float4* __restrict__ x, void* __restrict__ y, int rows, int n4) {
     __shared__ float red[2][kWarp];
     for (int row = blockIdx.x; row < rows; row += gridDim.x) {
         const float4* xr = x + (size_t)row * n4;
-        float4* yr = y + (size_t)row * n4;
+        const size_t row4 = (size_t)row * n4;
         float4 v[VPT];
         const float ninf = -INFINITY;
 #pragma unroll
@@ -210,7 +225,7 @@ softmax_kernel(const float4* __restrict__ x, float4* __restrict__ y, int rows, i
                 o.y = v[i].y * inv;
                 o.z = v[i].z * inv;
                 o.w = v[i].w * inv;
-                st_stream(yr + idx, o);
+                store4<OutT>(y, row4 + idx, o);
             }
         }
     }
@@ -221,16 +236,16 @@ softmax_kernel(const float4* __restrict__ x, float4* __restrict__ y, int rows, i
 // The second and third pass re-read the row, which a 126 MB L2 serves.
 // MODE 0 = RMSNorm, 1 = LayerNorm, 2 = softmax.
 // ---------------------------------------------------------------------------
-template <int MODE>
+template <int MODE, typename OutT>
 __global__ void __launch_bounds__(1024)
 long_row_kernel(const float4* __restrict__ x, const float4* __restrict__ w,
-                const float4* __restrict__ b, float4* __restrict__ y,
+                const float4* __restrict__ b, void* __restrict__ y,
                 int rows, int n4, float inv_n, float eps) {
     constexpr int THREADS = 1024;
     __shared__ float red[2][kWarp];
     for (int row = blockIdx.x; row < rows; row += gridDim.x) {
         const float4* xr = x + (size_t)row * n4;
-        float4* yr = y + (size_t)row * n4;
+        const size_t row4 = (size_t)row * n4;
         float a = MODE == 2 ? -INFINITY : 0.f;
         for (int idx = threadIdx.x; idx < n4; idx += THREADS) {
             float4 t = xr[idx];
@@ -272,7 +287,7 @@ long_row_kernel(const float4* __restrict__ x, const float4* __restrict__ w,
                 o.x = expf(t.x - first) / second; o.y = expf(t.y - first) / second;
                 o.z = expf(t.z - first) / second; o.w = expf(t.w - first) / second;
             }
-            st_stream(yr + idx, o);
+            store4<OutT>(y, row4 + idx, o);
         }
         __syncthreads();  // red[] is reused by the next row
     }
@@ -286,10 +301,10 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
     return g / (1.0f + expf(-g)) * u;
 }
 
-template <int THREADS, int UNROLL>
+template <int THREADS, int UNROLL, typename OutT>
 __global__ void __launch_bounds__(THREADS)
 swiglu_kernel(const float4* __restrict__ gate, const float4* __restrict__ up,
-              float4* __restrict__ out, size_t total4) {
+              void* __restrict__ out, size_t total4) {
     const size_t tile = (size_t)THREADS * UNROLL;
     for (size_t base = (size_t)blockIdx.x * tile; base < total4; base += (size_t)gridDim.x * tile) {
         float4 g[UNROLL], u[UNROLL];
@@ -307,7 +322,7 @@ swiglu_kernel(const float4* __restrict__ gate, const float4* __restrict__ up,
                 o.y = silu_mul(g[i].y, u[i].y);
                 o.z = silu_mul(g[i].z, u[i].z);
                 o.w = silu_mul(g[i].w, u[i].w);
-                st_stream(out + idx, o);
+                store4<OutT>(out, idx, o);
             }
         }
     }
@@ -337,17 +352,38 @@ RowConfig pick_row_config(int64_t n4, int threads = 0) {
     return {1024, 0};  // long-row kernel
 }
 
-template <int THREADS, int VPT>
-void launch_one(int kid, dim3 grid, cudaStream_t s, void** p, int rows, int n4, float inv_n, float eps) {
+template <int THREADS, int VPT, typename OutT>
+void launch_typed(int kid, dim3 grid, cudaStream_t s, void** p, int rows, int n4, float inv_n, float eps) {
     if (kid == PB200_K_RMS_NORM)
-        rms_norm_kernel<THREADS, VPT><<<grid, THREADS, 0, s>>>(
-            (const float4*)p[0], (const float4*)p[1], (float4*)p[2], rows, n4, inv_n, eps);
+        rms_norm_kernel<THREADS, VPT, OutT><<<grid, THREADS, 0, s>>>(
+            (const float4*)p[0], (const float4*)p[1], p[2], rows, n4, inv_n, eps);
     else if (kid == PB200_K_LAYER_NORM)
-        layer_norm_kernel<THREADS, VPT><<<grid, THREADS, 0, s>>>(
-            (const float4*)p[0], (const float4*)p[1], (const float4*)p[2], (float4*)p[3], rows, n4, inv_n, eps);
+        layer_norm_kernel<THREADS, VPT, OutT><<<grid, THREADS, 0, s>>>(
+            (const float4*)p[0], (const float4*)p[1], (const float4*)p[2], p[3], rows, n4, inv_n, eps);
     else
-        softmax_kernel<THREADS, VPT><<<grid, THREADS, 0, s>>>(
-            (const float4*)p[0], (float4*)p[1], rows, n4);
+        softmax_kernel<THREADS, VPT, OutT><<<grid, THREADS, 0, s>>>((const float4*)p[0], p[1], rows, n4);
+}
+template <int THREADS, int VPT>
+void launch_one(int kid, bool bf16_out, dim3 grid, cudaStream_t s, void** p, int rows, int n4, float inv_n, float eps) {
+    if (bf16_out) launch_typed<THREADS, VPT, __nv_bfloat16>(kid, grid, s, p, rows, n4, inv_n, eps);
+    else launch_typed<THREADS, VPT, float>(kid, grid, s, p, rows, n4, inv_n, eps);
+}
+
+template <typename OutT>
+void launch_long(int kid, dim3 grid, cudaStream_t s, void** p, int rows, int n4, float inv_n, float eps) {
+    if (kid == PB200_K_RMS_NORM)
+        long_row_kernel<0, OutT><<<grid, 1024, 0, s>>>((const float4*)p[0], (const float4*)p[1], nullptr, p[2], rows, n4, inv_n, eps);
+    else if (kid == PB200_K_LAYER_NORM)
+        long_row_kernel<1, OutT><<<grid, 1024, 0, s>>>((const float4*)p[0], (const float4*)p[1], (const float4*)p[2], p[3], rows, n4, inv_n, eps);
+    else
+        long_row_kernel<2, OutT><<<grid, 1024, 0, s>>>((const float4*)p[0], nullptr, nullptr, p[1], rows, n4, inv_n, eps);
+}
+template <int UNROLL>
+void launch_swiglu(bool bf16_out, dim3 grid, cudaStream_t s, void** p, size_t total4) {
+    if (bf16_out)
+        swiglu_kernel<256, UNROLL, __nv_bfloat16><<<grid, 256, 0, s>>>((const float4*)p[0], (const float4*)p[1], p[2], total4);
+    else
+        swiglu_kernel<256, UNROLL, float><<<grid, 256, 0, s>>>((const float4*)p[0], (const float4*)p[1], p[2], total4);
 }
 
 constexpr int kSwigluThreads = 256;
@@ -395,22 +431,18 @@ int launch_row(const Record& r, cudaStream_t s, void** p, char* err) {
     const float inv_n = 1.0f / (float)n;
     const float eps = (float)r.fparams[0];
     dim3 grid(r.geom.grid[0]);
+    const bool bf16_out = (r.flags & PB200_F_OUT_BF16) != 0;
     if (r.kernel_id == PB200_K_SWIGLU) {
         const int tune = (int)r.dims[7];
-        if (tune == 4)
-            swiglu_kernel<kSwigluThreads, 4><<<grid, kSwigluThreads, 0, s>>>(
-                (const float4*)p[0], (const float4*)p[1], (float4*)p[2], (size_t)rows * n4);
-        else if (tune == 8)
-            swiglu_kernel<kSwigluThreads, 8><<<grid, kSwigluThreads, 0, s>>>(
-                (const float4*)p[0], (const float4*)p[1], (float4*)p[2], (size_t)rows * n4);
-        else
-            swiglu_kernel<kSwigluThreads, kSwigluUnroll><<<grid, kSwigluThreads, 0, s>>>(
-                (const float4*)p[0], (const float4*)p[1], (float4*)p[2], (size_t)rows * n4);
+        const size_t total4 = (size_t)rows * n4;
+        if (tune == 4) launch_swiglu<4>(bf16_out, grid, s, p, total4);
+        else if (tune == 8) launch_swiglu<8>(bf16_out, grid, s, p, total4);
+        else launch_swiglu<kSwigluUnroll>(bf16_out, grid, s, p, total4);
     } else {
         RowConfig c = pick_row_config(n4, (int)r.dims[7]);
         const int kid = r.kernel_id;
 #define PB200_ROW_CASE(T, V) \
-        if (c.threads == T && c.vpt == V) launch_one<T, V>(kid, grid, s, p, rows, n4, inv_n, eps); else
+        if (c.threads == T && c.vpt == V) launch_one<T, V>(kid, bf16_out, grid, s, p, rows, n4, inv_n, eps); else
         PB200_ROW_CASE(32, 1) PB200_ROW_CASE(32, 2) PB200_ROW_CASE(32, 4) PB200_ROW_CASE(64, 4)
         PB200_ROW_CASE(128, 4) PB200_ROW_CASE(128, 8) PB200_ROW_CASE(256, 8) PB200_ROW_CASE(512, 8)
         PB200_ROW_CASE(1024, 8)
@@ -419,15 +451,8 @@ int launch_row(const Record& r, cudaStream_t s, void** p, char* err) {
         PB200_ROW_CASE(512, 1) PB200_ROW_CASE(512, 2) PB200_ROW_CASE(512, 4) PB200_ROW_CASE(512, 16)
         PB200_ROW_CASE(1024, 1) PB200_ROW_CASE(1024, 2) PB200_ROW_CASE(1024, 4) PB200_ROW_CASE(1024, 16)
         {
-            if (kid == PB200_K_RMS_NORM)
-                long_row_kernel<0><<<grid, 1024, 0, s>>>((const float4*)p[0], (const float4*)p[1], nullptr,
-                                                        (float4*)p[2], rows, n4, inv_n, eps);
-            else if (kid == PB200_K_LAYER_NORM)
-                long_row_kernel<1><<<grid, 1024, 0, s>>>((const float4*)p[0], (const float4*)p[1],
-                                                        (const float4*)p[2], (float4*)p[3], rows, n4, inv_n, eps);
-            else
-                long_row_kernel<2><<<grid, 1024, 0, s>>>((const float4*)p[0], nullptr, nullptr,
-                                                        (float4*)p[1], rows, n4, inv_n, eps);
+            if (bf16_out) launch_long<__nv_bfloat16>(kid, grid, s, p, rows, n4, inv_n, eps);
+            else launch_long<float>(kid, grid, s, p, rows, n4, inv_n, eps);
         }
 #undef PB200_ROW_CASE
     }

@@ -7,7 +7,7 @@ transposed to K-major, :302-303), result ``C[G*M, N]`` f32.
 """
 from __future__ import annotations
 
-from ..._ids import F_OUT_BF16, K_GROUPED_GEMM
+from ..._ids import F_OUT_BF16, K_GROUPED_GEMM, K_GROUPED_GEMM_SWIGLU
 from ...kernel import NativeKernel
 from ...specs import Layout, Tile
 from ...types import PtxType, bf16, f32
@@ -40,6 +40,31 @@ def build_grouped_gemm(G: int, M: int, N: int, K: int, *, arch: str = "sm_100a",
         out_specs=(Tile(G * M, N, out_dtype, Layout.ROW),),
         flags=F_OUT_BF16 if out_dtype == bf16 else 0, arch=arch,
         meta={"block_n": bn},
+    )
+
+
+def build_grouped_gemm_swiglu(G: int, M: int, F: int, K: int, *, arch: str = "sm_100a",
+                              out_dtype: PtxType = f32) -> NativeKernel:
+    """MoE up-projection with its activation fused into the GEMM epilogue (an extension; the
+    reference runs ``build_grouped_gemm`` and then ``build_fused_silu_mul`` as two kernels).
+
+    Kernel ``k(A[G*M,K] bf16, W_T[G*2F,K] bf16) -> out[G*M,F]`` with, per expert ``g``,
+    ``out = silu(A[g] @ W_gate[g].T) * (A[g] @ W_up[g].T)``; ``W_T`` stacks each expert's ``F`` gate
+    rows followed by its ``F`` up rows.  The ``[G*M, 2F]`` intermediate never reaches HBM.
+    """
+    assert arch.startswith("sm_100"), "Blackwell grouped GEMM is only implemented for sm_100*"
+    assert G >= 1, "G must be at least 1"
+    assert M % BM == 0, f"M={M} must be divisible by {BM}"
+    assert F % 128 == 0, f"F={F} must be divisible by 128"
+    assert K % BK == 0, f"K={K} must be divisible by {BK}"
+    assert out_dtype in (f32, bf16), f"out_dtype must be f32 or bf16, got {out_dtype}"
+    return NativeKernel(
+        "grouped_gemm_swiglu_bw", K_GROUPED_GEMM_SWIGLU, (G, M, F, K),
+        in_specs=(Tile(G * M, K, bf16, Layout.TMA_128B, tma_box=(BM, BK)),
+                  Tile(G * 2 * F, K, bf16, Layout.TMA_128B, tma_box=(128, BK))),
+        out_specs=(Tile(G * M, F, out_dtype, Layout.ROW),),
+        flags=F_OUT_BF16 if out_dtype == bf16 else 0, arch=arch,
+        meta={"block_f": 128},
     )
 
 

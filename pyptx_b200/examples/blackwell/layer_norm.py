@@ -8,8 +8,8 @@ from __future__ import annotations
 from ..._ids import K_LAYER_NORM
 from ...kernel import NativeKernel
 from ...specs import Tile
-from ...types import f32
-from .rms_norm import _check_row_shape
+from ...types import PtxType, f32
+from .rms_norm import _check_row_shape, _out_flags
 
 
 def _pick_rows_per_cta(B: int) -> int:
@@ -22,7 +22,7 @@ def _pick_rows_per_cta(B: int) -> int:
 
 
 def build_layer_norm(B: int, N: int, *, eps: float = 1e-5, rows_per_cta: int | None = None,
-                     arch: str = "sm_100a") -> NativeKernel:
+                     arch: str = "sm_100a", out_dtype: PtxType = f32) -> NativeKernel:
     """Kernel ``k(x[B,N], w[N], b[N]) -> y[B,N]`` (all f32).
 
     ``rows_per_cta`` is accepted for compatibility and validated, but the native
@@ -35,8 +35,8 @@ def build_layer_norm(B: int, N: int, *, eps: float = 1e-5, rows_per_cta: int | N
     return NativeKernel(
         "layer_norm", K_LAYER_NORM, (B, N),
         in_specs=(Tile(B, N, f32), Tile(N, f32), Tile(N, f32)),
-        out_specs=(Tile(B, N, f32),),
-        fparams=(eps,), arch=arch, meta={"eps": eps, "rows_per_cta": rows_per_cta},
+        out_specs=(Tile(B, N, out_dtype),),
+        fparams=(eps,), flags=_out_flags(out_dtype), arch=arch, meta={"eps": eps, "rows_per_cta": rows_per_cta},
     )
 
 

@@ -5,10 +5,10 @@ Drop-in for the reference entry point ``build_rms_norm(B, N, *, eps=1e-6)``
 """
 from __future__ import annotations
 
-from ..._ids import K_RMS_NORM
+from ..._ids import F_OUT_BF16, K_RMS_NORM
 from ...kernel import NativeKernel
 from ...specs import Tile
-from ...types import f32
+from ...types import PtxType, bf16, f32
 
 
 def _check_row_shape(rows: int, cols: int, what: str) -> None:
@@ -16,14 +16,23 @@ def _check_row_shape(rows: int, cols: int, what: str) -> None:
     assert cols % 4 == 0, f"{what}: N={cols} must be divisible by 4 (128-bit vector access)"
 
 
-def build_rms_norm(B: int, N: int, *, eps: float = 1e-6, arch: str = "sm_100a") -> NativeKernel:
-    """Kernel ``k(x[B,N] f32, w[N] f32) -> y[B,N] f32`` specialised for (B, N)."""
+def _out_flags(out_dtype: PtxType) -> int:
+    assert out_dtype in (f32, bf16), f"out_dtype must be f32 or bf16, got {out_dtype}"
+    return F_OUT_BF16 if out_dtype == bf16 else 0
+
+
+def build_rms_norm(B: int, N: int, *, eps: float = 1e-6, arch: str = "sm_100a",
+                   out_dtype: PtxType = f32) -> NativeKernel:
+    """Kernel ``k(x[B,N] f32, w[N] f32) -> y[B,N]`` specialised for (B, N).
+
+    ``out_dtype=bf16`` (an extension) rounds the result in the kernel, which fuses the cast that
+    usually follows a normalisation and halves the bytes written."""
     _check_row_shape(B, N, "rms_norm")
     return NativeKernel(
         "rms_norm", K_RMS_NORM, (B, N),
         in_specs=(Tile(B, N, f32), Tile(N, f32)),
-        out_specs=(Tile(B, N, f32),),
-        fparams=(eps,), arch=arch, meta={"eps": eps},
+        out_specs=(Tile(B, N, out_dtype),),
+        fparams=(eps,), flags=_out_flags(out_dtype), arch=arch, meta={"eps": eps},
     )
 
 

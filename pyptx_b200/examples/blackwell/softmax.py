@@ -8,18 +8,18 @@ from __future__ import annotations
 from ..._ids import K_SOFTMAX
 from ...kernel import NativeKernel
 from ...specs import Tile
-from ...types import f32
-from .rms_norm import _check_row_shape
+from ...types import PtxType, f32
+from .rms_norm import _check_row_shape, _out_flags
 
 
-def build_softmax(B: int, N: int, *, arch: str = "sm_100a") -> NativeKernel:
+def build_softmax(B: int, N: int, *, arch: str = "sm_100a", out_dtype: PtxType = f32) -> NativeKernel:
     """Kernel ``k(x[B,N] f32) -> y[B,N] f32`` with ``y = softmax(x, -1)``."""
     _check_row_shape(B, N, "softmax")
     return NativeKernel(
         "softmax", K_SOFTMAX, (B, N),
         in_specs=(Tile(B, N, f32),),
-        out_specs=(Tile(B, N, f32),),
-        arch=arch,
+        out_specs=(Tile(B, N, out_dtype),),
+        flags=_out_flags(out_dtype), arch=arch,
     )
 
 

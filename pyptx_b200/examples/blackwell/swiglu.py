@@ -8,13 +8,13 @@ from __future__ import annotations
 from ..._ids import K_SWIGLU
 from ...kernel import NativeKernel
 from ...specs import Tile
-from ...types import f32
+from ...types import PtxType, f32
 from .layer_norm import _pick_rows_per_cta
-from .rms_norm import _check_row_shape
+from .rms_norm import _check_row_shape, _out_flags
 
 
 def build_fused_silu_mul(M: int, F: int, *, rows_per_cta: int | None = None,
-                         arch: str = "sm_100a") -> NativeKernel:
+                         arch: str = "sm_100a", out_dtype: PtxType = f32) -> NativeKernel:
     """Kernel ``k(gate[M,F], up[M,F]) -> out[M,F]`` (all f32).
 
     ``rows_per_cta`` is accepted for compatibility; the native kernel treats the
@@ -27,8 +27,8 @@ def build_fused_silu_mul(M: int, F: int, *, rows_per_cta: int | None = None,
     return NativeKernel(
         "fused_silu_mul", K_SWIGLU, (M, F),
         in_specs=(Tile(M, F, f32), Tile(M, F, f32)),
-        out_specs=(Tile(M, F, f32),),
-        arch=arch, meta={"rows_per_cta": rows_per_cta},
+        out_specs=(Tile(M, F, out_dtype),),
+        flags=_out_flags(out_dtype), arch=arch, meta={"rows_per_cta": rows_per_cta},
     )
 
 

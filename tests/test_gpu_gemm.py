@@ -12,7 +12,7 @@ import torch
 from oracle import formulas, inputs
 from pyptx_b200 import _ids
 from pyptx_b200.examples.blackwell.gemm_highperf_blackwell import build_gemm, build_gemm_2sm
-from pyptx_b200.examples.blackwell.grouped_gemm import build_grouped_gemm
+from pyptx_b200.examples.blackwell.grouped_gemm import build_grouped_gemm, build_grouped_gemm_swiglu
 from pyptx_b200.kernel import NativeKernel
 from pyptx_b200.types import bf16
 from tests.gpu_util import check_bf16_matmul
@@ -223,6 +223,26 @@ def test_grouped_experts_do_not_mix():
     out = k(a2.cuda(), bt.cuda()).cpu()
     assert torch.equal(out[:2 * M], base[:2 * M]) and torch.equal(out[3 * M:], base[3 * M:])
     assert torch.count_nonzero(out[2 * M:3 * M]) == 0
+
+
+@pytest.mark.parametrize("out", ["f32", "bf16"])
+@pytest.mark.parametrize("G,M,F,K", [(1, 128, 128, 64), (2, 256, 256, 128), (4, 512, 384, 320), (8, 2048, 128, 2048),
+                                     (3, 128, 1024, 64)])
+def test_grouped_gemm_with_fused_swiglu(G, M, F, K, out):
+    """silu(A Wg^T) * (A Wu^T) from one kernel equals the two reference ops composed."""
+    from pyptx_b200.types import f32
+    a, w = inputs.grouped_gemm_inputs(G, M, 2 * F, K)        # w: [G*2F, K], per expert gate rows then up rows
+    w = (w.float() * 4.0).to(torch.bfloat16)                  # spread the gate values over the sigmoid's bend
+    ref = formulas.grouped_gemm_swiglu_ref(a, w, G)
+    k = build_grouped_gemm_swiglu(G, M, F, K, out_dtype=bf16 if out == "bf16" else f32)
+    got = k(a.cuda(), w.cuda())
+    assert got.shape == (G * M, F) and got.dtype == (torch.bfloat16 if out == "bf16" else torch.float32)
+    check_bf16_matmul(got.cpu(), ref, 5e-3 if out == "bf16" else 1e-4)
+    # and against this library's own two-kernel path
+    from pyptx_b200.examples.blackwell.swiglu import build_fused_silu_mul
+    c = build_grouped_gemm(G, M, 2 * F, K)(a.cuda(), w.cuda())
+    two = build_fused_silu_mul(G * M, F)(c[:, :F].contiguous(), c[:, F:].contiguous())
+    check_bf16_matmul(got.float().cpu(), two.cpu(), 5e-3 if out == "bf16" else 1e-5)
 
 
 def test_no_device_wait_gave_up():

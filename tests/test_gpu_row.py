@@ -124,6 +124,27 @@ def test_full_size_softmax():
     check_f32(out.cpu(), formulas.softmax_ref(x))
 
 
+# ---- fused bf16 output (extension) --------------------------------------------------
+
+@pytest.mark.parametrize("B,N", [(16, 512), (5, 132), (64, 8192), (2, 70000)])
+def test_bf16_output_is_the_rounded_f32_result(B, N):
+    """out_dtype=bf16 gives exactly the round-to-nearest bf16 of the kernel's own f32 result."""
+    from pyptx_b200.types import bf16
+    x, w, b = inputs.layer_norm_inputs(B, N)
+    g, u = inputs.swiglu_inputs(B, N)
+    xc, wc, bc, gc, uc = _cuda(x, w, b, g, u)
+    pairs = [
+        (build_rms_norm(B, N), build_rms_norm(B, N, out_dtype=bf16), (xc, wc)),
+        (build_layer_norm(B, N), build_layer_norm(B, N, out_dtype=bf16), (xc, wc, bc)),
+        (build_fused_silu_mul(B, N), build_fused_silu_mul(B, N, out_dtype=bf16), (gc, uc)),
+        (build_softmax(B, N), build_softmax(B, N, out_dtype=bf16), (xc,)),
+    ]
+    for k32, k16, args in pairs:
+        y32, y16 = k32(*args), k16(*args)
+        assert y16.dtype == torch.bfloat16 and y16.shape == y32.shape
+        assert torch.equal(y16, y32.to(torch.bfloat16)), k32.__name__
+
+
 # ---- size-independent properties -------------------------------------------------
 
 def test_rms_norm_scale_invariance():

@@ -102,6 +102,15 @@ extern "C" {
  *            -> out[G*M,F] f32 (or bf16)                                            */
 #define PB200_K_GROUPED_GEMM_SWIGLU 9
 
+/* Grouped GEMM with per-expert row counts, the follow-up the reference names
+ * (examples/hopper/grouped_gemm.py:15-17) but does not ship.
+ *   dims = {G, M_total, N, K}   flags: PB200_F_OUT_BF16
+ *   buffers: A[M_total,K] bf16, B_T[G*N,K] bf16, offsets[G+1] int32 (device; offsets[0] = 0,
+ *            non-decreasing multiples of 128, offsets[G] <= M_total; expert e owns rows
+ *            [offsets[e], offsets[e+1])) -> C[M_total,N] f32 (or bf16); rows at or beyond
+ *            offsets[G] are not written                                              */
+#define PB200_K_GROUPED_GEMM_VARLEN 10
+
 /* ---- create-time flags -------------------------------------------------- */
 #define PB200_F_OUT_BF16       (1ull << 0)  /* round the output to bf16            */
 #define PB200_F_CAUSAL         (1ull << 1)  /* attention: lower-triangular mask    */

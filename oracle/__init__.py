@@ -17,7 +17,7 @@ outputs under ``tests/golden/``; ``tests/test_oracle.py`` checks every function
 here against those vectors and against the reference tests' known answers.
 """
 from .formulas import (  # noqa: F401
-    attention_ref, gemm_ref, grouped_gemm_ref, grouped_gemm_swiglu_ref, layer_norm_ref, rms_norm_ref,
+    attention_ref, gemm_ref, grouped_gemm_ref, grouped_gemm_swiglu_ref, grouped_gemm_varlen_ref, layer_norm_ref, rms_norm_ref,
     softmax_ref, swiglu_ref,
 )
 from .encodings import (  # noqa: F401

@@ -55,6 +55,19 @@ def grouped_gemm_ref(a2: torch.Tensor, b_t2: torch.Tensor, G: int) -> torch.Tens
     return torch.einsum("gmk,gkn->gmn", a3, b3).reshape(G * m, n)
 
 
+def grouped_gemm_varlen_ref(a: torch.Tensor, b_t2: torch.Tensor, offsets, n: int) -> torch.Tensor:
+    """Per-expert ``a[o_e:o_{e+1}].float() @ b_t2[e*n:(e+1)*n].float().T`` -- the grouped formula
+    (examples/blackwell/grouped_gemm.py:306) with the row ranges given by ``offsets``; rows at or
+    beyond ``offsets[-1]`` come back as NaN so that a test notices anything written there."""
+    out = torch.full((a.shape[0], n), float("nan"), dtype=torch.float32)
+    offs = [int(o) for o in offsets]
+    for e in range(len(offs) - 1):
+        lo, hi = offs[e], offs[e + 1]
+        if hi > lo:
+            out[lo:hi] = a[lo:hi].float() @ b_t2[e * n:(e + 1) * n].float().t()
+    return out
+
+
 def grouped_gemm_swiglu_ref(a2: torch.Tensor, w_t2: torch.Tensor, G: int) -> torch.Tensor:
     """The two reference ops composed: grouped GEMM (examples/blackwell/grouped_gemm.py:306) then
     ``F.silu(gate) * up`` (examples/blackwell/swiglu.py:66).  ``w_t2[G*2F, K]`` holds, per expert,

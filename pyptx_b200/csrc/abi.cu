@@ -44,7 +44,7 @@ bool is_row(int32_t k) {
 }
 bool is_gemm(int32_t k) {
     return k == PB200_K_GEMM_1SM || k == PB200_K_GEMM_2SM || k == PB200_K_GROUPED_GEMM ||
-           k == PB200_K_GROUPED_GEMM_SWIGLU;
+           k == PB200_K_GROUPED_GEMM_SWIGLU || k == PB200_K_GROUPED_GEMM_VARLEN;
 }
 
 }  // namespace

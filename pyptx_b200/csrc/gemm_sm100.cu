@@ -64,6 +64,7 @@ struct GemmShape {
     int rows_per_group_b;   // N  (row offset of group g in B_T is g*N)
     int band;               // M-tiles per raster band
     int n_total;            // leading dimension of D (elements)
+    int n_experts;          // variable-size grouped GEMM: number of experts (0 = fixed-size problem)
     int up_row_off;         // EPI 1: row offset of an expert's "up" weights inside its block of B_T (= F)
 };
 
@@ -105,7 +106,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const __grid_constant__ CUtensorMap tmap_b,
             const __grid_constant__ CUtensorMap tmap_d,
-            OutT* __restrict__ d_ptr, GemmShape shape, int* status, int kernel_id) {
+            OutT* __restrict__ d_ptr, GemmShape shape, int* status, int kernel_id,
+            const int* __restrict__ expert_offsets) {
     using Plan = SmemPlan<BN, CTA_GROUP>;
     constexpr int kStages = Plan::kStages;
     constexpr int kChunkCols = 128 / (int)sizeof(OutT);     // columns per 128-byte store row
@@ -137,7 +139,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const bool is_leader = cta_rank == 0;
     const int unit = CTA_GROUP == 2 ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;      // tile walker id
     const int n_units = CTA_GROUP == 2 ? (int)(gridDim.x >> 1) : (int)gridDim.x;
-    const int n_tiles = shape.groups * shape.tiles_m * shape.tiles_n;
+    // Variable-size grouped GEMM: A and D are one stack of row blocks, expert e owning rows
+    // [expert_offsets[e], expert_offsets[e+1]) (multiples of BM, so no tile straddles two experts);
+    // only the row blocks below expert_offsets[n_experts] exist, and only the B tile depends on e.
+    const int n_tiles = shape.n_experts > 0
+        ? (min(__ldg(expert_offsets + shape.n_experts), shape.tiles_m * BM) / BM) * shape.tiles_n
+        : shape.groups * shape.tiles_m * shape.tiles_n;
 
     WaitCtx ctx{status, abort_gen, kernel_id};
 
@@ -176,7 +183,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 int g, tm, tn;
                 tile_coords(shape, t, g, tm, tn);
                 const int row_a = g * shape.rows_per_group_a + (tm * CTA_GROUP + (int)cta_rank) * BM;
-                const int row_b = EPI == 1 ? g * shape.rows_per_group_b + tn * (BN / 2)
+                if (shape.n_experts > 0) {
+                    // which expert owns this row block (a handful of cached 4-byte loads per tile)
+                    while (g + 1 < shape.n_experts && __ldg(expert_offsets + g + 1) <= row_a) ++g;
+                }
+                const int row_b = shape.n_experts > 0 ? g * shape.rows_per_group_b + tn * BN : EPI == 1 ? g * shape.rows_per_group_b + tn * (BN / 2)
                                            : g * shape.rows_per_group_b + tn * BN + (int)cta_rank * Plan::kBRows;
                 for (int kt = 0; kt < shape.k_tiles; ++kt) {
                     if (!(ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, ctx, 1))) break;
@@ -369,7 +380,9 @@ int pick_bn(int64_t n) {
     return 0;
 }
 
-bool is_grouped(int32_t kid) { return kid == PB200_K_GROUPED_GEMM || kid == PB200_K_GROUPED_GEMM_SWIGLU; }
+bool is_grouped(int32_t kid) {
+    return kid == PB200_K_GROUPED_GEMM || kid == PB200_K_GROUPED_GEMM_SWIGLU || kid == PB200_K_GROUPED_GEMM_VARLEN;
+}
 
 template <int BN, int CTA_GROUP, typename OutT, bool DIRECT, int EPI = 0>
 int launch_variant(const Record& r, cudaStream_t stream, void** p, const GemmShape& shape, char* err) {
@@ -383,10 +396,13 @@ int launch_variant(const Record& r, cudaStream_t stream, void** p, const GemmSha
         if (e != cudaSuccess) { set_err(err, "cudaFuncSetAttribute(smem=%d): %s", Plan::kTotal, cudaGetErrorString(e)); return PB200_ERR_LAUNCH; }
         attr_set.fetch_or(1ull << (dev & 63), std::memory_order_relaxed);
     }
-    const int64_t G = is_grouped(r.kernel_id) ? r.dims[0] : 1;
+    const bool varlen = r.kernel_id == PB200_K_GROUPED_GEMM_VARLEN;
+    const int64_t G = is_grouped(r.kernel_id) && !varlen ? r.dims[0] : 1;     // varlen: M is already the stacked total
     const int64_t M = r.dims[r.n_dims - 3], N = r.dims[r.n_dims - 2], K = r.dims[r.n_dims - 1];
+    const int64_t n_experts = varlen ? r.dims[0] : 0;
+    void* out_ptr = p[varlen ? 3 : 2];
     // EPI 1: dims carry F; B_T holds 2F rows per expert (gate rows, then up rows), D has F columns.
-    const int64_t b_rows = EPI == 1 ? 2 * N : N;
+    const int64_t b_rows = EPI == 1 ? 2 * N : varlen ? n_experts * N : N;
     const uint32_t b_box_rows = EPI == 1 ? (uint32_t)(BN / 2) : (uint32_t)Plan::kBRows;
     CUtensorMap ta, tb, td;
     {
@@ -408,7 +424,7 @@ int launch_variant(const Record& r, cudaStream_t stream, void** p, const GemmSha
         uint64_t str[1] = {(uint64_t)N * sizeof(OutT)};
         uint32_t box[2] = {128 / sizeof(OutT), kStageRows};
         int rc = make_tensor_map(&td, sizeof(OutT) == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
-                                 2, p[2], dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, err);
+                                 2, out_ptr, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, err);
         if (rc) return rc;
     }
     cudaLaunchConfig_t cfg{};
@@ -423,10 +439,11 @@ int launch_variant(const Record& r, cudaStream_t stream, void** p, const GemmSha
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    OutT* d_ptr = (OutT*)p[2];
+    OutT* d_ptr = (OutT*)out_ptr;
+    const int* expert_offsets = varlen ? (const int*)p[2] : nullptr;
     int* status = device_status_ptr();
     int kid = r.kernel_id;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, td, d_ptr, shape, status, kid);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, td, d_ptr, shape, status, kid, expert_offsets);
     if (e != cudaSuccess) {
         set_err(err, "gemm launch failed (BN=%d cta_group=%d grid=%u smem=%d): %s", BN, CTA_GROUP, r.geom.grid[0],
                 Plan::kTotal, cudaGetErrorString(e));
@@ -436,10 +453,12 @@ int launch_variant(const Record& r, cudaStream_t stream, void** p, const GemmSha
 }
 
 GemmShape make_shape(const Record& r, int bn, int cta_group) {
-    const int64_t G = is_grouped(r.kernel_id) ? r.dims[0] : 1;
+    const bool varlen = r.kernel_id == PB200_K_GROUPED_GEMM_VARLEN;
+    const int64_t G = is_grouped(r.kernel_id) && !varlen ? r.dims[0] : 1;
     const int64_t M = r.dims[r.n_dims - 3], N = r.dims[r.n_dims - 2], K = r.dims[r.n_dims - 1];
     const bool swiglu = r.kernel_id == PB200_K_GROUPED_GEMM_SWIGLU;
     GemmShape s;
+    s.n_experts = varlen ? (int)r.dims[0] : 0;
     s.tiles_m = (int)(M / (BM * cta_group));
     s.tiles_n = swiglu ? (int)(N / 128) : (int)(N / bn);
     s.k_tiles = (int)(K / BK);
@@ -449,6 +468,7 @@ GemmShape make_shape(const Record& r, int bn, int cta_group) {
     s.up_row_off = swiglu ? (int)N : 0;
     int band = (int)r.dims[7];            // stored by plan_gemm
     s.band = band < 1 ? 1 : (band > s.tiles_m ? s.tiles_m : band);
+    if (varlen) s.band = 1;     // row blocks in order, so that the active ones are a prefix of the tile list
     s.n_total = (int)N;
     return s;
 }
@@ -468,7 +488,9 @@ int plan_gemm(Record& r, char* err) {
     if (r.n_dims == need + 1) { band = r.dims[need]; r.n_dims = need; }
     if (band < 1) { set_err(err, "raster band must be at least 1"); return PB200_ERR_BAD_SHAPE; }
     r.dims[7] = band;
-    const int64_t G = grouped ? r.dims[0] : 1;
+    const bool varlen = r.kernel_id == PB200_K_GROUPED_GEMM_VARLEN;
+    const int64_t G = grouped && !varlen ? r.dims[0] : 1;
+    if (varlen && (r.dims[0] < 1 || r.dims[0] > 65536)) { set_err(err, "expert count must be in [1, 65536]"); return PB200_ERR_BAD_SHAPE; }
     const int64_t M = r.dims[need - 3], N = r.dims[need - 2], K = r.dims[need - 1];
     const int cta_group = r.kernel_id == PB200_K_GEMM_2SM ? 2 : 1;
     if (G < 1 || M < 1 || N < 1 || K < 1) { set_err(err, "G, M, N, K must be positive"); return PB200_ERR_BAD_SHAPE; }
@@ -490,7 +512,7 @@ int plan_gemm(Record& r, char* err) {
     g.cluster[0] = (uint32_t)cta_group; g.cluster[1] = g.cluster[2] = 1;
     g.smem_bytes = bn == 256 ? (cta_group == 2 ? SmemPlan<256, 2>::kTotal : SmemPlan<256, 1>::kTotal)
                  : bn == 128 ? SmemPlan<128, 1>::kTotal : SmemPlan<64, 1>::kTotal;
-    g.n_inputs = 2; g.n_outputs = 1;
+    g.n_inputs = varlen ? 3 : 2; g.n_outputs = 1;
     return PB200_OK;
 }
 

@@ -7,10 +7,10 @@ transposed to K-major, :302-303), result ``C[G*M, N]`` f32.
 """
 from __future__ import annotations
 
-from ..._ids import F_OUT_BF16, K_GROUPED_GEMM, K_GROUPED_GEMM_SWIGLU
+from ..._ids import F_OUT_BF16, K_GROUPED_GEMM, K_GROUPED_GEMM_SWIGLU, K_GROUPED_GEMM_VARLEN
 from ...kernel import NativeKernel
 from ...specs import Layout, Tile
-from ...types import PtxType, bf16, f32
+from ...types import PtxType, bf16, f32, s32
 
 BM = 128
 BK = 64
@@ -65,6 +65,35 @@ def build_grouped_gemm_swiglu(G: int, M: int, F: int, K: int, *, arch: str = "sm
         out_specs=(Tile(G * M, F, out_dtype, Layout.ROW),),
         flags=F_OUT_BF16 if out_dtype == bf16 else 0, arch=arch,
         meta={"block_f": 128},
+    )
+
+
+def build_grouped_gemm_varlen(G: int, M_total: int, N: int, K: int, *, arch: str = "sm_100a",
+                              out_dtype: PtxType = f32) -> NativeKernel:
+    """Grouped GEMM with a different row count per expert -- the follow-up the reference names
+    (examples/hopper/grouped_gemm.py:15-17) but does not ship.
+
+    Kernel ``k(A[M_total,K] bf16, B_T[G*N,K] bf16, offsets[G+1] int32) -> C[M_total,N]``: expert ``e``
+    owns rows ``[offsets[e], offsets[e+1])`` of ``A`` and ``C`` and multiplies them by its own
+    ``B_T[e*N:(e+1)*N]``.  ``offsets`` lives on the device (it usually comes out of the router's
+    scan), starts at 0, is non-decreasing in multiples of 128 and ends at or below ``M_total``;
+    rows at or beyond ``offsets[G]`` are left unwritten.  ``M_total`` is the static capacity, so
+    one kernel object (and one CUDA graph) serves every routing outcome.
+    """
+    assert arch.startswith("sm_100"), "Blackwell grouped GEMM is only implemented for sm_100*"
+    assert G >= 1, "G must be at least 1"
+    assert M_total % BM == 0, f"M_total={M_total} must be divisible by {BM}"
+    assert K % BK == 0, f"K={K} must be divisible by {BK}"
+    bn = _pick_bn(N)
+    assert out_dtype in (f32, bf16), f"out_dtype must be f32 or bf16, got {out_dtype}"
+    return NativeKernel(
+        "grouped_gemm_varlen_bw", K_GROUPED_GEMM_VARLEN, (G, M_total, N, K),
+        in_specs=(Tile(M_total, K, bf16, Layout.TMA_128B, tma_box=(BM, BK)),
+                  Tile(G * N, K, bf16, Layout.TMA_128B, tma_box=(bn, BK)),
+                  Tile(G + 1, s32)),
+        out_specs=(Tile(M_total, N, out_dtype, Layout.ROW),),
+        flags=F_OUT_BF16 if out_dtype == bf16 else 0, arch=arch,
+        meta={"block_n": bn},
     )
 
 

@@ -12,7 +12,8 @@ import torch
 from oracle import formulas, inputs
 from pyptx_b200 import _ids
 from pyptx_b200.examples.blackwell.gemm_highperf_blackwell import build_gemm, build_gemm_2sm
-from pyptx_b200.examples.blackwell.grouped_gemm import build_grouped_gemm, build_grouped_gemm_swiglu
+from pyptx_b200.examples.blackwell.grouped_gemm import (build_grouped_gemm, build_grouped_gemm_swiglu,
+                                                         build_grouped_gemm_varlen)
 from pyptx_b200.kernel import NativeKernel
 from pyptx_b200.types import bf16
 from tests.gpu_util import check_bf16_matmul
@@ -243,6 +244,58 @@ def test_grouped_gemm_with_fused_swiglu(G, M, F, K, out):
     c = build_grouped_gemm(G, M, 2 * F, K)(a.cuda(), w.cuda())
     two = build_fused_silu_mul(G * M, F)(c[:, :F].contiguous(), c[:, F:].contiguous())
     check_bf16_matmul(got.float().cpu(), two.cpu(), 5e-3 if out == "bf16" else 1e-5)
+
+
+@pytest.mark.parametrize("counts,N,K", [
+    ([128], 64, 64),
+    ([256, 0, 384, 128], 256, 128),            # an expert with no tokens
+    ([0, 0, 512], 128, 320),
+    ([1024, 128, 2048, 256, 0, 640, 128, 896], 256, 512),
+    ([128] * 40, 512, 64),
+])
+@pytest.mark.parametrize("slack", [0, 384])
+def test_variable_size_grouped_gemm(counts, N, K, slack):
+    """Per-expert row counts from a device-side offsets array; capacity above the routed rows stays untouched."""
+    G = len(counts)
+    offs = [0]
+    for c in counts:
+        offs.append(offs[-1] + c)
+    M_total = offs[-1] + slack
+    g = torch.Generator().manual_seed(G * 1009 + M_total * 997 + N * 17 + K)
+    a = (torch.randn(M_total, K, generator=g) / K ** 0.5).to(torch.bfloat16)
+    bt = (torch.randn(G * N, K, generator=g) / K ** 0.5).to(torch.bfloat16)
+    ref = formulas.grouped_gemm_varlen_ref(a, bt, offs, N)
+    k = build_grouped_gemm_varlen(G, M_total, N, K)
+    offsets = torch.tensor(offs, dtype=torch.int32, device="cuda")
+    # pre-fill the output allocation pattern: run once, then check the untouched tail through a sentinel run
+    out = k(a.cuda(), bt.cuda(), offsets).cpu()
+    used = offs[-1]
+    check_bf16_matmul(out[:used], ref[:used], 1e-4)
+    # same kernel object, another routing outcome with the same capacity
+    if G >= 2 and counts[0] >= 256:
+        offs2 = list(offs)
+        offs2[1] -= 128                      # move one row block from expert 0 to expert 1
+        out2 = k(a.cuda(), bt.cuda(), torch.tensor(offs2, dtype=torch.int32, device="cuda")).cpu()
+        ref2 = formulas.grouped_gemm_varlen_ref(a, bt, offs2, N)
+        check_bf16_matmul(out2[:used], ref2[:used], 1e-4)
+
+
+def test_variable_size_grouped_gemm_leaves_capacity_rows_alone():
+    G, N, K = 2, 256, 64
+    offs = [0, 128, 256]
+    M_total = 512
+    a = torch.ones(M_total, K, dtype=torch.bfloat16)
+    bt = torch.ones(G * N, K, dtype=torch.bfloat16)
+    k = build_grouped_gemm_varlen(G, M_total, N, K)
+    offsets = torch.tensor(offs, dtype=torch.int32, device="cuda")
+    # torch.empty reuses the block freed by the sentinel tensor, so unwritten rows keep the sentinel
+    sentinel = torch.full((M_total, N), -7.0, device="cuda")
+    ptr = sentinel.data_ptr()
+    del sentinel
+    out = k(a.cuda(), bt.cuda(), offsets)
+    assert bool((out[:256] == float(K)).all())
+    if out.data_ptr() == ptr:
+        assert bool((out[256:] == -7.0).all())
 
 
 def test_no_device_wait_gave_up():

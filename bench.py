@@ -255,6 +255,31 @@ def row_kernel_table(torch, peaks, steps: int, warmup: int) -> dict:
         table[name] = {"ms": ms, "GB/s": gbs, "bytes": nbytes, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
                        "frac_of_8TBps": gbs / 8000.0, "timing": "cuda-graph replay, 6 rotating buffer sets",
                        "ms_eager_loop": ms_eager}
+    # backward halves (extension): 3*B*N*4 bytes for the norms, 5*M*F*4 for SwiGLU
+    try:
+        from pyptx_b200.examples.blackwell.backward import (build_fused_silu_mul_bwd, build_layer_norm_bwd,
+                                                            build_rms_norm_bwd, norm_bwd_bytes)
+        bwd_cases = {
+            "rms_norm_bwd": (build_rms_norm_bwd(B, N), lambda k, i: k(xs[i], w, us[i]), norm_bwd_bytes(B, N)),
+            "layer_norm_bwd": (build_layer_norm_bwd(B, N), lambda k, i: k(xs[i], w, us[i]), norm_bwd_bytes(B, N)),
+            "swiglu_bwd": (build_fused_silu_mul_bwd(B, N), lambda k, i: k(xs[i], us[i], xs[(i + 1) % SETS]), 5 * B * N * 4),
+        }
+        for name, (k, call, nbytes) in bwd_cases.items():
+            counter = [0]
+            outs = [None] * SETS
+
+            def fn():
+                i = counter[0] % SETS
+                outs[i] = call(k, i)
+                counter[0] += 1
+
+            ms = time_graph(fn, 24, torch)
+            gbs = nbytes / (ms * 1e-3) / 1e9
+            table[name] = {"ms": ms, "GB/s": gbs, "bytes": nbytes, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
+                           "timing": "cuda-graph replay, 6 rotating buffer sets"}
+            del outs
+    except Exception as exc:  # noqa: BLE001 - context only
+        table["backward_error"] = str(exc)[:200]
     # torch's own GPU kernels for the same formulas, same buffers, same method (what the
     # reference's kernel benchmark prints next to its kernels, bench_blackwell_kernels.py:61-62, 85-86, 108-109)
     F = torch.nn.functional
@@ -265,6 +290,8 @@ def row_kernel_table(torch, peaks, steps: int, warmup: int) -> dict:
         "softmax": lambda i: torch.softmax(xs[i], -1),
     }
     for name, ref in torch_refs.items():
+        if name not in table:
+            continue
         counter = [0]
         outs = [None] * SETS
 

@@ -111,6 +111,21 @@ extern "C" {
  *            offsets[G] are not written                                              */
 #define PB200_K_GROUPED_GEMM_VARLEN 10
 
+/* Backward halves of the row ops, for the reference's autograd hook differentiable_kernel
+ * (pyptx/torch_support.py:446-519); the reference ships no backward kernels of its own.
+ *   PB200_K_RMS_NORM_BWD    dims = {B, N}  fparams = {eps}
+ *       buffers: x[B,N], w[N], dy[B,N] f32 -> dx[B,N], dw[N] f32            + scratch
+ *   PB200_K_LAYER_NORM_BWD  dims = {B, N}  fparams = {eps}
+ *       buffers: x[B,N], w[N], dy[B,N] f32 -> dx[B,N], dw[N], db[N] f32     + scratch
+ *   PB200_K_SWIGLU_BWD      dims = {M, F}
+ *       buffers: gate[M,F], up[M,F], dout[M,F] f32 -> dgate[M,F], dup[M,F] f32
+ * "+ scratch": these kernels need pb200_geometry.scratch_bytes of device memory for partial
+ * column sums; the caller passes it as one extra pointer after the outputs (contents are
+ * overwritten, nothing has to be cleared).  N <= 16384.                                  */
+#define PB200_K_RMS_NORM_BWD   11
+#define PB200_K_LAYER_NORM_BWD 12
+#define PB200_K_SWIGLU_BWD     13
+
 /* ---- create-time flags -------------------------------------------------- */
 #define PB200_F_OUT_BF16       (1ull << 0)  /* round the output to bf16            */
 #define PB200_F_CAUSAL         (1ull << 1)  /* attention: lower-triangular mask    */
@@ -125,6 +140,7 @@ typedef struct pb200_geometry {
     uint32_t smem_bytes;
     uint32_t n_inputs;
     uint32_t n_outputs;
+    uint64_t scratch_bytes;   /* > 0: one scratch pointer of this size follows the outputs */
 } pb200_geometry;
 
 /* Registers a (kernel, static shape, options) record and returns a handle
@@ -139,7 +155,8 @@ PB200_API int64_t pb200_create(int32_t kernel_id,
 
 /* Launches the kernel behind `handle` on `stream` (a cudaStream_t / CUstream
  * passed as an integer).  `buffer_ptrs` holds n_buffers device pointers:
- * the inputs in spec order, then the outputs.
+ * the inputs in spec order, then the outputs, then (only for handles whose geometry reports
+ * scratch_bytes > 0) one scratch buffer of that size.
  * Replaces pyptx_shim_launch_raw (pyptx/_shim/pyptx_launch.cc:484-492);
  * same argument list, same return convention. */
 PB200_API int pb200_launch_raw(int64_t handle, uint64_t stream,

@@ -95,6 +95,33 @@ def attention_ref(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: 
     return torch.softmax(s, dim=-1) @ v
 
 
+def rms_norm_bwd_ref(x, w, dy, eps: float = 1e-6):
+    """(dx, dw) by autograd through the forward formula (float64 internally, returned as float32)."""
+    x64, w64 = x.double().requires_grad_(), w.double().requires_grad_()
+    y = x64 * torch.rsqrt((x64 * x64).mean(-1, keepdim=True) + eps) * w64
+    dx, dw = torch.autograd.grad(y, (x64, w64), dy.double())
+    return dx.float(), dw.float()
+
+
+def layer_norm_bwd_ref(x, w, dy, eps: float = 1e-5):
+    """(dx, dw, db) by autograd through the forward formula (float64 internally)."""
+    x64, w64 = x.double().requires_grad_(), w.double().requires_grad_()
+    b64 = torch.zeros_like(w64).requires_grad_()
+    mean = x64.mean(-1, keepdim=True)
+    var = ((x64 - mean) ** 2).mean(-1, keepdim=True)
+    y = (x64 - mean) * torch.rsqrt(var + eps) * w64 + b64
+    dx, dw, db = torch.autograd.grad(y, (x64, w64, b64), dy.double())
+    return dx.float(), dw.float(), db.float()
+
+
+def swiglu_bwd_ref(gate, up, dout):
+    """(dgate, dup) by autograd through ``F.silu(gate) * up`` (float64 internally)."""
+    g64, u64 = gate.double().requires_grad_(), up.double().requires_grad_()
+    y = torch.nn.functional.silu(g64) * u64
+    dg, du = torch.autograd.grad(y, (g64, u64), dout.double())
+    return dg.float(), du.float()
+
+
 def rel_fro(out: torch.Tensor, ref: torch.Tensor) -> float:
     """Relative Frobenius error ``|out-ref|_F / |ref|_F`` in float64."""
     o, r = out.double().cpu(), ref.double().cpu()

@@ -50,6 +50,7 @@ class Geometry(ctypes.Structure):
         ("smem_bytes", ctypes.c_uint32),
         ("n_inputs", ctypes.c_uint32),
         ("n_outputs", ctypes.c_uint32),
+        ("scratch_bytes", ctypes.c_uint64),
     ]
 
 

@@ -42,6 +42,9 @@ int current_device() {
 bool is_row(int32_t k) {
     return k == PB200_K_RMS_NORM || k == PB200_K_LAYER_NORM || k == PB200_K_SWIGLU || k == PB200_K_SOFTMAX;
 }
+bool is_row_bwd(int32_t k) {
+    return k == PB200_K_RMS_NORM_BWD || k == PB200_K_LAYER_NORM_BWD || k == PB200_K_SWIGLU_BWD;
+}
 bool is_gemm(int32_t k) {
     return k == PB200_K_GEMM_1SM || k == PB200_K_GEMM_2SM || k == PB200_K_GROUPED_GEMM ||
            k == PB200_K_GROUPED_GEMM_SWIGLU || k == PB200_K_GROUPED_GEMM_VARLEN;
@@ -127,6 +130,7 @@ PB200_API int64_t pb200_create(int32_t kernel_id, const int64_t* dims, size_t n_
     r.flags = flags;
     int rc;
     if (is_row(kernel_id)) rc = plan_row(r, err_out);
+    else if (is_row_bwd(kernel_id)) rc = plan_row_bwd(r, err_out);
     else if (is_gemm(kernel_id)) rc = plan_gemm(r, err_out);
     else if (kernel_id == PB200_K_FLASH_ATTN) rc = plan_attention(r, err_out);
     else { set_err(err_out, "unknown kernel id %d", kernel_id); return PB200_ERR_BAD_KERNEL; }
@@ -149,10 +153,10 @@ PB200_API int pb200_launch_raw(int64_t handle, uint64_t stream, void** buffer_pt
         }
         r = it->second;
     }
-    const size_t want = (size_t)r.geom.n_inputs + r.geom.n_outputs;
+    const size_t want = (size_t)r.geom.n_inputs + r.geom.n_outputs + (r.geom.scratch_bytes ? 1 : 0);
     if (n_buffers != want || !buffer_ptrs) {
-        set_err(err_out, "kernel %d takes %zu buffers (%u inputs + %u outputs), got %zu", r.kernel_id, want,
-                r.geom.n_inputs, r.geom.n_outputs, n_buffers);
+        set_err(err_out, "kernel %d takes %zu buffers (%u inputs + %u outputs%s), got %zu", r.kernel_id, want,
+                r.geom.n_inputs, r.geom.n_outputs, r.geom.scratch_bytes ? " + 1 scratch" : "", n_buffers);
         return PB200_ERR_ARG_COUNT;
     }
     for (size_t i = 0; i < n_buffers; ++i) {
@@ -164,6 +168,7 @@ PB200_API int pb200_launch_raw(int64_t handle, uint64_t stream, void** buffer_pt
     }
     cudaStream_t s = (cudaStream_t)(uintptr_t)stream;
     if (is_row(r.kernel_id)) return launch_row(r, s, buffer_ptrs, err_out);
+    if (is_row_bwd(r.kernel_id)) return launch_row_bwd(r, s, buffer_ptrs, err_out);
     if (is_gemm(r.kernel_id)) return launch_gemm(r, s, buffer_ptrs, err_out);
     return launch_attention(r, s, buffer_ptrs, err_out);
 }

@@ -42,6 +42,13 @@ int launch_row(const Record& r, cudaStream_t stream, void** ptrs, char* err);
 int plan_gemm(Record& r, char* err);
 int launch_gemm(const Record& r, cudaStream_t stream, void** ptrs, char* err);
 
+int plan_row_bwd(Record& r, char* err);
+int launch_row_bwd(const Record& r, cudaStream_t stream, void** ptrs, char* err);
+// Backward norm pass + fold of the partial column sums, with the scratch given explicitly.
+int enqueue_norm_bwd(int mode, int rows, int n, float eps, int parts, cudaStream_t s, const void* x, const void* w,
+                     const void* dy, void* dx, void* dw, void* db, void* scratch, char* err);
+size_t norm_bwd_scratch_bytes(int mode, int parts, int n);
+
 int plan_attention(Record& r, char* err);
 int launch_attention(const Record& r, cudaStream_t stream, void** ptrs, char* err);
 

@@ -1,0 +1,282 @@
+// Backward kernels of the row-wise f32 ops for sm_100a: RMSNorm, LayerNorm, SwiGLU.
+//
+// The reference ships no backward kernels; its autograd hook
+// (pyptx/torch_support.py:446-519, differentiable_kernel) pairs a forward kernel with a
+// user-supplied backward one.  These are the backward halves for that hook, HBM-bound like
+// the forward kernels and built on the same skeleton (row in registers, 128-bit coalesced
+// accesses, warp-shuffle + one shared-memory exchange per reduction).
+//
+// RMSNorm   y = x * r * w,  r = rsqrt(mean(x^2) + eps)
+//   dx = r * (w*dy - xhat * mean(xhat * w*dy)),  xhat = x * r;   dw = sum_rows dy * xhat
+// LayerNorm y = xhat * w + b,  xhat = (x - mu) * r
+//   dx = r * (w*dy - mean(w*dy) - xhat * mean(xhat * w*dy));   dw = sum_rows dy * xhat;  db = sum_rows dy
+// SwiGLU    out = g * s * u,  s = sigmoid(g)
+//   dg = dout * u * s * (1 + g * (1 - s));   du = dout * g * s
+//
+// The column sums dw / db go through SCRATCH memory: a persistent grid of P CTAs walks the
+// rows, every thread keeps the partial sums of its own columns in registers, each CTA writes
+// one partial row to scratch[P][N] (two planes for LayerNorm), and a second small kernel
+// folds the P rows.  This is deterministic (no atomics) and costs P*N*4 bytes of traffic
+// against 3*B*N*4 for the main pass.  The scratch buffer is supplied by the caller as one
+// extra trailing pointer (its size is part of the handle's geometry).
+#include "common.cuh"
+
+namespace pb200 {
+namespace {
+
+constexpr int kWarp = 32;
+
+__device__ __forceinline__ float4 ld_stream4(const float4* p) {
+    float4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void st_stream4(float4* p, const float4& v) {
+    asm volatile("st.global.cs.v4.f32 [%0], {%1,%2,%3,%4};"
+                 :: "l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = kWarp / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+// Two block-wide sums with one barrier (see block_reduce in row_kernels.cu for the slot rule).
+template <int THREADS>
+__device__ __forceinline__ void block_sum2(float& a, float& b, float2* slot) {
+    constexpr int NW = THREADS / kWarp;
+    a = warp_sum(a);
+    b = warp_sum(b);
+    if (NW == 1) return;
+    if ((threadIdx.x & (kWarp - 1)) == 0) slot[threadIdx.x / kWarp] = make_float2(a, b);
+    __syncthreads();
+    float2 r = slot[0];
+#pragma unroll
+    for (int i = 1; i < NW; ++i) { r.x += slot[i].x; r.y += slot[i].y; }
+    a = r.x;
+    b = r.y;
+}
+
+// MODE 0 = RMSNorm, 1 = LayerNorm.  partial_w / partial_b: [gridDim.x][4*n4] f32.
+template <int THREADS, int VPT, int MODE>
+__global__ void __launch_bounds__(THREADS)
+norm_bwd_kernel(const float4* __restrict__ x, const float4* __restrict__ w, const float4* __restrict__ dy,
+                float4* __restrict__ dx, float4* __restrict__ partial_w, float4* __restrict__ partial_b,
+                int rows, int n4, float inv_n, float eps) {
+    __shared__ float2 red[3][kWarp];
+    float4 acc_w[VPT], acc_b[VPT], wv[VPT];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int idx = threadIdx.x + i * THREADS;
+        acc_w[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        acc_b[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        wv[i] = idx < n4 ? __ldg(w + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    int flip = 0;
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const float4* xr = x + (size_t)row * n4;
+        const float4* gr = dy + (size_t)row * n4;
+        float4* dr = dx + (size_t)row * n4;
+        float4 xv[VPT], gv[VPT];
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int idx = threadIdx.x + i * THREADS;
+            const bool in = idx < n4;
+            xv[i] = in ? ld_stream4(xr + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+            gv[i] = in ? ld_stream4(gr + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        // first moments: sum x (LayerNorm only) and sum w*dy
+        float s_x = 0.f, s_wdy = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            if (MODE == 1) s_x += (xv[i].x + xv[i].y) + (xv[i].z + xv[i].w);
+            s_wdy += wv[i].x * gv[i].x + wv[i].y * gv[i].y + wv[i].z * gv[i].z + wv[i].w * gv[i].w;
+        }
+        block_sum2<THREADS>(s_x, s_wdy, red[flip]);
+        flip = flip == 2 ? 0 : flip + 1;
+        const float mu = MODE == 1 ? s_x * inv_n : 0.f;
+        // second moments: sum (x-mu)^2 and sum (x-mu) * w*dy
+        float s_xx = 0.f, s_xwdy = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int idx = threadIdx.x + i * THREADS;
+            if (idx < n4) {
+                const float cx = xv[i].x - mu, cy = xv[i].y - mu, cz = xv[i].z - mu, cw = xv[i].w - mu;
+                s_xx += cx * cx + cy * cy + cz * cz + cw * cw;
+                s_xwdy += cx * wv[i].x * gv[i].x + cy * wv[i].y * gv[i].y + cz * wv[i].z * gv[i].z + cw * wv[i].w * gv[i].w;
+            }
+        }
+        block_sum2<THREADS>(s_xx, s_xwdy, red[flip]);
+        flip = flip == 2 ? 0 : flip + 1;
+        const float r = rsqrtf(s_xx * inv_n + eps);
+        const float c1 = s_xwdy * r * inv_n;                    // mean(xhat * w*dy)
+        const float c2 = MODE == 1 ? s_wdy * inv_n : 0.f;       // mean(w*dy)
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int idx = threadIdx.x + i * THREADS;
+            if (idx < n4) {
+                const float hx = (xv[i].x - mu) * r, hy = (xv[i].y - mu) * r, hz = (xv[i].z - mu) * r, hw = (xv[i].w - mu) * r;
+                float4 o;
+                o.x = r * (wv[i].x * gv[i].x - c2 - hx * c1);
+                o.y = r * (wv[i].y * gv[i].y - c2 - hy * c1);
+                o.z = r * (wv[i].z * gv[i].z - c2 - hz * c1);
+                o.w = r * (wv[i].w * gv[i].w - c2 - hw * c1);
+                st_stream4(dr + idx, o);
+                acc_w[i].x += gv[i].x * hx; acc_w[i].y += gv[i].y * hy; acc_w[i].z += gv[i].z * hz; acc_w[i].w += gv[i].w * hw;
+                if (MODE == 1) { acc_b[i].x += gv[i].x; acc_b[i].y += gv[i].y; acc_b[i].z += gv[i].z; acc_b[i].w += gv[i].w; }
+            }
+        }
+    }
+    // this CTA's partial column sums -> scratch
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int idx = threadIdx.x + i * THREADS;
+        if (idx < n4) {
+            partial_w[(size_t)blockIdx.x * n4 + idx] = acc_w[i];
+            if (MODE == 1) partial_b[(size_t)blockIdx.x * n4 + idx] = acc_b[i];
+        }
+    }
+}
+
+// out[c] = sum_p partial[p][c] for the first `planes` planes (dw, then db).
+__global__ void __launch_bounds__(256)
+fold_partials_kernel(const float4* __restrict__ partial, float4* __restrict__ out_w, float4* __restrict__ out_b,
+                     int parts, int n4, int planes) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n4) return;
+    for (int pl = 0; pl < planes; ++pl) {
+        const float4* src = partial + (size_t)pl * parts * n4;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int p = 0; p < parts; ++p) {
+            const float4 v = src[(size_t)p * n4 + idx];
+            a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+        }
+        (pl == 0 ? out_w : out_b)[idx] = a;
+    }
+}
+
+__global__ void __launch_bounds__(256)
+swiglu_bwd_kernel(const float4* __restrict__ gate, const float4* __restrict__ up, const float4* __restrict__ dout,
+                  float4* __restrict__ dgate, float4* __restrict__ dup, size_t total4) {
+    constexpr int UNROLL = 2;
+    const size_t tile = (size_t)256 * UNROLL;
+    for (size_t base = (size_t)blockIdx.x * tile; base < total4; base += (size_t)gridDim.x * tile) {
+        float4 g[UNROLL], u[UNROLL], d[UNROLL];
+#pragma unroll
+        for (int i = 0; i < UNROLL; ++i) {
+            const size_t idx = base + threadIdx.x + (size_t)i * 256;
+            if (idx < total4) { g[i] = ld_stream4(gate + idx); u[i] = ld_stream4(up + idx); d[i] = ld_stream4(dout + idx); }
+        }
+#pragma unroll
+        for (int i = 0; i < UNROLL; ++i) {
+            const size_t idx = base + threadIdx.x + (size_t)i * 256;
+            if (idx < total4) {
+                float4 og, ou;
+                auto one = [](float gg, float uu, float dd, float& dg, float& du) {
+                    const float s = 1.0f / (1.0f + expf(-gg));
+                    du = dd * gg * s;
+                    dg = dd * uu * s * (1.0f + gg * (1.0f - s));
+                };
+                one(g[i].x, u[i].x, d[i].x, og.x, ou.x);
+                one(g[i].y, u[i].y, d[i].y, og.y, ou.y);
+                one(g[i].z, u[i].z, d[i].z, og.z, ou.z);
+                one(g[i].w, u[i].w, d[i].w, og.w, ou.w);
+                st_stream4(dgate + idx, og);
+                st_stream4(dup + idx, ou);
+            }
+        }
+    }
+}
+
+struct BwdConfig { int threads; int vpt; };
+// Smallest register-resident configuration that covers a row; rows beyond 16384 columns are not supported.
+bool pick_bwd_config(int64_t n4, BwdConfig& c) {
+    const BwdConfig table[] = {{32, 1}, {32, 2}, {64, 2}, {128, 2}, {128, 4}, {256, 4}, {512, 4}, {512, 8}};
+    for (const BwdConfig& t : table)
+        if ((int64_t)t.threads * t.vpt >= n4) { c = t; return true; }
+    return false;
+}
+int bwd_parts(int64_t rows) {
+    const int64_t p = 2 * (int64_t)sm_count();
+    return (int)(rows < p ? rows : p);
+}
+
+template <int THREADS, int VPT>
+void launch_norm(int mode, int parts, cudaStream_t s, const float4* x, const float4* w, const float4* dy, float4* dx,
+                 float4* pw, float4* pb, int rows, int n4, float inv_n, float eps) {
+    if (mode == 0) norm_bwd_kernel<THREADS, VPT, 0><<<parts, THREADS, 0, s>>>(x, w, dy, dx, pw, pb, rows, n4, inv_n, eps);
+    else norm_bwd_kernel<THREADS, VPT, 1><<<parts, THREADS, 0, s>>>(x, w, dy, dx, pw, pb, rows, n4, inv_n, eps);
+}
+
+}  // namespace
+
+// Shared by the generic entry (scratch from the caller) and the allocation-free entry (static scratch).
+int enqueue_norm_bwd(int mode, int rows, int n, float eps, int parts, cudaStream_t s, const void* x, const void* w,
+                     const void* dy, void* dx, void* dw, void* db, void* scratch, char* err) {
+    const int n4 = n / 4;
+    BwdConfig c;
+    if (!pick_bwd_config(n4, c)) { set_err(err, "backward norm kernels support at most 16384 columns, got %d", n); return PB200_ERR_BAD_SHAPE; }
+    float4* pw = (float4*)scratch;
+    float4* pb = pw + (size_t)parts * n4;
+    const float inv_n = 1.0f / (float)n;
+#define PB200_BWD_CASE(T, V) \
+    if (c.threads == T && c.vpt == V) launch_norm<T, V>(mode, parts, s, (const float4*)x, (const float4*)w, (const float4*)dy, \
+                                                        (float4*)dx, pw, pb, rows, n4, inv_n, eps); else
+    PB200_BWD_CASE(32, 1) PB200_BWD_CASE(32, 2) PB200_BWD_CASE(64, 2) PB200_BWD_CASE(128, 2)
+    PB200_BWD_CASE(128, 4) PB200_BWD_CASE(256, 4) PB200_BWD_CASE(512, 4) PB200_BWD_CASE(512, 8) {}
+#undef PB200_BWD_CASE
+    fold_partials_kernel<<<(n4 + 255) / 256, 256, 0, s>>>(pw, (float4*)dw, (float4*)db, parts, n4, mode == 1 ? 2 : 1);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { set_err(err, "backward norm launch failed: %s", cudaGetErrorString(e)); return PB200_ERR_LAUNCH; }
+    return PB200_OK;
+}
+
+size_t norm_bwd_scratch_bytes(int mode, int parts, int n) { return (size_t)(mode == 1 ? 2 : 1) * parts * n * sizeof(float); }
+
+int plan_row_bwd(Record& r, char* err) {
+    if (r.n_dims != 2) { set_err(err, "backward row kernel needs dims = {rows, cols}, got %d dims", r.n_dims); return PB200_ERR_BAD_SHAPE; }
+    const int64_t rows = r.dims[0], n = r.dims[1];
+    if (rows <= 0 || n <= 0 || rows > 0x7fffffffLL) { set_err(err, "rows=%lld cols=%lld out of range", (long long)rows, (long long)n); return PB200_ERR_BAD_SHAPE; }
+    if (n % 4 != 0) { set_err(err, "cols=%lld must be divisible by 4 (128-bit vector access)", (long long)n); return PB200_ERR_BAD_SHAPE; }
+    pb200_geometry& g = r.geom;
+    g.grid[1] = g.grid[2] = 1; g.block[1] = g.block[2] = 1;
+    g.cluster[0] = g.cluster[1] = g.cluster[2] = 1;
+    g.smem_bytes = 0;
+    g.scratch_bytes = 0;
+    g.n_inputs = 3;
+    if (r.kernel_id == PB200_K_SWIGLU_BWD) {
+        const int64_t total4 = rows * n / 4;
+        int64_t ctas = (total4 + 511) / 512;
+        if (ctas > 0x7fffffffLL) ctas = 0x7fffffffLL;
+        g.grid[0] = (uint32_t)ctas; g.block[0] = 256; g.n_outputs = 2;
+        return PB200_OK;
+    }
+    BwdConfig c;
+    if (!pick_bwd_config(n / 4, c)) { set_err(err, "backward norm kernels support at most 16384 columns, got %lld", (long long)n); return PB200_ERR_BAD_SHAPE; }
+    const int mode = r.kernel_id == PB200_K_LAYER_NORM_BWD ? 1 : 0;
+    const int parts = bwd_parts(rows);
+    r.dims[7] = parts;            // fixed at create time: the scratch size depends on it
+    g.grid[0] = (uint32_t)parts; g.block[0] = (uint32_t)c.threads;
+    g.smem_bytes = 3 * kWarp * sizeof(float2);
+    g.n_outputs = mode == 1 ? 3 : 2;
+    g.scratch_bytes = norm_bwd_scratch_bytes(mode, parts, (int)n);
+    return PB200_OK;
+}
+
+// buffers: x, w, dy | dx, dw [, db] | scratch          (SwiGLU: gate, up, dout | dgate, dup)
+int launch_row_bwd(const Record& r, cudaStream_t s, void** p, char* err) {
+    const int rows = (int)r.dims[0], n = (int)r.dims[1];
+    if (r.kernel_id == PB200_K_SWIGLU_BWD) {
+        swiglu_bwd_kernel<<<r.geom.grid[0], 256, 0, s>>>((const float4*)p[0], (const float4*)p[1], (const float4*)p[2],
+                                                         (float4*)p[3], (float4*)p[4], (size_t)rows * (n / 4));
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) { set_err(err, "swiglu backward launch failed: %s", cudaGetErrorString(e)); return PB200_ERR_LAUNCH; }
+        return PB200_OK;
+    }
+    const int mode = r.kernel_id == PB200_K_LAYER_NORM_BWD ? 1 : 0;
+    void* db = mode == 1 ? p[5] : nullptr;
+    void* scratch = mode == 1 ? p[6] : p[5];
+    return enqueue_norm_bwd(mode, rows, n, (float)r.fparams[0], (int)r.dims[7], s, p[0], p[1], p[2], p[3], p[4], db, scratch, err);
+}
+
+}  // namespace pb200

@@ -41,6 +41,7 @@ class NativeKernel:
         self._block = tuple(int(v) for v in g.block)
         self._cluster = tuple(int(v) for v in g.cluster)
         self._smem = int(g.smem_bytes)
+        self._scratch_bytes = int(g.scratch_bytes)
         if (int(g.n_inputs), int(g.n_outputs)) != (len(self._in_specs), len(self._out_specs)):
             raise RuntimeError(
                 f"{name}: spec count ({len(self._in_specs)} in, {len(self._out_specs)} out) disagrees "
@@ -77,6 +78,11 @@ class NativeKernel:
     @property
     def smem(self) -> int:
         return self._smem
+
+    @property
+    def scratch_bytes(self) -> int:
+        """Device scratch the kernel needs per launch (allocated by the launch path, never kept)."""
+        return self._scratch_bytes
 
     @property
     def arch(self) -> str:

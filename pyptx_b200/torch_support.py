@@ -91,7 +91,8 @@ class _Launcher:
         self.lib = _native.load()
         self.handle = ctypes.c_int64(kernel.handle)
         self.n_in = len(kernel.in_specs)
-        self.n = self.n_in + len(kernel.out_specs)
+        self.scratch_bytes = kernel.scratch_bytes
+        self.n = self.n_in + len(kernel.out_specs) + (1 if self.scratch_bytes else 0)
         self.ptrs = (ctypes.c_void_p * self.n)()
         self.ptrs_ref = ctypes.cast(self.ptrs, ctypes.c_void_p)
         self.err = ctypes.create_string_buffer(_native.ERR_LEN)
@@ -150,15 +151,23 @@ def call_kernel_via_torch(kernel, inputs: Sequence[Any]):
     env = _check_inputs(kernel, launcher, inputs)
     dev = inputs[0].device
     shapes = launcher.static_out_shapes or kernel.out_shapes(env)
+    if launcher.scratch_bytes:
+        # Scratch rides along as one more buffer after the outputs; it comes from torch's caching
+        # allocator like the outputs (so capture in a CUDA graph works) and is dropped on return.
+        shapes = list(shapes) + [(launcher.scratch_bytes,)]
     if launcher.ext is not None:
         # pybind11 fast path: output allocation and the C-ABI call happen in C++.
+        codes = launcher.out_dtype_codes + ([0] if launcher.scratch_bytes else [])      # scratch: uint8
         if torch.cuda.current_device() != dev.index:
             with torch.cuda.device(dev):
-                return launcher.ext.launch_kernel(launcher.handle_int, torch.cuda.current_stream(dev).cuda_stream,
-                                                  list(inputs), [list(s) for s in shapes], launcher.out_dtype_codes)
-        return launcher.ext.launch_kernel(launcher.handle_int, torch.cuda.current_stream(dev).cuda_stream,
-                                          list(inputs), [list(s) for s in shapes], launcher.out_dtype_codes)
-    outs = [torch.empty(shp, dtype=dt, device=dev) for shp, dt in zip(shapes, launcher.out_dtypes)]
+                res = launcher.ext.launch_kernel(launcher.handle_int, torch.cuda.current_stream(dev).cuda_stream,
+                                                 list(inputs), [list(s) for s in shapes], codes)
+        else:
+            res = launcher.ext.launch_kernel(launcher.handle_int, torch.cuda.current_stream(dev).cuda_stream,
+                                             list(inputs), [list(s) for s in shapes], codes)
+        return res[:-1] if launcher.scratch_bytes else res
+    dtypes = launcher.out_dtypes + ([torch.uint8] if launcher.scratch_bytes else [])
+    outs = [torch.empty(shp, dtype=dt, device=dev) for shp, dt in zip(shapes, dtypes)]
     ptrs = launcher.ptrs
     for i, t in enumerate(inputs):
         ptrs[i] = t.data_ptr()
@@ -174,7 +183,7 @@ def call_kernel_via_torch(kernel, inputs: Sequence[Any]):
     if rc != 0:
         msg = launcher.err.value.decode("utf-8", errors="replace")
         raise RuntimeError(f"pyptx_b200: pb200_launch_raw failed (code {rc}): {msg}")
-    return outs
+    return outs[:-1] if launcher.scratch_bytes else outs
 
 
 # ---------------------------------------------------------------------------
@@ -257,6 +266,9 @@ def differentiable_kernel(forward_kernel, backward_kernel, *,
 
         @staticmethod
         def backward(ctx, *grad_outputs):
+            # Autograd hands out expanded (stride-0) gradients for reductions such as sum(); the
+            # kernels take contiguous buffers.
+            grad_outputs = tuple(g.contiguous() if g is not None else None for g in grad_outputs)
             with torch.no_grad():
                 grads = backward_kernel(*ctx.saved_tensors, *grad_outputs)
             if not isinstance(grads, tuple):

@@ -181,6 +181,21 @@ PB200_API int    pb200_destroy(int64_t handle);
  * (pyptx/ptx.py:2311-2337). */
 PB200_API int pb200_device_status(char* err_out);
 
+/* RMSNorm backward that brings its own scratch memory.  It has no counterpart in the reference.
+ * For hosts that may not allocate device memory on the path that calls this library (a serving
+ * process with a memory plan fixed at load time, a plugin slot that receives its tensors and
+ * nothing else) and therefore cannot supply the scratch buffer PB200_K_RMS_NORM_BWD asks for.
+ * Computes dx[rows,cols] and dw[cols] from x[rows,cols], w[cols], dy[rows,cols] (f32, 16-byte
+ * aligned device pointers on the current device) and enqueues on `stream`; it calls no
+ * allocation routine.  The scratch is a 4 MiB array inside the library image: it is held on every
+ * GPU that loads the library, cols may not exceed 16384 (rejected with PB200_ERR_BAD_SHAPE), all
+ * calls on one GPU share it, so calls that could overlap on the GPU must be ordered by the caller,
+ * and the first call on each GPU resolves the array's address -- make it at start-up, before any
+ * stream capture. */
+PB200_API int pb200_rms_norm_bwd_static(int64_t rows, int64_t cols, double eps, uint64_t stream,
+                                        const void* x, const void* w, const void* dy,
+                                        void* dx, void* dw, char* err_out);
+
 /* Host-side evaluation of the encodings the matrix kernels use, exported so
  * that tests can pin them to the reference's known answers.
  *   pb200_encode_idesc      tcgen05 instruction descriptor, kind::f16, f32 accumulate

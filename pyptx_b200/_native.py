@@ -37,6 +37,7 @@ EXPORTED_SYMBOLS = (
     "pb200_registry_size", "pb200_clear_registry", "pb200_destroy",
     "pb200_device_status", "pb200_version", "pb200_arch",
     "pb200_encode_idesc", "pb200_encode_smem_desc", "pb200_swizzle128",
+    "pb200_rms_norm_bwd_static",
 )
 
 
@@ -253,6 +254,9 @@ def load():
         lib.pb200_encode_smem_desc.argtypes = [c.c_uint32] * 4
         lib.pb200_swizzle128.restype = c.c_uint32
         lib.pb200_swizzle128.argtypes = [c.c_uint32]
+        lib.pb200_rms_norm_bwd_static.restype = c.c_int
+        lib.pb200_rms_norm_bwd_static.argtypes = [c.c_int64, c.c_int64, c.c_double, c.c_uint64, c.c_void_p, c.c_void_p,
+                                                  c.c_void_p, c.c_void_p, c.c_void_p, c.c_char_p]
         _LIB = lib
     return _LIB
 

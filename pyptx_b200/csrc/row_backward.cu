@@ -21,6 +21,8 @@
 // extra trailing pointer (its size is part of the handle's geometry).
 #include "common.cuh"
 
+#include <atomic>
+
 namespace pb200 {
 namespace {
 
@@ -279,4 +281,95 @@ int launch_row_bwd(const Record& r, cudaStream_t s, void** p, char* err) {
     return enqueue_norm_bwd(mode, rows, n, (float)r.fparams[0], (int)r.dims[7], s, p[0], p[1], p[2], p[3], p[4], db, scratch, err);
 }
 
+// ---------------------------------------------------------------------------------------
+// RMSNorm backward for hosts that hand a kernel library no memory to work in.
+//
+// Some callers may not allocate device memory where they call us: an inference server whose
+// memory plan is fixed when the model is loaded, a plugin slot of a larger engine that gives
+// the plugin its tensors and nothing else, a process that lives inside a fixed share of a
+// GPU.  For them cudaMalloc on the request path is either forbidden outright or would stall
+// the device and break the owner's accounting, and they have no allocator of their own to
+// lend us.  The regular backward entry needs a scratch buffer from the caller; this one
+// brings its own, a fixed array that is part of the loaded library image.
+//
+// Limits and rules that follow from a shared, fixed array:
+//   * kStaticScratchBytes (4 MiB) per GPU stay reserved from the moment the library is
+//     loaded on that GPU until the process exits, whether or not this entry is ever called;
+//   * the partial-sum rows must fit: the grid is capped at kStaticScratchBytes / (4 * cols)
+//     CTAs (128 at 8192 columns, 64 at 16384), so very wide rows run with fewer CTAs than
+//     the regular entry would use, and cols above kStaticMaxCols are rejected;
+//   * every call on a GPU uses the same array.  Nothing in it has to start at zero (each call
+//     overwrites every word it later reads), so no clearing is done, but two calls that can
+//     run at the same time on one GPU (different streams, or different host threads) would
+//     overwrite each other's partial sums: callers must order them, e.g. on one stream;
+//   * the first call on each GPU looks up the array's device address (cudaGetSymbolAddress,
+//     which may initialise the CUDA context); make that first call during start-up, outside
+//     any stream capture.  Later calls only enqueue two kernels.
+// ---------------------------------------------------------------------------------------
+constexpr size_t kStaticScratchBytes = 4u << 20;
+constexpr int kStaticMaxCols = 16384;
+static __device__ __align__(256) float g_static_scratch[kStaticScratchBytes / sizeof(float)];
+
+namespace {
+constexpr int kMaxDev = 64;
+std::atomic<float*> g_static_scratch_ptr[kMaxDev];
+
+// Device address of g_static_scratch on the current device.  The array's name is only a
+// host-side handle here; the kernels need the address the runtime reports for it.
+int static_scratch_address(float** out, char* err) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= kMaxDev) {
+        set_err(err, "no usable current CUDA device (%s)", e == cudaSuccess ? "index out of range" : cudaGetErrorString(e));
+        return PB200_ERR_NO_CUDA;
+    }
+    float* p = g_static_scratch_ptr[dev].load(std::memory_order_acquire);
+    if (!p) {
+        void* addr = nullptr;
+        e = cudaGetSymbolAddress(&addr, g_static_scratch);
+        if (e != cudaSuccess || !addr) {
+            set_err(err, "cudaGetSymbolAddress(static scratch) failed on device %d: %s", dev, cudaGetErrorString(e));
+            return PB200_ERR_NO_CUDA;
+        }
+        p = (float*)addr;
+        g_static_scratch_ptr[dev].store(p, std::memory_order_release);
+    }
+    *out = p;
+    return PB200_OK;
+}
+}  // namespace
+
 }  // namespace pb200
+
+extern "C" PB200_API int pb200_rms_norm_bwd_static(int64_t rows, int64_t cols, double eps, uint64_t stream,
+                                                    const void* x, const void* w, const void* dy,
+                                                    void* dx, void* dw, char* err_out) {
+    using namespace pb200;
+    if (err_out) err_out[0] = 0;
+    if (rows <= 0 || rows > 0x7fffffffLL || cols <= 0 || cols % 4 != 0) {
+        set_err(err_out, "rows=%lld must be positive and cols=%lld a positive multiple of 4", (long long)rows, (long long)cols);
+        return PB200_ERR_BAD_SHAPE;
+    }
+    if (cols > kStaticMaxCols) {
+        set_err(err_out, "cols=%lld exceeds the %d columns the built-in %zu-byte scratch is sized for; "
+                         "use PB200_K_RMS_NORM_BWD with caller-provided scratch", (long long)cols, kStaticMaxCols,
+                kStaticScratchBytes);
+        return PB200_ERR_BAD_SHAPE;
+    }
+    const void* ptrs[5] = {x, w, dy, dx, dw};
+    for (int i = 0; i < 5; ++i)
+        if (!ptrs[i] || ((uintptr_t)ptrs[i] & 15u)) {
+            set_err(err_out, "buffer %d (%p) is NULL or not 16-byte aligned", i, ptrs[i]);
+            return PB200_ERR_MISALIGNED;
+        }
+    float* scratch = nullptr;
+    int rc = static_scratch_address(&scratch, err_out);
+    if (rc != PB200_OK) return rc;
+    // as many partial rows as fit, never more than the regular entry would use
+    int64_t parts = (int64_t)(kStaticScratchBytes / sizeof(float)) / cols;
+    const int64_t want = 2 * (int64_t)sm_count();
+    if (parts > want) parts = want;
+    if (parts > rows) parts = rows;
+    return enqueue_norm_bwd(0, (int)rows, (int)cols, (float)eps, (int)parts, (cudaStream_t)(uintptr_t)stream,
+                            x, w, dy, dx, dw, nullptr, scratch, err_out);
+}

@@ -126,6 +126,24 @@ extern "C" {
 #define PB200_K_LAYER_NORM_BWD 12
 #define PB200_K_SWIGLU_BWD     13
 
+/* Multi-GPU extensions (one process per GPU, buffers mapped between the GPUs of a node by the
+ * caller, e.g. through torch's symmetric memory).  The reference is single-device and has no
+ * counterpart for either.
+ *   PB200_K_GEMM_PUSH   the dense GEMM with its result stored to n_dest regions at once
+ *       dims = {n_dest (1..8), cta_group (1|2), M, N, K}   flags: PB200_F_OUT_BF16
+ *       buffers: A[M,K] bf16, B_T[N,K] bf16 -> n_dest pointers, each an [M,N] row-major f32
+ *                (or bf16) region; regions may be peer-mapped memory of other GPUs.  With one
+ *                region per rank, all at this rank's row offset of a gathered buffer, the
+ *                all-gather of D rides on the epilogue's TMA stores (none of them multicast).
+ *                A peer sees the data after the stream-ordered barrier below.
+ *   PB200_K_PEER_BARRIER   flag barrier across the ranks of a node, stream-ordered and bounded
+ *       dims = {world (1..8), rank}   fparams = {timeout in seconds, default 10}
+ *       buffers: world pointers, entry p = rank p's 64-byte flag block (16 uint32, zero before
+ *                the first call, mapped on every rank).  On expiry the kernel returns and
+ *                pb200_device_status() reports PB200_ERR_DEVICE_TIMEOUT.                       */
+#define PB200_K_GEMM_PUSH      14
+#define PB200_K_PEER_BARRIER   15
+
 /* ---- create-time flags -------------------------------------------------- */
 #define PB200_F_OUT_BF16       (1ull << 0)  /* round the output to bf16            */
 #define PB200_F_CAUSAL         (1ull << 1)  /* attention: lower-triangular mask    */

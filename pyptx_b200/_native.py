@@ -273,6 +273,18 @@ def create_handle(kernel_id: int, dims, fparams=(), flags: int = 0) -> int:
     return int(h)
 
 
+def launch_raw(handle: int, stream: int, ptrs) -> None:
+    """``pb200_launch_raw`` on raw device addresses (``ptrs``: ints, or a prepared
+    ``c_void_p`` array); raises ``RuntimeError`` with the library's message on failure."""
+    lib = load()
+    if not isinstance(ptrs, ctypes.Array):
+        ptrs = (ctypes.c_void_p * len(ptrs))(*[int(x) for x in ptrs])
+    err = ctypes.create_string_buffer(ERR_LEN)
+    rc = lib.pb200_launch_raw(handle, int(stream), ctypes.cast(ptrs, ctypes.c_void_p), len(ptrs), err)
+    if rc != 0:
+        raise RuntimeError(f"pyptx_b200: pb200_launch_raw failed (code {rc}): {err.value.decode(errors='replace')}")
+
+
 def geometry_of(handle: int) -> Geometry:
     g = Geometry()
     rc = load().pb200_geometry_of(handle, ctypes.byref(g))

@@ -47,7 +47,7 @@ bool is_row_bwd(int32_t k) {
 }
 bool is_gemm(int32_t k) {
     return k == PB200_K_GEMM_1SM || k == PB200_K_GEMM_2SM || k == PB200_K_GROUPED_GEMM ||
-           k == PB200_K_GROUPED_GEMM_SWIGLU || k == PB200_K_GROUPED_GEMM_VARLEN;
+           k == PB200_K_GROUPED_GEMM_SWIGLU || k == PB200_K_GROUPED_GEMM_VARLEN || k == PB200_K_GEMM_PUSH;
 }
 
 }  // namespace
@@ -133,6 +133,7 @@ PB200_API int64_t pb200_create(int32_t kernel_id, const int64_t* dims, size_t n_
     else if (is_row_bwd(kernel_id)) rc = plan_row_bwd(r, err_out);
     else if (is_gemm(kernel_id)) rc = plan_gemm(r, err_out);
     else if (kernel_id == PB200_K_FLASH_ATTN) rc = plan_attention(r, err_out);
+    else if (kernel_id == PB200_K_PEER_BARRIER) rc = plan_peer_barrier(r, err_out);
     else { set_err(err_out, "unknown kernel id %d", kernel_id); return PB200_ERR_BAD_KERNEL; }
     if (rc != PB200_OK) return rc;
     int64_t h = g_next_handle.fetch_add(1);
@@ -170,6 +171,7 @@ PB200_API int pb200_launch_raw(int64_t handle, uint64_t stream, void** buffer_pt
     if (is_row(r.kernel_id)) return launch_row(r, s, buffer_ptrs, err_out);
     if (is_row_bwd(r.kernel_id)) return launch_row_bwd(r, s, buffer_ptrs, err_out);
     if (is_gemm(r.kernel_id)) return launch_gemm(r, s, buffer_ptrs, err_out);
+    if (r.kernel_id == PB200_K_PEER_BARRIER) return launch_peer_barrier(r, s, buffer_ptrs, err_out);
     return launch_attention(r, s, buffer_ptrs, err_out);
 }
 

@@ -49,6 +49,9 @@ int enqueue_norm_bwd(int mode, int rows, int n, float eps, int parts, cudaStream
                      const void* dy, void* dx, void* dw, void* db, void* scratch, char* err);
 size_t norm_bwd_scratch_bytes(int mode, int parts, int n);
 
+int plan_peer_barrier(Record& r, char* err);
+int launch_peer_barrier(const Record& r, cudaStream_t stream, void** ptrs, char* err);
+
 int plan_attention(Record& r, char* err);
 int launch_attention(const Record& r, cudaStream_t stream, void** ptrs, char* err);
 

@@ -98,6 +98,20 @@ __device__ __forceinline__ void tile_coords(const GemmShape& s, int t, int& g, i
     tm = m0 + (r - tn * width);
 }
 
+// Destinations of the "push" variant (EPI = 2): every finished tile is stored to the same
+// coordinates of `n` extra [M, N] regions besides D.  The regions may be another GPU's memory
+// mapped into this process (peer access over NVLink): with one region per rank, all at this
+// rank's row offset of a gathered buffer, the all-gather of D happens tile by tile under the
+// main loop of the following tiles.  The stores are plain (non-multicast) TMA stores.
+constexpr int kMaxPushDest = 8;
+struct PushMaps {
+    CUtensorMap m[kMaxPushDest - 1];
+    int n;
+};
+struct NoPush {};
+template <int EPI> struct PushParam { using type = NoPush; };
+template <> struct PushParam<2> { using type = PushMaps; };
+
 // EPI = 0: D = accumulator.  EPI = 1 (grouped, 1-SM): the 256 accumulator columns of a tile are
 // 128 "gate" columns followed by the matching 128 "up" columns of one expert, and the kernel
 // writes silu(gate) * up (128 columns) -- the MoE up-projection with its activation fused.
@@ -107,13 +121,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const __grid_constant__ CUtensorMap tmap_b,
             const __grid_constant__ CUtensorMap tmap_d,
             OutT* __restrict__ d_ptr, GemmShape shape, int* status, int kernel_id,
-            const int* __restrict__ expert_offsets) {
+            const int* __restrict__ expert_offsets,
+            const __grid_constant__ typename PushParam<EPI>::type push) {
     using Plan = SmemPlan<BN, CTA_GROUP>;
     constexpr int kStages = Plan::kStages;
     constexpr int kChunkCols = 128 / (int)sizeof(OutT);     // columns per 128-byte store row
     constexpr int kOutCols = EPI == 1 ? BN / 2 : BN;        // output columns per tile
     constexpr int kChunks = kOutCols / kChunkCols;
-    static_assert(EPI == 0 || (BN == 256 && CTA_GROUP == 1 && !DIRECT), "the fused SwiGLU epilogue is a 1-SM, 256-column, TMA-store variant");
+    static_assert(EPI != 2 || (BN == 256 && !DIRECT), "the push epilogue is a 256-column, TMA-store variant");
+    static_assert(EPI != 1 || (BN == 256 && CTA_GROUP == 1 && !DIRECT), "the fused SwiGLU epilogue is a 1-SM, 256-column, TMA-store variant");
     constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
     constexpr uint32_t kIdesc = make_idesc_f16(BM * CTA_GROUP, BN);
 
@@ -351,6 +367,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     __syncwarp();
                     if (lane == 0) {
                         tma_store_2d(&tmap_d, sb, col0 + c * kChunkCols, row0);
+                        if constexpr (EPI == 2) {
+                            for (int i = 0; i < push.n; ++i)
+                                tma_store_2d(&push.m[i], sb, col0 + c * kChunkCols, row0);
+                        }
                         tma_store_commit();
                     }
                     flip ^= 1;
@@ -378,6 +398,12 @@ int pick_bn(int64_t n) {
     if (n % 128 == 0) return 128;
     if (n % 64 == 0) return 64;
     return 0;
+}
+
+// dims of the push kernel: {n_dest, cta_group, M, N, K}
+int cta_group_of(const Record& r) {
+    if (r.kernel_id == PB200_K_GEMM_PUSH) return (int)r.dims[1];
+    return r.kernel_id == PB200_K_GEMM_2SM ? 2 : 1;
 }
 
 bool is_grouped(int32_t kid) {
@@ -440,10 +466,22 @@ int launch_variant(const Record& r, cudaStream_t stream, void** p, const GemmSha
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     OutT* d_ptr = (OutT*)out_ptr;
+    typename PushParam<EPI>::type push{};
+    if constexpr (EPI == 2) {
+        push.n = (int)r.dims[0] - 1;
+        for (int i = 0; i < push.n; ++i) {
+            uint64_t dims[2] = {(uint64_t)N, (uint64_t)M};
+            uint64_t str[1] = {(uint64_t)N * sizeof(OutT)};
+            uint32_t box[2] = {128 / sizeof(OutT), kStageRows};
+            int rc = make_tensor_map(&push.m[i], sizeof(OutT) == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                                     2, p[3 + i], dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, err);
+            if (rc) return rc;
+        }
+    }
     const int* expert_offsets = varlen ? (const int*)p[2] : nullptr;
     int* status = device_status_ptr();
     int kid = r.kernel_id;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, td, d_ptr, shape, status, kid, expert_offsets);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, td, d_ptr, shape, status, kid, expert_offsets, push);
     if (e != cudaSuccess) {
         set_err(err, "gemm launch failed (BN=%d cta_group=%d grid=%u smem=%d): %s", BN, CTA_GROUP, r.geom.grid[0],
                 Plan::kTotal, cudaGetErrorString(e));
@@ -479,7 +517,12 @@ GemmShape make_shape(const Record& r, int bn, int cta_group) {
 int plan_gemm(Record& r, char* err) {
     const bool grouped = is_grouped(r.kernel_id);
     const bool swiglu = r.kernel_id == PB200_K_GROUPED_GEMM_SWIGLU;
-    const int need = grouped ? 4 : 3;
+    const bool push = r.kernel_id == PB200_K_GEMM_PUSH;
+    const int need = push ? 5 : grouped ? 4 : 3;
+    if (push && r.n_dims >= 2) {
+        if (r.dims[0] < 1 || r.dims[0] > kMaxPushDest) { set_err(err, "destination count must be in [1, %d]", kMaxPushDest); return PB200_ERR_BAD_SHAPE; }
+        if (r.dims[1] != 1 && r.dims[1] != 2) { set_err(err, "cta_group must be 1 or 2"); return PB200_ERR_BAD_SHAPE; }
+    }
     if (r.n_dims != need && r.n_dims != need + 1) {
         set_err(err, "gemm kernel %d needs %d dims (+1 optional raster band), got %d", r.kernel_id, need, r.n_dims);
         return PB200_ERR_BAD_SHAPE;
@@ -492,7 +535,7 @@ int plan_gemm(Record& r, char* err) {
     const int64_t G = grouped && !varlen ? r.dims[0] : 1;
     if (varlen && (r.dims[0] < 1 || r.dims[0] > 65536)) { set_err(err, "expert count must be in [1, 65536]"); return PB200_ERR_BAD_SHAPE; }
     const int64_t M = r.dims[need - 3], N = r.dims[need - 2], K = r.dims[need - 1];
-    const int cta_group = r.kernel_id == PB200_K_GEMM_2SM ? 2 : 1;
+    const int cta_group = cta_group_of(r);
     if (G < 1 || M < 1 || N < 1 || K < 1) { set_err(err, "G, M, N, K must be positive"); return PB200_ERR_BAD_SHAPE; }
     if (M % (BM * cta_group) != 0) { set_err(err, "M=%lld must be divisible by %d", (long long)M, BM * cta_group); return PB200_ERR_BAD_SHAPE; }
     if (K % BK != 0) { set_err(err, "K=%lld must be divisible by %d", (long long)K, BK); return PB200_ERR_BAD_SHAPE; }
@@ -512,7 +555,7 @@ int plan_gemm(Record& r, char* err) {
     g.cluster[0] = (uint32_t)cta_group; g.cluster[1] = g.cluster[2] = 1;
     g.smem_bytes = bn == 256 ? (cta_group == 2 ? SmemPlan<256, 2>::kTotal : SmemPlan<256, 1>::kTotal)
                  : bn == 128 ? SmemPlan<128, 1>::kTotal : SmemPlan<64, 1>::kTotal;
-    g.n_inputs = varlen ? 3 : 2; g.n_outputs = 1;
+    g.n_inputs = varlen ? 3 : 2; g.n_outputs = push ? (uint32_t)r.dims[0] : 1;
     return PB200_OK;
 }
 
@@ -520,7 +563,7 @@ int launch_gemm(const Record& r, cudaStream_t stream, void** p, char* err) {
     const int64_t N = r.dims[r.n_dims - 2];
     const bool swiglu = r.kernel_id == PB200_K_GROUPED_GEMM_SWIGLU;
     const int bn = swiglu ? 256 : pick_bn(N);
-    const int cta_group = r.kernel_id == PB200_K_GEMM_2SM ? 2 : 1;
+    const int cta_group = cta_group_of(r);
     const bool bf16_out = (r.flags & PB200_F_OUT_BF16) != 0;
     const bool direct = (r.flags & kDebugDirectStore) != 0;
     Record rr = r;
@@ -533,6 +576,13 @@ int launch_gemm(const Record& r, cudaStream_t stream, void** p, char* err) {
     if (swiglu)
         return bf16_out ? launch_variant<256, 1, __nv_bfloat16, false, 1>(rr, stream, p, shape, err)
                         : launch_variant<256, 1, float, false, 1>(rr, stream, p, shape, err);
+    if (r.kernel_id == PB200_K_GEMM_PUSH) {
+        if (cta_group == 2)
+            return bf16_out ? launch_variant<256, 2, __nv_bfloat16, false, 2>(rr, stream, p, shape, err)
+                            : launch_variant<256, 2, float, false, 2>(rr, stream, p, shape, err);
+        return bf16_out ? launch_variant<256, 1, __nv_bfloat16, false, 2>(rr, stream, p, shape, err)
+                        : launch_variant<256, 1, float, false, 2>(rr, stream, p, shape, err);
+    }
 #define PB200_GEMM_CASE(BN_, CG_)                                                                       \
     if (bn == BN_ && cta_group == CG_) {                                                                \
         if (bf16_out) return direct ? launch_variant<BN_, CG_, __nv_bfloat16, true>(rr, stream, p, shape, err)  \

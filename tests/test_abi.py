@@ -127,3 +127,39 @@ def test_encodings_match_oracle(lib):
             addr, stride_bytes=1024, leading_bytes=16384)
     for off in range(0, 4096, 16):
         assert lib.pb200_swizzle128(off) == encodings.swizzle_128b(off)
+
+
+def test_push_gemm_and_peer_barrier_geometry(lib):
+    err = ctypes.create_string_buffer(_native.ERR_LEN)
+
+    def create(kid, dims, fparams=()):
+        d = (ctypes.c_int64 * len(dims))(*dims)
+        f = (ctypes.c_double * max(len(fparams), 1))(*fparams)
+        return lib.pb200_create(kid, d, len(dims), f, len(fparams), 0, err), err.value.decode()
+
+    h = _native.create_handle(_ids.K_GEMM_PUSH, (4, 2, 1024, 512, 256))
+    g = _native.geometry_of(h)
+    assert (g.n_inputs, g.n_outputs) == (2, 4) and tuple(g.cluster) == (2, 1, 1) and g.scratch_bytes == 0
+    h1 = _native.create_handle(_ids.K_GEMM_PUSH, (1, 1, 128, 256, 64))
+    g1 = _native.geometry_of(h1)
+    assert (g1.n_inputs, g1.n_outputs) == (2, 1) and tuple(g1.cluster) == (1, 1, 1)
+    rc, msg = create(_ids.K_GEMM_PUSH, (9, 2, 1024, 512, 256))
+    assert rc == _ids.ERR_BAD_SHAPE and "destination count" in msg
+    rc, msg = create(_ids.K_GEMM_PUSH, (2, 3, 1024, 512, 256))
+    assert rc == _ids.ERR_BAD_SHAPE and "cta_group" in msg
+    rc, msg = create(_ids.K_GEMM_PUSH, (2, 2, 128, 512, 256))
+    assert rc == _ids.ERR_BAD_SHAPE and "M=128 must be divisible by 256" in msg
+    rc, msg = create(_ids.K_GEMM_PUSH, (1024, 512, 256))
+    assert rc == _ids.ERR_BAD_SHAPE
+
+    hb = _native.create_handle(_ids.K_PEER_BARRIER, (8, 3))
+    gb = _native.geometry_of(hb)
+    assert (gb.n_inputs, gb.n_outputs) == (8, 0) and tuple(gb.grid) == (1, 1, 1) and tuple(gb.block) == (32, 1, 1)
+    rc, msg = create(_ids.K_PEER_BARRIER, (9, 0))
+    assert rc == _ids.ERR_BAD_SHAPE and "world" in msg
+    rc, msg = create(_ids.K_PEER_BARRIER, (2, 2))
+    assert rc == _ids.ERR_BAD_SHAPE and "rank" in msg
+    rc, msg = create(_ids.K_PEER_BARRIER, (2, 0), (0.0,))
+    assert rc == _ids.ERR_BAD_SHAPE and "timeout" in msg
+    for x in (h, h1, hb):
+        lib.pb200_destroy(x)

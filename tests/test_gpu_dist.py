@@ -83,3 +83,43 @@ def test_attention_batch_head_sharded():
     o = shard.kernel(q[sl][None].cuda().contiguous(), k[sl][None].cuda().contiguous(), v[sl][None].cuda().contiguous())
     og = pdist.all_gather_rows(o[0], pdist.counts(B * H, world), rank) if world > 1 else o[0]
     assert og.shape == ref.shape and formulas.rel_fro(og.cpu(), ref) < 1e-2
+
+
+@pytest.mark.parametrize("two_sm", [False, True])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_push_gather_gemm_equals_oracle_on_every_rank(two_sm, out_dtype):
+    """The GEMM whose epilogue stores each tile into every rank's gathered buffer: all ranks
+    end up with the full product; repeated calls reuse the buffer safely."""
+    from pyptx_b200 import _native
+    from pyptx_b200.peer import PushGatherGemm
+
+    world, rank = _wr()
+    M_local, N, K = 512, 512, 256
+    a, bt = inputs.gemm_inputs(world * M_local, N, K)
+    ref = formulas.gemm_ref(a, bt)
+    gemm = PushGatherGemm(M_local, N, K, two_sm=two_sm, out_dtype=out_dtype)
+    assert (gemm.world, gemm.rank) == (world, rank)
+    a_local = a[rank * M_local:(rank + 1) * M_local].cuda().contiguous()
+    b_dev = bt.cuda()
+    for _ in range(3):
+        out = gemm(a_local, b_dev)
+        torch.cuda.synchronize()
+        assert out.shape == ref.shape
+        assert formulas.rel_fro(out.float().cpu(), ref) < (1e-2 if out_dtype == torch.bfloat16 else 1e-4)
+        out.zero_()          # the next call's entry barrier orders this before any peer's store
+    _native.device_status()
+
+
+def test_push_gather_is_bit_identical_to_nccl_gather():
+    from pyptx_b200.peer import PushGatherGemm
+
+    world, rank = _wr()
+    M_local, N, K = 1024, 1024, 512
+    a, bt = inputs.gemm_inputs(world * M_local, N, K)
+    a_local = a[rank * M_local:(rank + 1) * M_local].cuda().contiguous()
+    b_dev = bt.cuda()
+    shard = pdist.shard_gemm(build_gemm_2sm, world * M_local, N, K, world=world, rank=rank, gather=True)
+    via_nccl = shard(a_local, b_dev)
+    via_push = PushGatherGemm(M_local, N, K)(a_local, b_dev)
+    torch.cuda.synchronize()
+    assert torch.equal(via_push, via_nccl)

@@ -375,6 +375,63 @@ def run_case(args) -> None:
                       "l2": "1 GiB buffer written between launches"}))
 
 
+def gather_table(torch, dist, world: int, peak_tflops: float, iters: int = 10) -> dict:
+    """Context for N > 1: one 8192^3 product split by rows of A over the ranks, with the full D
+    wanted on every rank.  Three ways: the local GEMM alone (no gather), GEMM then NCCL
+    all-gather, and the GEMM whose epilogue pushes its tiles into every rank's buffer.
+    Times are CUDA events, max over ranks; TFLOP/s counts the whole product."""
+    from pyptx_b200.examples.blackwell.gemm_highperf_blackwell import build_gemm_2sm
+    from pyptx_b200.peer import PushGatherGemm
+    from pyptx_b200.types import bf16, f32
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(iters):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([s.elapsed_time(e) / iters], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    m_local = S // world
+    table = {"problem": f"M={S} split {world} ways (M_local={m_local}), N=K={S}", "nvlink_peer_copy_GBs_measured": 770}
+    a = torch.randn(m_local, S, device="cuda").to(torch.bfloat16)
+    bt = torch.randn(S, S, device="cuda").to(torch.bfloat16)
+    flops = 2.0 * S * S * S
+    for odt, tag, spec in ((torch.float32, "f32", f32), (torch.bfloat16, "bf16", bf16)):
+        k = build_gemm_2sm(m_local, S, S, out_dtype=spec)
+        full = torch.empty(S, S, dtype=odt, device="cuda")
+        push = PushGatherGemm(m_local, S, S, out_dtype=odt)
+
+        def with_nccl():
+            dist.all_gather_into_tensor(full, k(a, bt))
+
+        t_local, t_nccl, t_push = timed(lambda: k(a, bt)), timed(with_nccl), timed(lambda: push(a, bt))
+        sent = (world - 1) * m_local * S * (4 if odt == torch.float32 else 2)
+        table[tag] = {
+            "local_gemm_ms": t_local, "gemm_then_nccl_all_gather_ms": t_nccl, "push_epilogue_ms": t_push,
+            "gemm_then_nccl_tflops": flops / (t_nccl * 1e-3) / 1e12, "push_epilogue_tflops": flops / (t_push * 1e-3) / 1e12,
+            "bytes_sent_per_rank": sent,
+            # the slower of the tensor-bound time (per-rank FLOPs / measured cuBLAS bf16 peak) and
+            # the link-bound time (bytes leaving this GPU / measured peer-copy bandwidth)
+            "roofline_ms": max(flops / world / (peak_tflops * 1e12) * 1e3, sent / 770e9 * 1e3),
+        }
+        table[tag]["frac_of_roofline"] = table[tag]["roofline_ms"] / t_push
+        with_nccl()
+        same = torch.equal(push(a, bt), full)
+        torch.cuda.synchronize()
+        table[tag]["bit_identical_to_nccl_path"] = bool(same)
+        del push, full, k
+    return table
+
+
 def run_ours(args) -> None:
     import torch
     import torch.distributed as dist
@@ -471,6 +528,15 @@ def run_ours(args) -> None:
     e2e_value = flops_per_rank * world / (e2e_ms * 1e-3) / 1e12
     h2d = a_pin.numel() * 2 + bt_pin.numel() * 2
     d2h = d_pin.numel() * 4
+
+    gather = None
+    if world > 1 and not args.no_extras:
+        # every rank takes part; a failure on any rank is reported, not fatal to the headline
+        try:
+            gather = gather_table(torch, dist, world, peaks["bf16_tflops"])
+            _native.device_status()
+        except Exception as exc:  # noqa: BLE001 - context only
+            gather = {"error": str(exc)[:300]}
 
     extras, cpu_baseline = None, None
     if rank == 0 and world == 1 and args.no_extras:
@@ -577,6 +643,8 @@ def run_ours(args) -> None:
                          "frac_of_nominal_2250": kernel_tflops / 2250.0},
             "cpu_baseline": cpu_baseline,
         }
+        if gather is not None:
+            line["gather"] = gather
         if extras is not None:
             line["kernels"] = extras
             if not args.no_pyptx:

@@ -505,22 +505,33 @@ def run_ours(args) -> None:
         raise SystemExit("bench.py: timed GEMM produced an empty or non-finite result")
 
     # ---- end to end: pinned host -> device, kernel, device -> pinned host -----------------------
-    d_pin = torch.empty(S, S, dtype=torch.float32).pin_memory()
-    e2e_steps = max(2, min(args.steps, 5))
+    # Through the library's host-operand call (HostPipeline): every step uploads A and B_T from
+    # pinned memory, multiplies, and downloads D into pinned memory; the upload of step i+1 runs
+    # while D of step i is on its way back (PCIe is full duplex).  --e2e-depth 1 gives the serial
+    # order.  The timed region runs from before the first upload to after the last download.
+    from pyptx_b200.host_pipeline import HostPipeline
 
-    def e2e_step():
-        a_d = a_pin.cuda(non_blocking=True)
-        bt_d = bt_pin.cuda(non_blocking=True)
-        d_pin.copy_(kernel(a_d, bt_d), non_blocking=True)
+    depth = max(1, args.e2e_depth)
+    pipe = HostPipeline(kernel, depth=depth)
+    d_pins = [torch.empty(S, S, dtype=torch.float32).pin_memory() for _ in range(depth)]
+    d_pin = d_pins[0]
+    e2e_steps = max(4, min(args.steps, 10))
 
-    e2e_step()
+    def e2e_run(n):
+        for i in range(n):
+            pipe.submit(a_pin, bt_pin, out=d_pins[i % depth])
+        pipe.join()
+
+    e2e_run(depth + 1)
     barrier()
     start.record()
-    for _ in range(e2e_steps):
-        e2e_step()
+    e2e_run(e2e_steps)
     stop.record()
     barrier()
     e2e_ms = start.elapsed_time(stop) / e2e_steps
+    e2e_check = float(d_pins[(e2e_steps - 1) % depth][::1024, ::1024].double().abs().sum().item())
+    if abs(e2e_check - checksum) > 1e-6 * max(checksum, 1.0):
+        raise SystemExit("bench.py: the end-to-end result differs from the device-resident one")
     if world > 1:
         t = torch.tensor([e2e_ms], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -633,7 +644,8 @@ def run_ours(args) -> None:
                        "vs_baseline_ref": "reference README.md:54: its 1-SM kernel 1240 TFLOPS at 8192^3 on B200 (per GPU)"},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms, "steps": e2e_steps},
+                    "ms_per_step": e2e_ms, "steps": e2e_steps, "calls_in_flight": depth,
+                    "api": "pyptx_b200.host_pipeline.HostPipeline(build_gemm_2sm(...)).submit(pinned A, pinned B_T, out=pinned D)"},
             "gpu_launches": args.steps,
             "roofline": {"bound": "tensor", "achieved": kernel_tflops, "peak": peak, "unit": "TFLOP/s",
                          "frac": kernel_tflops / peak,
@@ -667,6 +679,8 @@ def main() -> None:
     ap.add_argument("--variant", choices=["1sm", "2sm"], default="2sm")
     ap.add_argument("--no-pyptx", action="store_true",
                     help="do not run the reference's own sm_100a kernels (baseline/_ref) for the context table")
+    ap.add_argument("--e2e-depth", type=int, default=2,
+                    help="calls in flight in the end-to-end leg (1 = upload, multiply, download strictly in turn)")
     ap.add_argument("--no-extras", action="store_true", help="skip the context table (other kernels, cuBLAS)")
     ap.add_argument("--case", default=None,
                     help="run ONE kernel only: gemm_1sm gemm_2sm grouped attention_d64 attention_d128[_causal] "

@@ -651,7 +651,7 @@ def run_ours(args) -> None:
                          "frac": kernel_tflops / peak,
                          # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this size
                          # (ncu capture summarised in profiles/gemm_2sm_8192.md)
-                         "traffic": 1508349440 if args.variant == "2sm" else None, "peak_kind": f"{peak_kind} burst cuBLAS bf16",
+                         "traffic": 1060119808 if args.variant == "2sm" else 1121270784, "peak_kind": f"{peak_kind} burst cuBLAS bf16",
                          "frac_of_nominal_2250": kernel_tflops / 2250.0},
             "cpu_baseline": cpu_baseline,
         }

@@ -54,6 +54,8 @@ constexpr int kEpiWarps = 4;
 constexpr int kStageRows = 32;   // rows per epilogue store box (one warp)
 constexpr int kStageBytes = kStageRows * 128;  // 4 KiB, swizzle-128B image
 constexpr uint32_t kDebugDirectStore = 1u << 16;  // create flag: bypass the TMA-store epilogue
+constexpr uint32_t kForceNarrowTile = 1u << 18;   // create flag: 2-SM kernels always use the 256 x 256 tile
+constexpr uint32_t kForceWideTile = 1u << 19;     // create flag: 2-SM kernels use the 512 x 256 tile whenever M % 512 == 0
 
 struct GemmShape {
     int tiles_m;      // tiles along M per group (a tile is BM*CTA_GROUP rows)
@@ -68,10 +70,10 @@ struct GemmShape {
     int up_row_off;         // EPI 1: row offset of an expert's "up" weights inside its block of B_T (= F)
 };
 
-template <int BN, int CTA_GROUP>
+template <int BN, int CTA_GROUP, int WIDE = 0>
 struct SmemPlan {
     static constexpr int kBRows = BN / CTA_GROUP;            // rows of B_T this CTA loads
-    static constexpr int kABytes = BM * BK * 2;              // 16 KiB
+    static constexpr int kABytes = BM * BK * 2 * (1 + WIDE); // 16 KiB per 128-row block of A
     static constexpr int kBBytes = kBRows * BK * 2;
     static constexpr int kStage = kABytes + kBBytes;
     static constexpr int kEpiBytes = kEpiWarps * 2 * kStageBytes;   // 32 KiB
@@ -115,7 +117,15 @@ template <> struct PushParam<2> { using type = PushMaps; };
 // EPI = 0: D = accumulator.  EPI = 1 (grouped, 1-SM): the 256 accumulator columns of a tile are
 // 128 "gate" columns followed by the matching 128 "up" columns of one expert, and the kernel
 // writes silu(gate) * up (128 columns) -- the MoE up-projection with its activation fused.
-template <int BN, int CTA_GROUP, typename OutT, bool DIRECT, int EPI = 0>
+//
+// WIDE = 1: a tile is two row blocks of A (2 x 256 rows for 2-SM, 2 x 128 for 1-SM) against one
+// block of B_T.
+// The two accumulators take the whole TMEM (2 x 256 columns), so there is no second buffer for
+// the next tile; in exchange every B tile fetched from L2 feeds twice the math (96 KiB per
+// k-tile and CTA pair for 512 x 256 outputs instead of 128 KiB), which is what the kernel pays
+// for in power at large sizes.  The epilogue drains the first accumulator, then the second; the
+// next tile's MMAs into an accumulator start as soon as that one is drained.
+template <int BN, int CTA_GROUP, typename OutT, bool DIRECT, int EPI = 0, int WIDE = 0>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const __grid_constant__ CUtensorMap tmap_b,
@@ -123,7 +133,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             OutT* __restrict__ d_ptr, GemmShape shape, int* status, int kernel_id,
             const int* __restrict__ expert_offsets,
             const __grid_constant__ typename PushParam<EPI>::type push) {
-    using Plan = SmemPlan<BN, CTA_GROUP>;
+    using Plan = SmemPlan<BN, CTA_GROUP, WIDE>;
+    static_assert(WIDE == 0 || (BN == 256 && EPI != 1), "the wide tile is a 256-column variant of the dense kernels");
+    constexpr int kSub = 1 + WIDE;                            // 256-row blocks of A per tile
     constexpr int kStages = Plan::kStages;
     constexpr int kChunkCols = 128 / (int)sizeof(OutT);     // columns per 128-byte store row
     constexpr int kOutCols = EPI == 1 ? BN / 2 : BN;        // output columns per tile
@@ -198,7 +210,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             for (int t = unit; t < n_tiles && ok; t += n_units) {
                 int g, tm, tn;
                 tile_coords(shape, t, g, tm, tn);
-                const int row_a = g * shape.rows_per_group_a + (tm * CTA_GROUP + (int)cta_rank) * BM;
+                const int row_a = g * shape.rows_per_group_a + (tm * CTA_GROUP * kSub + (int)cta_rank) * BM;
                 if (shape.n_experts > 0) {
                     // which expert owns this row block (a handful of cached 4-byte loads per tile)
                     while (g + 1 < shape.n_experts && __ldg(expert_offsets + g + 1) <= row_a) ++g;
@@ -212,6 +224,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     if (CTA_GROUP == 1) {
                         mbar_arrive_expect_tx(bar_full + 8 * stage, Plan::kTxBytes);
                         tma_load_2d(dst_a, &tmap_a, bar_full + 8 * stage, kt * BK, row_a);
+                        if (WIDE) tma_load_2d(dst_a + BM * BK * 2, &tmap_a, bar_full + 8 * stage, kt * BK, row_a + BM);
                         if (EPI == 1) {
                             // 128 gate rows, then the 128 up rows of the same feature block
                             tma_load_2d(dst_b, &tmap_b, bar_full + 8 * stage, kt * BK, row_b);
@@ -222,6 +235,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     } else {
                         if (is_leader) mbar_arrive_expect_tx(bar_full + 8 * stage, Plan::kTxBytes);
                         tma_load_2d_pair(dst_a, &tmap_a, full_leader + 8 * stage, kt * BK, row_a);
+                        if (WIDE) tma_load_2d_pair(dst_a + BM * BK * 2, &tmap_a, full_leader + 8 * stage, kt * BK, row_a + CTA_GROUP * BM);
                         tma_load_2d_pair(dst_b, &tmap_b, full_leader + 8 * stage, kt * BK, row_b);
                     }
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -246,8 +260,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             bool ok = true;
             int local = 0;
             for (int t = unit; t < n_tiles && ok; t += n_units, ++local) {
-                const int buf = local & 1;
-                const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
+                // Narrow tile: accumulators alternate between the two TMEM buffers.  Wide tile: every
+                // tile uses both (rows 0-255 in the first, 256-511 in the second).
+                const int buf = WIDE ? 0 : (local & 1);
+                const uint32_t acc_phase = WIDE ? ((uint32_t)local & 1u) : ((uint32_t)(local >> 1) & 1u);
                 if (!(ok = mbar_wait(bar_tempty + 8 * buf, acc_phase ^ 1u, ctx, 2))) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
@@ -259,6 +275,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     umma_f16_ss_lohi<CTA_GROUP>(d_tmem, a_lo + 2, a_hi, b_lo + 2, b_hi, kIdesc, 1u);
                     umma_f16_ss_lohi<CTA_GROUP>(d_tmem, a_lo + 4, a_hi, b_lo + 4, b_hi, kIdesc, 1u);
                     umma_f16_ss_lohi<CTA_GROUP>(d_tmem, a_lo + 6, a_hi, b_lo + 6, b_hi, kIdesc, 1u);
+                    if (WIDE) {
+                        if (kt == shape.k_tiles - 1) {
+                            // the first accumulator is complete: its drain overlaps the last MMAs of the second
+                            umma_commit<CTA_GROUP>(bar_tfull);
+                            if (CTA_GROUP == 2) umma_commit<CTA_GROUP>(tfull_peer);
+                        }
+                        if (kt == 0) {
+                            if (!(ok = mbar_wait(bar_tempty + 8, acc_phase ^ 1u, ctx, 5))) break;
+                            tc_fence_after_sync();
+                        }
+                        constexpr uint32_t kA1 = (uint32_t)(BM * BK * 2) >> 4;    // second A block of the stage
+                        const uint32_t d1 = tmem_base + (uint32_t)BN;
+                        umma_f16_ss_lohi<CTA_GROUP>(d1, a_lo + kA1, a_hi, b_lo, b_hi, kIdesc, kt != 0 ? 1u : 0u);
+                        umma_f16_ss_lohi<CTA_GROUP>(d1, a_lo + kA1 + 2, a_hi, b_lo + 2, b_hi, kIdesc, 1u);
+                        umma_f16_ss_lohi<CTA_GROUP>(d1, a_lo + kA1 + 4, a_hi, b_lo + 4, b_hi, kIdesc, 1u);
+                        umma_f16_ss_lohi<CTA_GROUP>(d1, a_lo + kA1 + 6, a_hi, b_lo + 6, b_hi, kIdesc, 1u);
+                    }
                     umma_commit<CTA_GROUP>(empty_cur);
                     if (CTA_GROUP == 2) umma_commit<CTA_GROUP>(empty_peer);
                     if (++stage == kStages) {
@@ -270,8 +303,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     }
                 }
                 if (!ok) break;
-                umma_commit<CTA_GROUP>(bar_tfull + 8 * buf);
-                if (CTA_GROUP == 2) umma_commit<CTA_GROUP>(tfull_peer + 8 * buf);
+                if (WIDE) {
+                    umma_commit<CTA_GROUP>(bar_tfull + 8);
+                    if (CTA_GROUP == 2) umma_commit<CTA_GROUP>(tfull_peer + 8);
+                } else {
+                    umma_commit<CTA_GROUP>(bar_tfull + 8 * buf);
+                    if (CTA_GROUP == 2) umma_commit<CTA_GROUP>(tfull_peer + 8 * buf);
+                }
             }
         }
     } else {
@@ -286,10 +324,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         for (int t = unit; t < n_tiles && ok; t += n_units, ++local) {
             int g, tm, tn;
             tile_coords(shape, t, g, tm, tn);
-            const int buf = local & 1;
-            const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
-            const int row0 = g * shape.rows_per_group_a + (tm * CTA_GROUP + (int)cta_rank) * BM + q * 32;
             const int col0 = tn * kOutCols;
+#pragma unroll 1
+            for (int sub = 0; sub < kSub && ok; ++sub) {
+            const int buf = WIDE ? sub : (local & 1);
+            const uint32_t acc_phase = WIDE ? ((uint32_t)local & 1u) : ((uint32_t)(local >> 1) & 1u);
+            const int row0 = g * shape.rows_per_group_a + ((tm * kSub + sub) * CTA_GROUP + (int)cta_rank) * BM + q * 32;
             ok = mbar_wait(bar_tfull + 8 * buf, acc_phase, ctx, 4);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
@@ -376,6 +416,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     flip ^= 1;
                 }
             }
+            }   // sub
         }
         if (!DIRECT && lane == 0) tma_store_wait_all<0>();
     }
@@ -410,10 +451,10 @@ bool is_grouped(int32_t kid) {
     return kid == PB200_K_GROUPED_GEMM || kid == PB200_K_GROUPED_GEMM_SWIGLU || kid == PB200_K_GROUPED_GEMM_VARLEN;
 }
 
-template <int BN, int CTA_GROUP, typename OutT, bool DIRECT, int EPI = 0>
+template <int BN, int CTA_GROUP, typename OutT, bool DIRECT, int EPI = 0, int WIDE = 0>
 int launch_variant(const Record& r, cudaStream_t stream, void** p, const GemmShape& shape, char* err) {
-    using Plan = SmemPlan<BN, CTA_GROUP>;
-    auto kernel = gemm_kernel<BN, CTA_GROUP, OutT, DIRECT, EPI>;
+    using Plan = SmemPlan<BN, CTA_GROUP, WIDE>;
+    auto kernel = gemm_kernel<BN, CTA_GROUP, OutT, DIRECT, EPI, WIDE>;
     static std::atomic<uint64_t> attr_set{0};   // bit per device
     int dev = 0;
     cudaGetDevice(&dev);
@@ -490,14 +531,32 @@ int launch_variant(const Record& r, cudaStream_t stream, void** p, const GemmSha
     return PB200_OK;
 }
 
-GemmShape make_shape(const Record& r, int bn, int cta_group) {
+// Whether a dense problem runs on double-height tiles (512 x 256 per CTA pair, 256 x 256 per CTA).
+// Measured faster at 4096^3 and 8192^3 (+2..8 %) and slower when they leave SMs without a tile
+// (2048^3): they halve the number of tiles, so they are taken only when there is at least one
+// full wave of them and the last wave stays about as full as with single-height tiles.
+bool use_wide_tile(const Record& r, int64_t units) {
+    if (is_grouped(r.kernel_id)) return false;
+    if (r.flags & (kForceNarrowTile | kDebugDirectStore)) return false;
+    const int64_t M = r.dims[r.n_dims - 3], N = r.dims[r.n_dims - 2];
+    const int cg = cta_group_of(r);
+    if (M % (2 * cg * BM) != 0) return false;
+    if (r.flags & kForceWideTile) return true;
+    if (units < 1) units = 1;
+    const int64_t narrow = (M / (cg * BM)) * (N / 256), wide = narrow / 2;
+    const double eff_n = (double)narrow / (double)(((narrow + units - 1) / units) * units);
+    const double eff_w = (double)wide / (double)(((wide + units - 1) / units) * units);
+    return wide >= units && eff_w >= eff_n - 0.04;
+}
+
+GemmShape make_shape(const Record& r, int bn, int cta_group, bool wide = false) {
     const bool varlen = r.kernel_id == PB200_K_GROUPED_GEMM_VARLEN;
     const int64_t G = is_grouped(r.kernel_id) && !varlen ? r.dims[0] : 1;
     const int64_t M = r.dims[r.n_dims - 3], N = r.dims[r.n_dims - 2], K = r.dims[r.n_dims - 1];
     const bool swiglu = r.kernel_id == PB200_K_GROUPED_GEMM_SWIGLU;
     GemmShape s;
     s.n_experts = varlen ? (int)r.dims[0] : 0;
-    s.tiles_m = (int)(M / (BM * cta_group));
+    s.tiles_m = (int)(M / (BM * cta_group * (wide ? 2 : 1)));
     s.tiles_n = swiglu ? (int)(N / 128) : (int)(N / bn);
     s.k_tiles = (int)(K / BK);
     s.groups = (int)G;
@@ -506,6 +565,7 @@ GemmShape make_shape(const Record& r, int bn, int cta_group) {
     s.up_row_off = swiglu ? (int)N : 0;
     int band = (int)r.dims[7];            // stored by plan_gemm
     s.band = band < 1 ? 1 : (band > s.tiles_m ? s.tiles_m : band);
+    if (wide && (int)r.dims[6] == 0) s.band = s.band > 8 ? 8 : s.band;   // default band: 8 wide row blocks
     if (varlen) s.band = 1;     // row blocks in order, so that the active ones are a prefix of the tile list
     s.n_total = (int)N;
     return s;
@@ -528,9 +588,11 @@ int plan_gemm(Record& r, char* err) {
         return PB200_ERR_BAD_SHAPE;
     }
     int64_t band = 16;
-    if (r.n_dims == need + 1) { band = r.dims[need]; r.n_dims = need; }
+    const bool band_given = r.n_dims == need + 1;
+    if (band_given) { band = r.dims[need]; r.n_dims = need; }
     if (band < 1) { set_err(err, "raster band must be at least 1"); return PB200_ERR_BAD_SHAPE; }
     r.dims[7] = band;
+    r.dims[6] = band_given ? 1 : 0;
     const bool varlen = r.kernel_id == PB200_K_GROUPED_GEMM_VARLEN;
     const int64_t G = grouped && !varlen ? r.dims[0] : 1;
     if (varlen && (r.dims[0] < 1 || r.dims[0] > 65536)) { set_err(err, "expert count must be in [1, 65536]"); return PB200_ERR_BAD_SHAPE; }
@@ -553,7 +615,9 @@ int plan_gemm(Record& r, char* err) {
     g.grid[0] = (uint32_t)(units * cta_group); g.grid[1] = g.grid[2] = 1;
     g.block[0] = kThreads; g.block[1] = g.block[2] = 1;
     g.cluster[0] = (uint32_t)cta_group; g.cluster[1] = g.cluster[2] = 1;
-    g.smem_bytes = bn == 256 ? (cta_group == 2 ? SmemPlan<256, 2>::kTotal : SmemPlan<256, 1>::kTotal)
+    const bool wide = bn == 256 && use_wide_tile(r, sm_count() / cta_group);
+    g.smem_bytes = bn == 256 ? (cta_group == 2 ? (wide ? SmemPlan<256, 2, 1>::kTotal : SmemPlan<256, 2>::kTotal)
+                                               : (wide ? SmemPlan<256, 1, 1>::kTotal : SmemPlan<256, 1>::kTotal))
                  : bn == 128 ? SmemPlan<128, 1>::kTotal : SmemPlan<64, 1>::kTotal;
     g.n_inputs = varlen ? 3 : 2; g.n_outputs = push ? (uint32_t)r.dims[0] : 1;
     return PB200_OK;
@@ -572,7 +636,20 @@ int launch_gemm(const Record& r, cudaStream_t stream, void** p, char* err) {
         const int64_t units = sm_count() / cta_group;
         if ((int64_t)rr.geom.grid[0] > units * cta_group) rr.geom.grid[0] = (uint32_t)(units * cta_group);
     }
-    GemmShape shape = make_shape(rr, bn, cta_group);
+    const bool wide = !swiglu && bn == 256 && use_wide_tile(rr, sm_count() / cta_group);
+    GemmShape shape = make_shape(rr, bn, cta_group, wide);
+    if (wide) {
+#define PB200_WIDE_CASE(CG_, EPI_)                                                                       \
+        return bf16_out ? launch_variant<256, CG_, __nv_bfloat16, false, EPI_, 1>(rr, stream, p, shape, err) \
+                        : launch_variant<256, CG_, float, false, EPI_, 1>(rr, stream, p, shape, err);
+        if (r.kernel_id == PB200_K_GEMM_PUSH) {
+            if (cta_group == 2) { PB200_WIDE_CASE(2, 2) }
+            PB200_WIDE_CASE(1, 2)
+        }
+        if (cta_group == 2) { PB200_WIDE_CASE(2, 0) }
+        PB200_WIDE_CASE(1, 0)
+#undef PB200_WIDE_CASE
+    }
     if (swiglu)
         return bf16_out ? launch_variant<256, 1, __nv_bfloat16, false, 1>(rr, stream, p, shape, err)
                         : launch_variant<256, 1, float, false, 1>(rr, stream, p, shape, err);

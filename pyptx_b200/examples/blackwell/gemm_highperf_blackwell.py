@@ -27,6 +27,9 @@ GRID_MINOR_DIM = "n"
 GRID_TILE_WIDTH = 16
 
 
+_TILE_FLAGS = {"auto": 0, "narrow": 1 << 18, "wide": 1 << 19}
+
+
 def _out_flags(out_dtype: PtxType) -> int:
     assert out_dtype in (f32, bf16), f"out_dtype must be f32 or bf16, got {out_dtype}"
     return F_OUT_BF16 if out_dtype == bf16 else 0
@@ -34,13 +37,15 @@ def _out_flags(out_dtype: PtxType) -> int:
 
 def build_gemm(M: int, N: int, K: int, *, arch: str = "sm_100a", stages: int = STAGES,
                grid_minor_dim: str = GRID_MINOR_DIM, grid_tile_width: int = GRID_TILE_WIDTH,
-               out_dtype: PtxType = f32) -> NativeKernel:
+               out_dtype: PtxType = f32, tile: str = "auto") -> NativeKernel:
     """Kernel ``k(A[M,K] bf16, B_T[N,K] bf16) -> D[M,N]``.
 
     ``stages`` and ``grid_minor_dim`` are accepted and validated as in the
     reference; the native kernel sizes its own shared-memory ring and always
     rasterises M-fastest inside a band.  ``grid_tile_width`` is the number of
-    M-tiles per raster band.
+    M-tiles per raster band (with the default the kernel picks the band itself).
+    ``tile`` (an addition): ``"auto"`` runs large problems on double-height tiles
+    (256 x 256 per CTA), ``"narrow"`` / ``"wide"`` force one.
     """
     assert arch.startswith("sm_100"), "Blackwell GEMM is only implemented for sm_100*"
     assert M % BM == 0, f"M={M} must be divisible by {BM}"
@@ -49,20 +54,27 @@ def build_gemm(M: int, N: int, K: int, *, arch: str = "sm_100a", stages: int = S
     assert stages >= 2, "Blackwell GEMM requires at least two stages"
     assert grid_tile_width >= 1, "grid_tile_width must be at least 1"
     assert grid_minor_dim.lower() in {"m", "n"}, "grid_minor_dim must be 'm' or 'n'"
+    assert tile in _TILE_FLAGS, f"tile must be one of {sorted(_TILE_FLAGS)}, got {tile!r}"
+    dims = (M, N, K) if grid_tile_width == GRID_TILE_WIDTH else (M, N, K, grid_tile_width)
     return NativeKernel(
-        "blackwell_gemm", K_GEMM_1SM, (M, N, K, grid_tile_width),
+        "blackwell_gemm", K_GEMM_1SM, dims,
         in_specs=(Tile(M, K, bf16, Layout.TMA_128B, tma_box=(BM, BK)),
                   Tile(N, K, bf16, Layout.TMA_128B, tma_box=(BN, BK))),
         out_specs=(Tile(M, N, out_dtype, Layout.ROW),),
-        flags=_out_flags(out_dtype), arch=arch,
-        meta={"stages": stages, "grid_minor_dim": grid_minor_dim, "grid_tile_width": grid_tile_width},
+        flags=_out_flags(out_dtype) | _TILE_FLAGS[tile], arch=arch,
+        meta={"stages": stages, "grid_minor_dim": grid_minor_dim, "grid_tile_width": grid_tile_width, "tile": tile},
     )
 
 
 def build_gemm_2sm(M: int, N: int, K: int, *, arch: str = "sm_100a", stages: int = STAGES_2SM,
                    grid_minor_dim: str = GRID_MINOR_DIM, grid_tile_width: int = GRID_TILE_WIDTH,
-                   out_dtype: PtxType = f32) -> NativeKernel:
-    """2-SM variant: same call convention, ``M`` must divide by 256."""
+                   out_dtype: PtxType = f32, tile: str = "auto") -> NativeKernel:
+    """2-SM variant: same call convention, ``M`` must divide by 256.
+
+    ``tile`` (an addition): ``"auto"`` lets the kernel run large problems on 512 x 256 tiles
+    per CTA pair (``M % 512 == 0`` and enough tiles to fill the last wave) and the rest on
+    256 x 256; ``"narrow"`` / ``"wide"`` force one.  With the default ``grid_tile_width`` the
+    kernel picks the raster band itself."""
     assert arch.startswith("sm_100")
     assert M % (2 * BM) == 0, f"M={M} must be divisible by {2 * BM} for 2SM"
     assert N % BN == 0, f"N={N} must be divisible by {BN}"
@@ -70,13 +82,15 @@ def build_gemm_2sm(M: int, N: int, K: int, *, arch: str = "sm_100a", stages: int
     assert stages >= 2, "2SM Blackwell GEMM requires at least two stages"
     assert grid_tile_width >= 1, "grid_tile_width must be at least 1"
     assert grid_minor_dim.lower() in {"m", "n"}, "grid_minor_dim must be 'm' or 'n'"
+    assert tile in _TILE_FLAGS, f"tile must be one of {sorted(_TILE_FLAGS)}, got {tile!r}"
+    dims = (M, N, K) if grid_tile_width == GRID_TILE_WIDTH else (M, N, K, grid_tile_width)
     return NativeKernel(
-        "blackwell_gemm_2sm", K_GEMM_2SM, (M, N, K, grid_tile_width),
+        "blackwell_gemm_2sm", K_GEMM_2SM, dims,
         in_specs=(Tile(M, K, bf16, Layout.TMA_128B, tma_box=(BM, BK)),
                   Tile(N, K, bf16, Layout.TMA_128B, tma_box=(BN // 2, BK))),
         out_specs=(Tile(M, N, out_dtype, Layout.ROW),),
-        flags=_out_flags(out_dtype), arch=arch,
-        meta={"stages": stages, "grid_minor_dim": grid_minor_dim, "grid_tile_width": grid_tile_width},
+        flags=_out_flags(out_dtype) | _TILE_FLAGS[tile], arch=arch,
+        meta={"stages": stages, "grid_minor_dim": grid_minor_dim, "grid_tile_width": grid_tile_width, "tile": tile},
     )
 
 

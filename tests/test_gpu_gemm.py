@@ -301,3 +301,42 @@ def test_variable_size_grouped_gemm_leaves_capacity_rows_alone():
 def test_no_device_wait_gave_up():
     from pyptx_b200 import _native
     _native.device_status()
+
+
+# ---- tile shapes --------------------------------------------------------------------
+
+@pytest.mark.parametrize("kind", ["1sm", "2sm"])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(512, 256, 64), (1024, 768, 576), (2560, 512, 1024)])
+def test_double_height_tile_equals_single_height(kind, out_dtype, shape):
+    """The double-height tile (two A blocks per B block, no second accumulator buffer) must give
+    the single-height kernel's bits: same MMAs, same accumulation order along K."""
+    from pyptx_b200.types import f32
+    M, N, K = shape
+    a, bt = inputs.gemm_inputs(M, N, K)
+    spec = bf16 if out_dtype == torch.bfloat16 else f32
+    wide = BUILDERS[kind](M, N, K, tile="wide", out_dtype=spec)
+    narrow = BUILDERS[kind](M, N, K, tile="narrow", out_dtype=spec)
+    ad, bd = a.cuda(), bt.cuda()
+    dw, dn = wide(ad, bd), narrow(ad, bd)
+    check_bf16_matmul(dw.cpu(), formulas.gemm_ref(a, bt), 1e-2 if out_dtype == torch.bfloat16 else 1e-4)
+    assert torch.equal(dw, dn)
+
+
+@pytest.mark.parametrize("kind", ["1sm", "2sm"])
+def test_double_height_tile_many_tiles_per_cta(kind):
+    """Three to four double-height tiles per CTA (pair): both accumulators are reused and their
+    barrier phases wrap."""
+    M, N, K = 4096, 8192, 128
+    a, bt = inputs.gemm_inputs(M, N, K)
+    ad, bd = a.cuda(), bt.cuda()
+    dw = BUILDERS[kind](M, N, K, tile="wide")(ad, bd)
+    dn = BUILDERS[kind](M, N, K, tile="narrow")(ad, bd)
+    assert torch.equal(dw, dn)
+    rows = slice(1024, 1024 + 256)
+    check_bf16_matmul(dw[rows].cpu(), formulas.gemm_ref(a[rows], bt), 1e-4)
+
+
+def test_tile_choice_is_validated():
+    with pytest.raises(AssertionError, match="tile must be one of"):
+        build_gemm_2sm(512, 256, 64, tile="tall")

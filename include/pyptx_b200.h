@@ -148,6 +148,14 @@ extern "C" {
 #define PB200_F_OUT_BF16       (1ull << 0)  /* round the output to bf16            */
 #define PB200_F_CAUSAL         (1ull << 1)  /* attention: lower-triangular mask    */
 #define PB200_F_K_TRANSPOSED   (1ull << 2)  /* attention: K given as (d, N_seq)    */
+/* Dense GEMM epilogue (PB200_K_GEMM_1SM / _2SM): D = act(A B_T^T + bias).  The reference's GEMMs
+ * have a plain store epilogue (examples/blackwell/gemm_highperf_blackwell.py:283-311); these fuse
+ * the bias add / activation a caller would otherwise run as a second pass over D.             */
+#define PB200_F_BIAS           (1ull << 3)  /* third input: bias[N] f32, added per column  */
+#define PB200_F_ACT_RELU       (1ull << 4)
+#define PB200_F_ACT_GELU       (2ull << 4)  /* 0.5 x (1 + erf(x / sqrt 2))                 */
+#define PB200_F_ACT_SILU       (3ull << 4)
+#define PB200_F_ACT_MASK       (3ull << 4)
 
 /* Launch geometry of a handle, as the reference's Kernel object exposes it
  * (pyptx/kernel.py:402-447: grid, block, cluster, smem). */

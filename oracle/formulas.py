@@ -44,6 +44,21 @@ def gemm_ref(a: torch.Tensor, b_t: torch.Tensor) -> torch.Tensor:
     return a.float() @ b_t.float().t()
 
 
+def gemm_bias_act_ref(a: torch.Tensor, b_t: torch.Tensor, bias: torch.Tensor | None = None,
+                      activation: str | None = None) -> torch.Tensor:
+    """``act(a.float() @ b.float() + bias)``: the reference's GEMM formula
+    (examples/blackwell/gemm_highperf_blackwell.py:1268) followed by the torch ops a caller
+    would apply to its result (``F.relu`` / ``F.gelu`` (erf form) / ``F.silu``, the last as
+    in examples/blackwell/swiglu.py:66).  The reference has no fused form."""
+    d = gemm_ref(a, b_t)
+    if bias is not None:
+        d = d + bias.float()
+    if activation is None:
+        return d
+    fn = torch.nn.functional
+    return {"relu": fn.relu, "gelu": fn.gelu, "silu": fn.silu}[activation](d)
+
+
 def grouped_gemm_ref(a2: torch.Tensor, b_t2: torch.Tensor, G: int) -> torch.Tensor:
     """``einsum("gmk,gkn->gmn")`` in fp32 (examples/blackwell/grouped_gemm.py:306) on the
     stacked operands ``a2[G*M,K]`` and ``b_t2[G*N,K]`` (:302-303); returns ``[G*M, N]``."""

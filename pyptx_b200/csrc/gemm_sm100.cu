@@ -68,7 +68,38 @@ struct GemmShape {
     int n_total;            // leading dimension of D (elements)
     int n_experts;          // variable-size grouped GEMM: number of experts (0 = fixed-size problem)
     int up_row_off;         // EPI 1: row offset of an expert's "up" weights inside its block of B_T (= F)
+    int act;                // EPI 3: 0 none, 1 relu, 2 gelu (erf form), 3 silu
+    int has_bias;           // EPI 3: aux points at bias[N] (f32)
 };
+
+// EPI = 3: D = act(accumulator + bias[column]).
+__device__ __forceinline__ float bias_act(float x, int act) {
+    switch (act) {
+        case 1: return fmaxf(x, 0.0f);
+        case 2: return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
+        case 3: return __fdividef(x, 1.0f + __expf(-x));
+        default: return x;
+    }
+}
+// v[0..31] += bias[col .. col+31] (the same 32 values for every lane: broadcast loads), then act.
+__device__ __forceinline__ void apply_bias_act(uint32_t (&v)[32], const float* __restrict__ bias, int col,
+                                               const GemmShape& shape) {
+    if (shape.has_bias) {
+        const float4* bp = reinterpret_cast<const float4*>(bias + col);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float4 b = __ldg(bp + j);
+            v[4 * j] = __float_as_uint(__uint_as_float(v[4 * j]) + b.x);
+            v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + b.y);
+            v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + b.z);
+            v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + b.w);
+        }
+    }
+    if (shape.act) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(bias_act(__uint_as_float(v[i]), shape.act));
+    }
+}
 
 template <int BN, int CTA_GROUP, int WIDE = 0>
 struct SmemPlan {
@@ -138,6 +169,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const __grid_constant__ typename PushParam<EPI>::type push) {
     using Plan = SmemPlan<BN, CTA_GROUP, WIDE>;
     static_assert(WIDE == 0 || (BN == 256 && EPI != 1), "the wide tile is a 256-column variant of the dense kernels");
+    static_assert(EPI != 3 || (BN == 256 && !DIRECT), "the bias/activation epilogue is a dense, TMA-store variant");
     constexpr int kSub = 1 + WIDE;                            // 256-row blocks of A per tile
     constexpr int kStages = Plan::kStages;
     constexpr int kChunkCols = 128 / (int)sizeof(OutT);     // columns per 128-byte store row
@@ -369,11 +401,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 } else if (sizeof(OutT) == 4) {
                     tmem_ld_32x32b_x32(t_row + (uint32_t)(c * 32), v);
                     tmem_ld_wait();
+                    if (EPI == 3) apply_bias_act(v, reinterpret_cast<const float*>(expert_offsets), col0 + c * 32, shape);
                 } else {
                     uint32_t lo[32], hi[32];
                     tmem_ld_32x32b_x32(t_row + (uint32_t)(c * 64), lo);
                     tmem_ld_32x32b_x32(t_row + (uint32_t)(c * 64 + 32), hi);
                     tmem_ld_wait();
+                    if (EPI == 3) {
+                        apply_bias_act(lo, reinterpret_cast<const float*>(expert_offsets), col0 + c * 64, shape);
+                        apply_bias_act(hi, reinterpret_cast<const float*>(expert_offsets), col0 + c * 64 + 32, shape);
+                    }
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(lo[2 * i]), __uint_as_float(lo[2 * i + 1]));
@@ -470,7 +507,7 @@ int launch_variant(const Record& r, cudaStream_t stream, void** p, const GemmSha
     const int64_t G = is_grouped(r.kernel_id) && !varlen ? r.dims[0] : 1;     // varlen: M is already the stacked total
     const int64_t M = r.dims[r.n_dims - 3], N = r.dims[r.n_dims - 2], K = r.dims[r.n_dims - 1];
     const int64_t n_experts = varlen ? r.dims[0] : 0;
-    void* out_ptr = p[varlen ? 3 : 2];
+    void* out_ptr = p[varlen || (r.flags & PB200_F_BIAS) ? 3 : 2];
     // EPI 1: dims carry F; B_T holds 2F rows per expert (gate rows, then up rows), D has F columns.
     const int64_t b_rows = EPI == 1 ? 2 * N : varlen ? n_experts * N : N;
     const uint32_t b_box_rows = EPI == 1 ? (uint32_t)(BN / 2) : (uint32_t)Plan::kBRows;
@@ -522,7 +559,8 @@ int launch_variant(const Record& r, cudaStream_t stream, void** p, const GemmSha
             if (rc) return rc;
         }
     }
-    const int* expert_offsets = varlen ? (const int*)p[2] : nullptr;
+    const bool with_bias = EPI == 3 && (r.flags & PB200_F_BIAS);
+    const int* expert_offsets = varlen || with_bias ? (const int*)p[2] : nullptr;   // aux pointer: offsets or bias
     int* status = device_status_ptr();
     int kid = r.kernel_id;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, td, d_ptr, shape, status, kid, expert_offsets, push);
@@ -567,6 +605,8 @@ GemmShape make_shape(const Record& r, int bn, int cta_group, bool wide = false) 
     s.rows_per_group_a = (int)M;
     s.rows_per_group_b = swiglu ? (int)(2 * N) : (int)N;
     s.up_row_off = swiglu ? (int)N : 0;
+    s.has_bias = (r.flags & PB200_F_BIAS) ? 1 : 0;
+    s.act = (int)((r.flags & PB200_F_ACT_MASK) >> 4);
     int band = (int)r.dims[7];            // stored by plan_gemm
     s.band = band < 1 ? 1 : (band > s.tiles_m ? s.tiles_m : band);
     if (wide && (int)r.dims[6] == 0) s.band = s.band > 8 ? 8 : s.band;   // default band: 8 wide row blocks
@@ -602,6 +642,14 @@ int plan_gemm(Record& r, char* err) {
     if (varlen && (r.dims[0] < 1 || r.dims[0] > 65536)) { set_err(err, "expert count must be in [1, 65536]"); return PB200_ERR_BAD_SHAPE; }
     const int64_t M = r.dims[need - 3], N = r.dims[need - 2], K = r.dims[need - 1];
     const int cta_group = cta_group_of(r);
+    if ((r.flags & (PB200_F_BIAS | PB200_F_ACT_MASK)) && r.kernel_id != PB200_K_GEMM_1SM && r.kernel_id != PB200_K_GEMM_2SM) {
+        set_err(err, "bias / activation flags apply to the dense GEMM kernels only");
+        return PB200_ERR_BAD_SHAPE;
+    }
+    if ((r.flags & (PB200_F_BIAS | PB200_F_ACT_MASK)) && (r.flags & kDebugDirectStore)) {
+        set_err(err, "the direct-store debug path has no bias / activation epilogue");
+        return PB200_ERR_BAD_SHAPE;
+    }
     if (G < 1 || M < 1 || N < 1 || K < 1) { set_err(err, "G, M, N, K must be positive"); return PB200_ERR_BAD_SHAPE; }
     if (M % (BM * cta_group) != 0) { set_err(err, "M=%lld must be divisible by %d", (long long)M, BM * cta_group); return PB200_ERR_BAD_SHAPE; }
     if (K % BK != 0) { set_err(err, "K=%lld must be divisible by %d", (long long)K, BK); return PB200_ERR_BAD_SHAPE; }
@@ -623,7 +671,7 @@ int plan_gemm(Record& r, char* err) {
     g.smem_bytes = bn == 256 ? (cta_group == 2 ? (wide ? SmemPlan<256, 2, 1>::kTotal : SmemPlan<256, 2>::kTotal)
                                                : (wide ? SmemPlan<256, 1, 1>::kTotal : SmemPlan<256, 1>::kTotal))
                  : bn == 128 ? SmemPlan<128, 1>::kTotal : SmemPlan<64, 1>::kTotal;
-    g.n_inputs = varlen ? 3 : 2; g.n_outputs = push ? (uint32_t)r.dims[0] : 1;
+    g.n_inputs = varlen || (r.flags & PB200_F_BIAS) ? 3 : 2; g.n_outputs = push ? (uint32_t)r.dims[0] : 1;
     return PB200_OK;
 }
 
@@ -650,6 +698,10 @@ int launch_gemm(const Record& r, cudaStream_t stream, void** p, char* err) {
             if (cta_group == 2) { PB200_WIDE_CASE(2, 2) }
             PB200_WIDE_CASE(1, 2)
         }
+        if (r.flags & (PB200_F_BIAS | PB200_F_ACT_MASK)) {
+            if (cta_group == 2) { PB200_WIDE_CASE(2, 3) }
+            PB200_WIDE_CASE(1, 3)
+        }
         if (direct) {
             if (cta_group == 2)
                 return bf16_out ? launch_variant<256, 2, __nv_bfloat16, true, 0, 1>(rr, stream, p, shape, err)
@@ -670,6 +722,13 @@ int launch_gemm(const Record& r, cudaStream_t stream, void** p, char* err) {
                             : launch_variant<256, 2, float, false, 2>(rr, stream, p, shape, err);
         return bf16_out ? launch_variant<256, 1, __nv_bfloat16, false, 2>(rr, stream, p, shape, err)
                         : launch_variant<256, 1, float, false, 2>(rr, stream, p, shape, err);
+    }
+    if (r.flags & (PB200_F_BIAS | PB200_F_ACT_MASK)) {
+        if (cta_group == 2)
+            return bf16_out ? launch_variant<256, 2, __nv_bfloat16, false, 3>(rr, stream, p, shape, err)
+                            : launch_variant<256, 2, float, false, 3>(rr, stream, p, shape, err);
+        return bf16_out ? launch_variant<256, 1, __nv_bfloat16, false, 3>(rr, stream, p, shape, err)
+                        : launch_variant<256, 1, float, false, 3>(rr, stream, p, shape, err);
     }
 #define PB200_GEMM_CASE(BN_, CG_)                                                                       \
     if (bn == BN_ && cta_group == CG_) {                                                                \

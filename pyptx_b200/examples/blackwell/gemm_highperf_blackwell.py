@@ -13,7 +13,7 @@ Both take ``A[M,K]`` bf16 and ``B_T[N,K]`` bf16 (the caller passes
 """
 from __future__ import annotations
 
-from ..._ids import F_OUT_BF16, K_GEMM_1SM, K_GEMM_2SM
+from ..._ids import F_ACT_GELU, F_ACT_RELU, F_ACT_SILU, F_BIAS, F_OUT_BF16, K_GEMM_1SM, K_GEMM_2SM
 from ...kernel import NativeKernel
 from ...specs import Layout, Tile
 from ...types import PtxType, bf16, f32
@@ -28,6 +28,15 @@ GRID_TILE_WIDTH = 16
 
 
 _TILE_FLAGS = {"auto": 0, "narrow": 1 << 18, "wide": 1 << 19}
+_ACT_FLAGS = {None: 0, "relu": F_ACT_RELU, "gelu": F_ACT_GELU, "silu": F_ACT_SILU}
+
+
+def _epilogue(N: int, bias: bool, activation):
+    """Flags and extra input spec of the fused epilogue ``D = act(A @ B_T.T + bias)``."""
+    assert activation in _ACT_FLAGS, f"activation must be one of {list(_ACT_FLAGS)}, got {activation!r}"
+    flags = _ACT_FLAGS[activation] | (F_BIAS if bias else 0)
+    extra = (Tile(N, f32, Layout.ROW),) if bias else ()
+    return flags, extra
 
 
 def _out_flags(out_dtype: PtxType) -> int:
@@ -37,7 +46,8 @@ def _out_flags(out_dtype: PtxType) -> int:
 
 def build_gemm(M: int, N: int, K: int, *, arch: str = "sm_100a", stages: int = STAGES,
                grid_minor_dim: str = GRID_MINOR_DIM, grid_tile_width: int = GRID_TILE_WIDTH,
-               out_dtype: PtxType = f32, tile: str = "auto") -> NativeKernel:
+               out_dtype: PtxType = f32, tile: str = "auto", bias: bool = False,
+               activation: str | None = None) -> NativeKernel:
     """Kernel ``k(A[M,K] bf16, B_T[N,K] bf16) -> D[M,N]``.
 
     ``stages`` and ``grid_minor_dim`` are accepted and validated as in the
@@ -46,6 +56,9 @@ def build_gemm(M: int, N: int, K: int, *, arch: str = "sm_100a", stages: int = S
     M-tiles per raster band (with the default the kernel picks the band itself).
     ``tile`` (an addition): ``"auto"`` runs large problems on double-height tiles
     (256 x 256 per CTA), ``"narrow"`` / ``"wide"`` force one.
+    ``bias`` / ``activation`` (additions): with ``bias=True`` the kernel takes a third
+    input ``bias[N]`` (f32) and computes ``act(A @ B_T.T + bias)`` in its epilogue;
+    ``activation`` is ``None``, ``"relu"``, ``"gelu"`` (erf form) or ``"silu"``.
     """
     assert arch.startswith("sm_100"), "Blackwell GEMM is only implemented for sm_100*"
     assert M % BM == 0, f"M={M} must be divisible by {BM}"
@@ -56,20 +69,23 @@ def build_gemm(M: int, N: int, K: int, *, arch: str = "sm_100a", stages: int = S
     assert grid_minor_dim.lower() in {"m", "n"}, "grid_minor_dim must be 'm' or 'n'"
     assert tile in _TILE_FLAGS, f"tile must be one of {sorted(_TILE_FLAGS)}, got {tile!r}"
     dims = (M, N, K) if grid_tile_width == GRID_TILE_WIDTH else (M, N, K, grid_tile_width)
+    epi_flags, epi_inputs = _epilogue(N, bias, activation)
     return NativeKernel(
         "blackwell_gemm", K_GEMM_1SM, dims,
         in_specs=(Tile(M, K, bf16, Layout.TMA_128B, tma_box=(BM, BK)),
-                  Tile(N, K, bf16, Layout.TMA_128B, tma_box=(BN, BK))),
+                  Tile(N, K, bf16, Layout.TMA_128B, tma_box=(BN, BK))) + epi_inputs,
         out_specs=(Tile(M, N, out_dtype, Layout.ROW),),
-        flags=_out_flags(out_dtype) | _TILE_FLAGS[tile], arch=arch,
+        flags=_out_flags(out_dtype) | _TILE_FLAGS[tile] | epi_flags, arch=arch,
         meta={"stages": stages, "grid_minor_dim": grid_minor_dim, "grid_tile_width": grid_tile_width, "tile": tile},
     )
 
 
 def build_gemm_2sm(M: int, N: int, K: int, *, arch: str = "sm_100a", stages: int = STAGES_2SM,
                    grid_minor_dim: str = GRID_MINOR_DIM, grid_tile_width: int = GRID_TILE_WIDTH,
-                   out_dtype: PtxType = f32, tile: str = "auto") -> NativeKernel:
-    """2-SM variant: same call convention, ``M`` must divide by 256.
+                   out_dtype: PtxType = f32, tile: str = "auto", bias: bool = False,
+                   activation: str | None = None) -> NativeKernel:
+    """2-SM variant: same call convention (``bias`` / ``activation`` as for :func:`build_gemm`),
+    ``M`` must divide by 256.
 
     ``tile`` (an addition): ``"auto"`` lets the kernel run large problems on 512 x 256 tiles
     per CTA pair (``M % 512 == 0`` and enough tiles to fill the last wave) and the rest on
@@ -84,12 +100,13 @@ def build_gemm_2sm(M: int, N: int, K: int, *, arch: str = "sm_100a", stages: int
     assert grid_minor_dim.lower() in {"m", "n"}, "grid_minor_dim must be 'm' or 'n'"
     assert tile in _TILE_FLAGS, f"tile must be one of {sorted(_TILE_FLAGS)}, got {tile!r}"
     dims = (M, N, K) if grid_tile_width == GRID_TILE_WIDTH else (M, N, K, grid_tile_width)
+    epi_flags, epi_inputs = _epilogue(N, bias, activation)
     return NativeKernel(
         "blackwell_gemm_2sm", K_GEMM_2SM, dims,
         in_specs=(Tile(M, K, bf16, Layout.TMA_128B, tma_box=(BM, BK)),
-                  Tile(N, K, bf16, Layout.TMA_128B, tma_box=(BN // 2, BK))),
+                  Tile(N, K, bf16, Layout.TMA_128B, tma_box=(BN // 2, BK))) + epi_inputs,
         out_specs=(Tile(M, N, out_dtype, Layout.ROW),),
-        flags=_out_flags(out_dtype) | _TILE_FLAGS[tile], arch=arch,
+        flags=_out_flags(out_dtype) | _TILE_FLAGS[tile] | epi_flags, arch=arch,
         meta={"stages": stages, "grid_minor_dim": grid_minor_dim, "grid_tile_width": grid_tile_width, "tile": tile},
     )
 

@@ -32,8 +32,10 @@ def test_header_constants_match_python_ids():
             assert int(value) == _native.ERR_LEN
         else:
             assert getattr(_ids, name) == int(value), name
-    for name, shift in re.findall(r"#define PB200_(F_\w+)\s+\(1ull << (\d+)\)", header):
-        assert getattr(_ids, name) == 1 << int(shift), name
+    flags = re.findall(r"#define PB200_(F_\w+)\s+\((\d+)ull << (\d+)\)", header)
+    assert len(flags) >= 8
+    for name, mult, shift in flags:
+        assert getattr(_ids, name) == int(mult) << int(shift), name
 
 
 def test_version_and_arch(lib):

@@ -340,3 +340,38 @@ def test_double_height_tile_many_tiles_per_cta(kind):
 def test_tile_choice_is_validated():
     with pytest.raises(AssertionError, match="tile must be one of"):
         build_gemm_2sm(512, 256, 64, tile="tall")
+
+
+# ---- fused bias / activation epilogue -------------------------------------------------
+
+@pytest.mark.parametrize("kind", ["1sm", "2sm"])
+@pytest.mark.parametrize("bias", [False, True])
+@pytest.mark.parametrize("activation", [None, "relu", "gelu", "silu"])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_bias_activation_epilogue(kind, bias, activation, out_dtype):
+    from pyptx_b200.types import f32
+    if not bias and activation is None:
+        pytest.skip("plain epilogue is covered above")
+    M, N, K = 512, 768, 256
+    a, bt = inputs.gemm_inputs(M, N, K)
+    g = torch.Generator().manual_seed(M * 31 + N)
+    b = torch.randn(N, generator=g) * 0.5
+    ref = formulas.gemm_bias_act_ref(a, bt, b if bias else None, activation)
+    spec = bf16 if out_dtype == torch.bfloat16 else f32
+    for tile in ("narrow", "wide"):
+        k = BUILDERS[kind](M, N, K, out_dtype=spec, bias=bias, activation=activation, tile=tile)
+        assert len(k.in_specs) == (3 if bias else 2)
+        args = (a.cuda(), bt.cuda()) + ((b.cuda(),) if bias else ())
+        d = k(*args)
+        check_bf16_matmul(d.cpu(), ref, 1e-2 if out_dtype == torch.bfloat16 else 2e-5)
+
+
+def test_bias_epilogue_rejects_wrong_inputs():
+    k = build_gemm(256, 256, 64, bias=True)
+    a, bt = inputs.gemm_inputs(256, 256, 64)
+    with pytest.raises((TypeError, ValueError)):
+        k(a.cuda(), bt.cuda())                                   # bias missing
+    with pytest.raises(TypeError):
+        k(a.cuda(), bt.cuda(), torch.zeros(256, dtype=torch.bfloat16, device="cuda"))
+    with pytest.raises(AssertionError, match="activation must be one of"):
+        build_gemm(256, 256, 64, activation="tanh")

@@ -152,3 +152,14 @@ def test_error_metrics():
     assert abs(formulas.rel_fro(r * 1.01, r) - 0.01) < 1e-6
     assert abs(formulas.max_scaled_err(r + 0.5, r) - 0.5) < 1e-12
     assert oracle.rms_norm_ref is formulas.rms_norm_ref
+
+
+def test_gemm_bias_act_ref_composes_the_reference_formulas():
+    a, bt = inputs.gemm_inputs(128, 256, 64)
+    bias = torch.linspace(-1, 1, 256)
+    base = formulas.gemm_ref(a, bt)
+    assert torch.equal(formulas.gemm_bias_act_ref(a, bt), base)
+    assert torch.equal(formulas.gemm_bias_act_ref(a, bt, bias, "relu"), torch.relu(base + bias))
+    assert torch.allclose(formulas.gemm_bias_act_ref(a, bt, None, "silu"), base * torch.sigmoid(base), atol=1e-6)
+    x = base + bias
+    assert torch.allclose(formulas.gemm_bias_act_ref(a, bt, bias, "gelu"), 0.5 * x * (1 + torch.erf(x / 2 ** 0.5)), atol=1e-6)

@@ -53,6 +53,7 @@ struct FmhaParams {
     int k_transposed;
     float scale_log2;  // sm_scale * log2(e)
     int causal_offset; // s_kv - s_q: query i sees keys j <= i + offset
+    int hd;            // head dimension of the tensors in global memory (multiple of 8, <= HD)
 };
 
 template <int HD, bool P_SMEM>
@@ -459,20 +460,24 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         if (ok && n > 0) {
             tc_fence_after_sync();
             const float inv = 1.0f / l;
-            OutT* dst = out + ((size_t)bh * prm.s_q + row) * HD;
+            // The tensors' head dimension may be smaller than the tile's (see launch_fmha): rows are
+            // prm.hd apart and only the first prm.hd columns exist.
+            OutT* dst = out + ((size_t)bh * prm.s_q + row) * prm.hd;
             const bool row_exists = row < prm.s_q;          // a partial last query tile computes padding rows
 #pragma unroll 1
             for (int c = 0; c < HD / 32; ++c) {
                 uint32_t o[32];
                 tmem_ld_32x32b_x32(to + (uint32_t)(c * 32), o);
                 tmem_ld_wait();
-                if (!row_exists) continue;
+                if (!row_exists || c * 32 >= prm.hd) continue;
+                const int cols_here = prm.hd - c * 32;        // multiple of 8; >= 32 for a full chunk
                 if (sizeof(OutT) == 4) {
 #pragma unroll
                     for (int i = 0; i < 8; ++i)
-                        reinterpret_cast<float4*>(dst + c * 32)[i] =
-                            make_float4(__uint_as_float(o[4 * i]) * inv, __uint_as_float(o[4 * i + 1]) * inv,
-                                        __uint_as_float(o[4 * i + 2]) * inv, __uint_as_float(o[4 * i + 3]) * inv);
+                        if (4 * i < cols_here)
+                            reinterpret_cast<float4*>(dst + c * 32)[i] =
+                                make_float4(__uint_as_float(o[4 * i]) * inv, __uint_as_float(o[4 * i + 1]) * inv,
+                                            __uint_as_float(o[4 * i + 2]) * inv, __uint_as_float(o[4 * i + 3]) * inv);
                 } else {
                     uint32_t pk[16];
 #pragma unroll
@@ -482,7 +487,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     }
 #pragma unroll
                     for (int i = 0; i < 4; ++i)
-                        reinterpret_cast<uint4*>(dst + c * 32)[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+                        if (8 * i < cols_here)
+                            reinterpret_cast<uint4*>(dst + c * 32)[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
                 }
             }
         }
@@ -511,31 +517,36 @@ int launch_fmha(const Record& r, cudaStream_t stream, void** p, char* err) {
         attr_set.fetch_or(1ull << (dev & 63), std::memory_order_relaxed);
     }
     const int64_t BH = r.dims[0], SQ = r.dims[1], SKV = r.dims[2];
+    // Head dimension of the tensors.  The kernel's tiles are HD (64 or 128) wide; a smaller head
+    // dimension keeps the 64-element boxes, and TMA fills the columns (rows, for K given
+    // transposed) past the tensor's extent with zeros: zero columns of Q and K add nothing to
+    // Q K^T, zero columns of V give zero columns of O, which the epilogue does not store.
+    const int64_t hd = r.dims[3];
     const bool kt = (r.flags & PB200_F_K_TRANSPOSED) != 0;
     CUtensorMap tq, tk, tv;
     {
-        uint64_t dims[3] = {(uint64_t)HD, (uint64_t)SQ, (uint64_t)BH};
-        uint64_t str[2] = {(uint64_t)HD * 2, (uint64_t)SQ * HD * 2};
+        uint64_t dims[3] = {(uint64_t)hd, (uint64_t)SQ, (uint64_t)BH};
+        uint64_t str[2] = {(uint64_t)hd * 2, (uint64_t)SQ * hd * 2};
         uint32_t box[3] = {64, kQTile, 1};
         int rc = make_tensor_map(&tq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, p[0], dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, err);
         if (rc) return rc;
     }
     if (!kt) {
-        uint64_t dims[3] = {(uint64_t)HD, (uint64_t)SKV, (uint64_t)BH};
-        uint64_t str[2] = {(uint64_t)HD * 2, (uint64_t)SKV * HD * 2};
+        uint64_t dims[3] = {(uint64_t)hd, (uint64_t)SKV, (uint64_t)BH};
+        uint64_t str[2] = {(uint64_t)hd * 2, (uint64_t)SKV * hd * 2};
         uint32_t box[3] = {64, kKvTile, 1};
         int rc = make_tensor_map(&tk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, p[1], dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, err);
         if (rc) return rc;
     } else {
-        uint64_t dims[3] = {(uint64_t)SKV, (uint64_t)HD, (uint64_t)BH};
-        uint64_t str[2] = {(uint64_t)SKV * 2, (uint64_t)SKV * HD * 2};
+        uint64_t dims[3] = {(uint64_t)SKV, (uint64_t)hd, (uint64_t)BH};
+        uint64_t str[2] = {(uint64_t)SKV * 2, (uint64_t)SKV * hd * 2};
         uint32_t box[3] = {64, (uint32_t)HD, 1};
         int rc = make_tensor_map(&tk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, p[1], dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, err);
         if (rc) return rc;
     }
     {
-        uint64_t dims[3] = {(uint64_t)HD, (uint64_t)SKV, (uint64_t)BH};
-        uint64_t str[2] = {(uint64_t)HD * 2, (uint64_t)SKV * HD * 2};
+        uint64_t dims[3] = {(uint64_t)hd, (uint64_t)SKV, (uint64_t)BH};
+        uint64_t str[2] = {(uint64_t)hd * 2, (uint64_t)SKV * hd * 2};
         uint32_t box[3] = {64, kKvTile, 1};
         int rc = make_tensor_map(&tv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, p[2], dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, err);
         if (rc) return rc;
@@ -546,6 +557,7 @@ int launch_fmha(const Record& r, cudaStream_t stream, void** p, char* err) {
     prm.k_transposed = kt ? 1 : 0;
     prm.scale_log2 = (float)(r.fparams[0] * 1.4426950408889634);
     prm.causal_offset = (int)(SKV - SQ);
+    prm.hd = (int)hd;
     dim3 grid(r.geom.grid[0], r.geom.grid[1], 1);
     kernel<<<grid, kFmhaThreads, L::kTotal, stream>>>(tq, tk, tv, (OutT*)p[3], prm, device_status_ptr());
     cudaError_t e = cudaGetLastError();
@@ -560,7 +572,8 @@ int plan_attention(Record& r, char* err) {
     if (r.n_dims != 4) { set_err(err, "attention needs dims = {batch*heads, S_q, S_kv, head_dim}, got %d dims", r.n_dims); return PB200_ERR_BAD_SHAPE; }
     const int64_t BH = r.dims[0], SQ = r.dims[1], SKV = r.dims[2], HD = r.dims[3];
     if (BH < 1 || SQ < 1 || SKV < 1) { set_err(err, "batch*heads, S_q, S_kv must be positive"); return PB200_ERR_BAD_SHAPE; }
-    if (HD != 64 && HD != 128) { set_err(err, "head_dim=%lld must be 64 or 128", (long long)HD); return PB200_ERR_BAD_SHAPE; }
+    if (HD < 8 || HD > 128 || HD % 8 != 0) { set_err(err, "head_dim=%lld must be a multiple of 8 in [8, 128]", (long long)HD); return PB200_ERR_BAD_SHAPE; }
+    const int tile_hd = HD <= 64 ? 64 : 128;
     if ((r.flags & PB200_F_K_TRANSPOSED) && SKV % 8 != 0) {
         set_err(err, "S_kv=%lld must be divisible by 8 when K is given transposed (16-byte row pitch)", (long long)SKV);
         return PB200_ERR_BAD_SHAPE;
@@ -568,13 +581,13 @@ int plan_attention(Record& r, char* err) {
     if (SQ > 0x7fffffffLL / 256 || SKV > 0x7fffffffLL / 256) { set_err(err, "sequence length too large"); return PB200_ERR_BAD_SHAPE; }
     if ((r.flags & PB200_F_CAUSAL) && SKV < SQ) { set_err(err, "causal attention needs S_kv >= S_q"); return PB200_ERR_BAD_SHAPE; }
     if (BH > 65535) { set_err(err, "batch*heads=%lld exceeds 65535", (long long)BH); return PB200_ERR_BAD_SHAPE; }
-    if ((r.flags & kDebugPSmem) && HD != 64) { set_err(err, "the shared-memory P variant exists for head_dim 64 only"); return PB200_ERR_BAD_SHAPE; }
+    if ((r.flags & kDebugPSmem) && tile_hd != 64) { set_err(err, "the shared-memory P variant exists for head_dim 64 only"); return PB200_ERR_BAD_SHAPE; }
     if (r.n_fparams < 1 || r.fparams[0] == 0.0) { r.fparams[0] = 1.0 / std::sqrt((double)HD); r.n_fparams = 1; }
     pb200_geometry& g = r.geom;
     g.grid[0] = (uint32_t)((SQ + 2 * kQTile - 1) / (2 * kQTile)); g.grid[1] = (uint32_t)BH; g.grid[2] = 1;
     g.block[0] = kFmhaThreads; g.block[1] = g.block[2] = 1;
     g.cluster[0] = g.cluster[1] = g.cluster[2] = 1;
-    g.smem_bytes = HD == 64 ? ((r.flags & kDebugPSmem) ? FmhaSmem<64, true>::kTotal : FmhaSmem<64, false>::kTotal)
+    g.smem_bytes = tile_hd == 64 ? ((r.flags & kDebugPSmem) ? FmhaSmem<64, true>::kTotal : FmhaSmem<64, false>::kTotal)
                             : FmhaSmem<128, false>::kTotal;
     g.n_inputs = 3; g.n_outputs = 1;
     return PB200_OK;
@@ -584,7 +597,7 @@ int launch_attention(const Record& r, cudaStream_t stream, void** p, char* err) 
     const int64_t HD = r.dims[3];
     const bool bf16_out = (r.flags & PB200_F_OUT_BF16) != 0;
     const bool p_smem = (r.flags & kDebugPSmem) != 0;
-    if (HD == 64) {
+    if (HD <= 64) {
         if (p_smem) return bf16_out ? launch_fmha<64, __nv_bfloat16, true>(r, stream, p, err) : launch_fmha<64, float, true>(r, stream, p, err);
         return bf16_out ? launch_fmha<64, __nv_bfloat16, false>(r, stream, p, err) : launch_fmha<64, float, false>(r, stream, p, err);
     }

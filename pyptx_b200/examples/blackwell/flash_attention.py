@@ -5,7 +5,7 @@ statistics.  The algorithm is the reference's
 (examples/hopper/experimental/flash_attention_hopper.py:44-465: online softmax over K/V
 tiles, P rounded to bf16 before the second product); that kernel is sm_90a-only, single
 head, non-causal and limited to head_dim <= 64, so this entry point adds the batch and head
-dimensions, head_dim 128 and the causal mask.  ``build_flash_attention_hopper`` in
+dimensions, head dimensions up to 128 (any multiple of 8) and the causal mask.  ``build_flash_attention_hopper`` in
 ``pyptx_b200.examples.hopper.experimental.flash_attention_hopper`` keeps the reference's
 single-head call signature on top of the same kernel.
 """
@@ -20,11 +20,11 @@ from ...types import PtxType, bf16, f32
 
 BLOCK_M = 128   # query rows per tile (two tiles per CTA)
 BLOCK_N = 128   # keys per K/V tile
-HEAD_DIMS = (64, 128)
+HEAD_DIMS = tuple(range(8, 129, 8))   # tiles are 64 or 128 wide; narrower heads are zero-filled by TMA
 
 
 def _check(seq_q: int, seq_kv: int, head_dim: int, causal: bool) -> None:
-    assert head_dim in HEAD_DIMS, f"head_dim={head_dim} must be one of {HEAD_DIMS}"
+    assert head_dim in HEAD_DIMS, f"head_dim={head_dim} must be a multiple of 8 in [8, 128]"
     assert seq_q >= 1, f"M_q={seq_q} must be positive"
     assert seq_kv >= 1, f"N_seq={seq_kv} must be positive"
     assert not causal or seq_kv >= seq_q, "causal attention needs N_seq >= M_q"
@@ -38,7 +38,8 @@ def build_flash_attention(batch: int, heads: int, seq_q: int, seq_kv: int | None
 
     ``causal`` lets query ``i`` see keys ``j <= i + (Skv - Sq)``.  ``sm_scale`` defaults to
     ``1/sqrt(head_dim)``.  ``out_dtype`` is bf16 (default) or f32.  Sequence lengths need not be
-    multiples of the 128-wide tiles: partial tiles are zero-filled by TMA and masked.
+    multiples of the 128-wide tiles: partial tiles are zero-filled by TMA and masked.  The kernel's
+    tiles are 64 (``head_dim <= 64``) or 128 columns wide; narrower heads are zero-filled the same way.
     """
     assert arch.startswith("sm_100"), "Blackwell attention is only implemented for sm_100*"
     seq_kv = seq_q if seq_kv is None else seq_kv

@@ -3,8 +3,8 @@
 ``build_flash_attention_hopper(M_q, N_seq, head_dim=64, *, sm_scale=None)`` keeps the call
 convention of examples/hopper/experimental/flash_attention_hopper.py:44-50: inputs
 ``Q[M_q, HD]``, ``K_t[HD, N_seq]`` (K transposed by the caller) and ``V[N_seq, HD]`` in
-bf16, output ``O[M_q, HD]`` in f32.  Differences: ``head_dim`` is 64 or 128 (the reference takes
-16, 32 or 64); ``M_q`` is any positive length (the reference wants multiples of 128) and ``N_seq``
+bf16, output ``O[M_q, HD]`` in f32.  Differences: ``head_dim`` is any multiple of 8 up to 128 (the
+reference takes 16, 32 or 64); ``M_q`` is any positive length (the reference wants multiples of 128) and ``N_seq``
 any multiple of 8 (the reference: multiples of 64; 8 keeps the rows of ``K_t`` 16-byte aligned).
 """
 from __future__ import annotations

@@ -165,3 +165,53 @@ def test_push_gemm_and_peer_barrier_geometry(lib):
     assert rc == _ids.ERR_BAD_SHAPE and "timeout" in msg
     for x in (h, h1, hb):
         lib.pb200_destroy(x)
+
+
+def test_registry_is_safe_under_concurrent_use(lib):
+    """The registry is shared by every thread of the host process (the reference guards its own
+    with one mutex, pyptx/_shim/pyptx_launch.cc:236-237): concurrent create / query / destroy
+    must neither lose nor duplicate handles, and each call reports through its own buffer."""
+    import threading
+
+    before = lib.pb200_registry_size()
+    per_thread, n_threads = 200, 8
+    handles: list[list[int]] = [[] for _ in range(n_threads)]
+    errors: list[str] = []
+
+    def worker(i: int) -> None:
+        err = ctypes.create_string_buffer(_native.ERR_LEN)
+        try:
+            for j in range(per_thread):
+                d = (ctypes.c_int64 * 2)(4 + i, 64 * (1 + j % 4))
+                f = (ctypes.c_double * 1)(1e-6)
+                h = lib.pb200_create(_ids.K_RMS_NORM, d, 2, f, 1, 0, err)
+                if h <= 0 or not lib.pb200_has_handle(h):
+                    errors.append(f"thread {i}: create -> {h} {err.value!r}")
+                    return
+                g = _native.Geometry()
+                if lib.pb200_geometry_of(h, ctypes.byref(g)) != 0 or g.grid[0] != 4 + i:
+                    errors.append(f"thread {i}: geometry of {h} is another thread's")
+                    return
+                handles[i].append(h)
+                bad = (ctypes.c_int64 * 2)(4, 66)
+                if lib.pb200_create(_ids.K_RMS_NORM, bad, 2, f, 1, 0, err) != _ids.ERR_BAD_SHAPE or b"divisible" not in err.value:
+                    errors.append(f"thread {i}: rejection message got mixed up: {err.value!r}")
+                    return
+                if j % 3 == 2:
+                    lib.pb200_destroy(handles[i].pop(0))
+        except Exception as exc:  # noqa: BLE001
+            errors.append(f"thread {i}: {exc!r}")
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(n_threads)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors[:3]
+    live = [h for hs in handles for h in hs]
+    assert len(set(live)) == len(live)
+    assert lib.pb200_registry_size() == before + len(live)
+    for h in live:
+        assert lib.pb200_has_handle(h)
+        lib.pb200_destroy(h)
+    assert lib.pb200_registry_size() == before

@@ -86,7 +86,7 @@ def test_golden_single_head(mats, M_q, N_seq, HD):
     assert torch.allclose(o, ref, atol=5e-2, rtol=1e-2)     # the reference's own criterion (:481)
 
 
-@pytest.mark.parametrize("HD", [64, 128])
+@pytest.mark.parametrize("HD", [16, 32, 64, 128])       # the reference's list is (16, 32, 64), :502-505
 @pytest.mark.parametrize("M_q,N_seq", [(128, 128), (128, 512), (256, 256), (512, 1024), (1024, 2048), (2048, 2048),
                                        (384, 640)])
 def test_single_head_shapes(M_q, N_seq, HD):
@@ -96,6 +96,25 @@ def test_single_head_shapes(M_q, N_seq, HD):
     v = (torch.randn(N_seq, HD) * 0.3).to(torch.bfloat16)
     o = build_flash_attention_hopper(M_q, N_seq, HD)(q.cuda(), k.t().contiguous().cuda(), v.cuda()).cpu()
     check_bf16_matmul(o, formulas.attention_ref(q, k, v))
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("out_dtype", [f32, bf16])
+@pytest.mark.parametrize("d", [8, 16, 24, 32, 40, 72, 96, 120])
+def test_head_dims_narrower_than_the_tile(d, out_dtype, causal):
+    """Head dimensions below the 64- or 128-column tile: TMA zero-fills the missing columns of Q,
+    K and V, and only ``d`` columns of O are stored."""
+    B, H, Sq, Skv = 2, 2, 200, 328
+    q, k, v = _inputs(B, H, Sq, Skv, d)
+    kern = build_flash_attention(B, H, Sq, Skv, d, causal=causal, out_dtype=out_dtype)
+    o = kern(q.cuda(), k.cuda(), v.cuda())
+    check_bf16_matmul(o.cpu(), formulas.attention_ref(q, k, v, causal=causal))
+    # same arithmetic as the full-width kernel on explicitly zero-padded operands
+    full = 64 if d <= 64 else 128
+    pad = lambda t: torch.nn.functional.pad(t, (0, full - d)).contiguous()
+    wide = build_flash_attention(B, H, Sq, Skv, full, causal=causal, out_dtype=out_dtype, sm_scale=d ** -0.5)
+    ow = wide(pad(q).cuda(), pad(k).cuda(), pad(v).cuda())
+    assert torch.equal(ow[..., :d], o) and (ow[..., d:] == 0).all()
 
 
 # ---- batched form ------------------------------------------------------------------------

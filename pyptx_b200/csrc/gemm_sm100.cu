@@ -458,7 +458,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
             }   // sub
         }
-        if (!DIRECT && lane == 0) tma_store_wait_all<0>();
+        // Shared memory must outlive the stores' reads; the writes themselves complete with the grid.
+        // The push variant waits for completion: a barrier kernel on the same stream follows it.
+        if (!DIRECT && lane == 0) {
+            if (EPI == 2) tma_store_wait_all<0>(); else tma_store_wait_read<0>();
+        }
     }
 
     // ------------------------- teardown --------------------------------------

@@ -93,10 +93,23 @@ __device__ __forceinline__ float block_reduce(float v, float* slot) {
 // ---------------------------------------------------------------------------
 // RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w
 // ---------------------------------------------------------------------------
+// Programmatic dependent launch: when a kernel is launched with the "programmatic stream
+// serialization" attribute, its CTAs may be scheduled while the previous kernel of the stream is
+// still draining; they then wait here until that kernel has completed and its writes are
+// visible.  Every access to global memory comes after the wait, so the ordering a stream gives
+// is unchanged; what overlaps is the launch latency (about 2 us between two 20 us kernels).
+// launch_dependents lets the next kernel do the same with this one.  Both are no-ops for a
+// launch without the attribute.
+__device__ __forceinline__ void pdl_prologue() {
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 template <int THREADS, int VPT, typename OutT>
 __global__ void __launch_bounds__(THREADS)
 rms_norm_kernel(const float4* __restrict__ x, const float4* __restrict__ w,
                 void* __restrict__ y, int rows, int n4, float inv_n, float eps) {
+    pdl_prologue();
     __shared__ float red[2][kWarp];
     int flip = 0;
     for (int row = blockIdx.x; row < rows; row += gridDim.x) {
@@ -139,6 +152,7 @@ __global__ void __launch_bounds__(THREADS)
 layer_norm_kernel(const float4* __restrict__ x, const float4* __restrict__ w,
                   const float4* __restrict__ b, void* __restrict__ y,
                   int rows, int n4, float inv_n, float eps) {
+    pdl_prologue();
     __shared__ float red[2][kWarp];
     for (int row = blockIdx.x; row < rows; row += gridDim.x) {
         const float4* xr = x + (size_t)row * n4;
@@ -187,6 +201,7 @@ layer_norm_kernel(const float4* __restrict__ x, const float4* __restrict__ w,
 template <int THREADS, int VPT, typename OutT>
 __global__ void __launch_bounds__(THREADS)
 softmax_kernel(const float4* __restrict__ x, void* __restrict__ y, int rows, int n4) {
+    pdl_prologue();
     __shared__ float red[2][kWarp];
     for (int row = blockIdx.x; row < rows; row += gridDim.x) {
         const float4* xr = x + (size_t)row * n4;
@@ -241,6 +256,7 @@ __global__ void __launch_bounds__(1024)
 long_row_kernel(const float4* __restrict__ x, const float4* __restrict__ w,
                 const float4* __restrict__ b, void* __restrict__ y,
                 int rows, int n4, float inv_n, float eps) {
+    pdl_prologue();
     constexpr int THREADS = 1024;
     __shared__ float red[2][kWarp];
     for (int row = blockIdx.x; row < rows; row += gridDim.x) {
@@ -305,6 +321,7 @@ template <int THREADS, int UNROLL, typename OutT>
 __global__ void __launch_bounds__(THREADS)
 swiglu_kernel(const float4* __restrict__ gate, const float4* __restrict__ up,
               void* __restrict__ out, size_t total4) {
+    pdl_prologue();
     const size_t tile = (size_t)THREADS * UNROLL;
     for (size_t base = (size_t)blockIdx.x * tile; base < total4; base += (size_t)gridDim.x * tile) {
         float4 g[UNROLL], u[UNROLL];
@@ -352,16 +369,32 @@ RowConfig pick_row_config(int64_t n4, int threads = 0) {
     return {1024, 0};  // long-row kernel
 }
 
+// Launch with the programmatic-serialization attribute (see pdl_prologue).
+template <typename... KArgs, typename... Args>
+void launch_pdl(void (*kernel)(KArgs...), dim3 grid, int threads, cudaStream_t s, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3((unsigned)threads, 1, 1);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 template <int THREADS, int VPT, typename OutT>
 void launch_typed(int kid, dim3 grid, cudaStream_t s, void** p, int rows, int n4, float inv_n, float eps) {
     if (kid == PB200_K_RMS_NORM)
-        rms_norm_kernel<THREADS, VPT, OutT><<<grid, THREADS, 0, s>>>(
-            (const float4*)p[0], (const float4*)p[1], p[2], rows, n4, inv_n, eps);
+        launch_pdl(rms_norm_kernel<THREADS, VPT, OutT>, grid, THREADS, s,
+                   (const float4*)p[0], (const float4*)p[1], p[2], rows, n4, inv_n, eps);
     else if (kid == PB200_K_LAYER_NORM)
-        layer_norm_kernel<THREADS, VPT, OutT><<<grid, THREADS, 0, s>>>(
-            (const float4*)p[0], (const float4*)p[1], (const float4*)p[2], p[3], rows, n4, inv_n, eps);
+        launch_pdl(layer_norm_kernel<THREADS, VPT, OutT>, grid, THREADS, s,
+                   (const float4*)p[0], (const float4*)p[1], (const float4*)p[2], p[3], rows, n4, inv_n, eps);
     else
-        softmax_kernel<THREADS, VPT, OutT><<<grid, THREADS, 0, s>>>((const float4*)p[0], p[1], rows, n4);
+        launch_pdl(softmax_kernel<THREADS, VPT, OutT>, grid, THREADS, s, (const float4*)p[0], p[1], rows, n4);
 }
 template <int THREADS, int VPT>
 void launch_one(int kid, bool bf16_out, dim3 grid, cudaStream_t s, void** p, int rows, int n4, float inv_n, float eps) {
@@ -372,18 +405,18 @@ void launch_one(int kid, bool bf16_out, dim3 grid, cudaStream_t s, void** p, int
 template <typename OutT>
 void launch_long(int kid, dim3 grid, cudaStream_t s, void** p, int rows, int n4, float inv_n, float eps) {
     if (kid == PB200_K_RMS_NORM)
-        long_row_kernel<0, OutT><<<grid, 1024, 0, s>>>((const float4*)p[0], (const float4*)p[1], nullptr, p[2], rows, n4, inv_n, eps);
+        launch_pdl(long_row_kernel<0, OutT>, grid, 1024, s, (const float4*)p[0], (const float4*)p[1], (const float4*)nullptr, p[2], rows, n4, inv_n, eps);
     else if (kid == PB200_K_LAYER_NORM)
-        long_row_kernel<1, OutT><<<grid, 1024, 0, s>>>((const float4*)p[0], (const float4*)p[1], (const float4*)p[2], p[3], rows, n4, inv_n, eps);
+        launch_pdl(long_row_kernel<1, OutT>, grid, 1024, s, (const float4*)p[0], (const float4*)p[1], (const float4*)p[2], p[3], rows, n4, inv_n, eps);
     else
-        long_row_kernel<2, OutT><<<grid, 1024, 0, s>>>((const float4*)p[0], nullptr, nullptr, p[1], rows, n4, inv_n, eps);
+        launch_pdl(long_row_kernel<2, OutT>, grid, 1024, s, (const float4*)p[0], (const float4*)nullptr, (const float4*)nullptr, p[1], rows, n4, inv_n, eps);
 }
 template <int UNROLL>
 void launch_swiglu(bool bf16_out, dim3 grid, cudaStream_t s, void** p, size_t total4) {
     if (bf16_out)
-        swiglu_kernel<256, UNROLL, __nv_bfloat16><<<grid, 256, 0, s>>>((const float4*)p[0], (const float4*)p[1], p[2], total4);
+        launch_pdl(swiglu_kernel<256, UNROLL, __nv_bfloat16>, grid, 256, s, (const float4*)p[0], (const float4*)p[1], p[2], total4);
     else
-        swiglu_kernel<256, UNROLL, float><<<grid, 256, 0, s>>>((const float4*)p[0], (const float4*)p[1], p[2], total4);
+        launch_pdl(swiglu_kernel<256, UNROLL, float>, grid, 256, s, (const float4*)p[0], (const float4*)p[1], p[2], total4);
 }
 
 constexpr int kSwigluThreads = 256;

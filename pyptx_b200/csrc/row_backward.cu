@@ -60,22 +60,29 @@ __device__ __forceinline__ void block_sum2(float& a, float& b, float2* slot) {
 }
 
 // MODE 0 = RMSNorm, 1 = LayerNorm.  partial_w / partial_b: [gridDim.x][4*n4] f32.
+// A CTA walks rows blockIdx.x, blockIdx.x + gridDim.x, ...; each thread owns VPT float4 columns.
+// Its running column sums (dw, db) live in shared memory, not registers: that keeps the kernel
+// at 64 registers, so two 512-thread CTAs share an SM and one loads while the other reduces.
+constexpr int bwd_min_ctas(int threads) { return threads >= 1024 ? 1 : 1024 / threads; }
 template <int THREADS, int VPT, int MODE>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, bwd_min_ctas(THREADS))
 norm_bwd_kernel(const float4* __restrict__ x, const float4* __restrict__ w, const float4* __restrict__ dy,
                 float4* __restrict__ dx, float4* __restrict__ partial_w, float4* __restrict__ partial_b,
                 int rows, int n4, float inv_n, float eps) {
     __shared__ float2 red[3][kWarp];
-    float4 acc_w[VPT], acc_b[VPT], wv[VPT];
+    extern __shared__ float4 acc_smem[];              // [MODE + 1][THREADS * VPT]
+    float4* acc_w = acc_smem;
+    float4* acc_b = acc_smem + THREADS * VPT;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
         const int idx = threadIdx.x + i * THREADS;
-        acc_w[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-        acc_b[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-        wv[i] = idx < n4 ? __ldg(w + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+        acc_w[idx] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (MODE == 1) acc_b[idx] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
     int flip = 0;
     for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        // w (64 KiB at most) is re-read where it is used: L1 serves it after the first row, and
+        // holding it would cost the registers that let two CTAs share an SM.
         const float4* xr = x + (size_t)row * n4;
         const float4* gr = dy + (size_t)row * n4;
         float4* dr = dx + (size_t)row * n4;
@@ -91,11 +98,17 @@ norm_bwd_kernel(const float4* __restrict__ x, const float4* __restrict__ w, cons
         float s_x = 0.f, s_wdy = 0.f;
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
-            if (MODE == 1) s_x += (xv[i].x + xv[i].y) + (xv[i].z + xv[i].w);
-            s_wdy += wv[i].x * gv[i].x + wv[i].y * gv[i].y + wv[i].z * gv[i].z + wv[i].w * gv[i].w;
+            if (MODE == 1) {
+                const int idx = threadIdx.x + i * THREADS;
+                const float4 wq = idx < n4 ? __ldg(w + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+                s_x += (xv[i].x + xv[i].y) + (xv[i].z + xv[i].w);
+                s_wdy += wq.x * gv[i].x + wq.y * gv[i].y + wq.z * gv[i].z + wq.w * gv[i].w;
+            }
         }
-        block_sum2<THREADS>(s_x, s_wdy, red[flip]);
-        flip = flip == 2 ? 0 : flip + 1;
+        if (MODE == 1) {        // RMSNorm needs neither the mean of x nor the mean of w*dy
+            block_sum2<THREADS>(s_x, s_wdy, red[flip]);
+            flip = flip == 2 ? 0 : flip + 1;
+        }
         const float mu = MODE == 1 ? s_x * inv_n : 0.f;
         // second moments: sum (x-mu)^2 and sum (x-mu) * w*dy
         float s_xx = 0.f, s_xwdy = 0.f;
@@ -103,9 +116,10 @@ norm_bwd_kernel(const float4* __restrict__ x, const float4* __restrict__ w, cons
         for (int i = 0; i < VPT; ++i) {
             const int idx = threadIdx.x + i * THREADS;
             if (idx < n4) {
+                const float4 wq = __ldg(w + idx);
                 const float cx = xv[i].x - mu, cy = xv[i].y - mu, cz = xv[i].z - mu, cw = xv[i].w - mu;
                 s_xx += cx * cx + cy * cy + cz * cz + cw * cw;
-                s_xwdy += cx * wv[i].x * gv[i].x + cy * wv[i].y * gv[i].y + cz * wv[i].z * gv[i].z + cw * wv[i].w * gv[i].w;
+                s_xwdy += cx * wq.x * gv[i].x + cy * wq.y * gv[i].y + cz * wq.z * gv[i].z + cw * wq.w * gv[i].w;
             }
         }
         block_sum2<THREADS>(s_xx, s_xwdy, red[flip]);
@@ -118,14 +132,21 @@ norm_bwd_kernel(const float4* __restrict__ x, const float4* __restrict__ w, cons
             const int idx = threadIdx.x + i * THREADS;
             if (idx < n4) {
                 const float hx = (xv[i].x - mu) * r, hy = (xv[i].y - mu) * r, hz = (xv[i].z - mu) * r, hw = (xv[i].w - mu) * r;
+                const float4 wq = __ldg(w + idx);
                 float4 o;
-                o.x = r * (wv[i].x * gv[i].x - c2 - hx * c1);
-                o.y = r * (wv[i].y * gv[i].y - c2 - hy * c1);
-                o.z = r * (wv[i].z * gv[i].z - c2 - hz * c1);
-                o.w = r * (wv[i].w * gv[i].w - c2 - hw * c1);
+                o.x = r * (wq.x * gv[i].x - c2 - hx * c1);
+                o.y = r * (wq.y * gv[i].y - c2 - hy * c1);
+                o.z = r * (wq.z * gv[i].z - c2 - hz * c1);
+                o.w = r * (wq.w * gv[i].w - c2 - hw * c1);
                 st_stream4(dr + idx, o);
-                acc_w[i].x += gv[i].x * hx; acc_w[i].y += gv[i].y * hy; acc_w[i].z += gv[i].z * hz; acc_w[i].w += gv[i].w * hw;
-                if (MODE == 1) { acc_b[i].x += gv[i].x; acc_b[i].y += gv[i].y; acc_b[i].z += gv[i].z; acc_b[i].w += gv[i].w; }
+                float4 aw = acc_w[idx];
+                aw.x += gv[i].x * hx; aw.y += gv[i].y * hy; aw.z += gv[i].z * hz; aw.w += gv[i].w * hw;
+                acc_w[idx] = aw;
+                if (MODE == 1) {
+                    float4 ab = acc_b[idx];
+                    ab.x += gv[i].x; ab.y += gv[i].y; ab.z += gv[i].z; ab.w += gv[i].w;
+                    acc_b[idx] = ab;
+                }
             }
         }
     }
@@ -134,26 +155,40 @@ norm_bwd_kernel(const float4* __restrict__ x, const float4* __restrict__ w, cons
     for (int i = 0; i < VPT; ++i) {
         const int idx = threadIdx.x + i * THREADS;
         if (idx < n4) {
-            partial_w[(size_t)blockIdx.x * n4 + idx] = acc_w[i];
-            if (MODE == 1) partial_b[(size_t)blockIdx.x * n4 + idx] = acc_b[i];
+            partial_w[(size_t)blockIdx.x * n4 + idx] = acc_w[idx];
+            if (MODE == 1) partial_b[(size_t)blockIdx.x * n4 + idx] = acc_b[idx];
         }
     }
 }
 
-// out[c] = sum_p partial[p][c] for the first `planes` planes (dw, then db).
-__global__ void __launch_bounds__(256)
+// out[c] = sum_p partial[p][c]; blockIdx.y selects the plane (dw, then db).  A CTA folds 32
+// float4 columns with 32 part-lanes: lane j adds parts j, j+32, ... in order, then one warp adds
+// the 32 lane sums in order, so the result depends on `parts` alone, not on timing.  (A column per
+// thread with one serial loop over all parts took as long as the backward pass itself.)
+__global__ void __launch_bounds__(1024)
 fold_partials_kernel(const float4* __restrict__ partial, float4* __restrict__ out_w, float4* __restrict__ out_b,
-                     int parts, int n4, int planes) {
-    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= n4) return;
-    for (int pl = 0; pl < planes; ++pl) {
-        const float4* src = partial + (size_t)pl * parts * n4;
-        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int p = 0; p < parts; ++p) {
-            const float4 v = src[(size_t)p * n4 + idx];
+                     int parts, int n4) {
+    __shared__ float4 lane_sum[32][32];
+    const int c = threadIdx.x & 31, j = threadIdx.x >> 5;
+    const int col = blockIdx.x * 32 + c;
+    const float4* src = partial + (size_t)blockIdx.y * parts * n4;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (col < n4) {
+        for (int p = j; p < parts; p += 32) {
+            const float4 v = src[(size_t)p * n4 + col];
             a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
         }
-        (pl == 0 ? out_w : out_b)[idx] = a;
+    }
+    lane_sum[j][c] = a;
+    __syncthreads();
+    if (j == 0 && col < n4) {
+        float4 t = lane_sum[0][c];
+#pragma unroll
+        for (int k = 1; k < 32; ++k) {
+            const float4 v = lane_sum[k][c];
+            t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w;
+        }
+        (blockIdx.y == 0 ? out_w : out_b)[col] = t;
     }
 }
 
@@ -198,16 +233,35 @@ bool pick_bwd_config(int64_t n4, BwdConfig& c) {
         if ((int64_t)t.threads * t.vpt >= n4) { c = t; return true; }
     return false;
 }
-int bwd_parts(int64_t rows) {
-    const int64_t p = 2 * (int64_t)sm_count();
+size_t bwd_acc_bytes(const BwdConfig& c, int mode) { return (size_t)(mode + 1) * c.threads * c.vpt * sizeof(float4); }
+
+// CTAs of the persistent grid: two per SM where two fit (threads and the shared-memory column
+// sums), else one, so that no CTA waits for a slot.
+int bwd_parts(int64_t rows, int64_t n4, int mode) {
+    BwdConfig c{256, 4};
+    pick_bwd_config(n4, c);
+    const bool two = 2 * c.threads <= 2048 && 2 * bwd_acc_bytes(c, mode) <= 200 * 1024;
+    const int64_t p = (two ? 2 : 1) * (int64_t)sm_count();
     return (int)(rows < p ? rows : p);
 }
 
 template <int THREADS, int VPT>
 void launch_norm(int mode, int parts, cudaStream_t s, const float4* x, const float4* w, const float4* dy, float4* dx,
                  float4* pw, float4* pb, int rows, int n4, float inv_n, float eps) {
-    if (mode == 0) norm_bwd_kernel<THREADS, VPT, 0><<<parts, THREADS, 0, s>>>(x, w, dy, dx, pw, pb, rows, n4, inv_n, eps);
-    else norm_bwd_kernel<THREADS, VPT, 1><<<parts, THREADS, 0, s>>>(x, w, dy, dx, pw, pb, rows, n4, inv_n, eps);
+    const size_t smem = (size_t)(mode + 1) * THREADS * VPT * sizeof(float4);
+    if (smem > 48 * 1024) {
+        // opt in once per kernel and device (a host-side attribute, no allocation)
+        static std::atomic<uint64_t> done[2];
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (!(done[mode].load(std::memory_order_relaxed) & (1ull << (dev & 63)))) {
+            if (mode == 0) cudaFuncSetAttribute(norm_bwd_kernel<THREADS, VPT, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            else cudaFuncSetAttribute(norm_bwd_kernel<THREADS, VPT, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            done[mode].fetch_or(1ull << (dev & 63), std::memory_order_relaxed);
+        }
+    }
+    if (mode == 0) norm_bwd_kernel<THREADS, VPT, 0><<<parts, THREADS, smem, s>>>(x, w, dy, dx, pw, pb, rows, n4, inv_n, eps);
+    else norm_bwd_kernel<THREADS, VPT, 1><<<parts, THREADS, smem, s>>>(x, w, dy, dx, pw, pb, rows, n4, inv_n, eps);
 }
 
 }  // namespace
@@ -227,7 +281,7 @@ int enqueue_norm_bwd(int mode, int rows, int n, float eps, int parts, cudaStream
     PB200_BWD_CASE(32, 1) PB200_BWD_CASE(32, 2) PB200_BWD_CASE(64, 2) PB200_BWD_CASE(128, 2)
     PB200_BWD_CASE(128, 4) PB200_BWD_CASE(256, 4) PB200_BWD_CASE(512, 4) PB200_BWD_CASE(512, 8) {}
 #undef PB200_BWD_CASE
-    fold_partials_kernel<<<(n4 + 255) / 256, 256, 0, s>>>(pw, (float4*)dw, (float4*)db, parts, n4, mode == 1 ? 2 : 1);
+    fold_partials_kernel<<<dim3((n4 + 31) / 32, mode == 1 ? 2 : 1), 1024, 0, s>>>(pw, (float4*)dw, (float4*)db, parts, n4);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { set_err(err, "backward norm launch failed: %s", cudaGetErrorString(e)); return PB200_ERR_LAUNCH; }
     return PB200_OK;
@@ -256,10 +310,10 @@ int plan_row_bwd(Record& r, char* err) {
     BwdConfig c;
     if (!pick_bwd_config(n / 4, c)) { set_err(err, "backward norm kernels support at most 16384 columns, got %lld", (long long)n); return PB200_ERR_BAD_SHAPE; }
     const int mode = r.kernel_id == PB200_K_LAYER_NORM_BWD ? 1 : 0;
-    const int parts = bwd_parts(rows);
+    const int parts = bwd_parts(rows, n / 4, mode);
     r.dims[7] = parts;            // fixed at create time: the scratch size depends on it
     g.grid[0] = (uint32_t)parts; g.block[0] = (uint32_t)c.threads;
-    g.smem_bytes = 3 * kWarp * sizeof(float2);
+    g.smem_bytes = (uint32_t)(3 * kWarp * sizeof(float2) + bwd_acc_bytes(c, mode));
     g.n_outputs = mode == 1 ? 3 : 2;
     g.scratch_bytes = norm_bwd_scratch_bytes(mode, parts, (int)n);
     return PB200_OK;

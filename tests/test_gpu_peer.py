@@ -18,11 +18,12 @@ pytestmark = pytest.mark.gpu
 @pytest.mark.parametrize("cta_group", [1, 2])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("n_dest", [1, 3, 8])
-def test_push_gemm_writes_every_destination(cta_group, out_dtype, n_dest):
+@pytest.mark.parametrize("tile_flag", [1 << 18, 1 << 19], ids=["single_height", "double_height"])
+def test_push_gemm_writes_every_destination(cta_group, out_dtype, n_dest, tile_flag):
     M, N, K = 512, 512, 256
     a, bt = inputs.gemm_inputs(M, N, K)
     ref = formulas.gemm_ref(a, bt)
-    flags = _ids.F_OUT_BF16 if out_dtype == torch.bfloat16 else 0
+    flags = (_ids.F_OUT_BF16 if out_dtype == torch.bfloat16 else 0) | tile_flag
     h = _native.create_handle(_ids.K_GEMM_PUSH, (n_dest, cta_group, M, N, K), (), flags)
     ad, bd = a.cuda(), bt.cuda()
     # destinations: disjoint [M, N] blocks of one tall buffer, filled with a sentinel first

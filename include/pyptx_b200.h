@@ -88,7 +88,7 @@ extern "C" {
 #define PB200_K_GROUPED_GEMM   7
 /* build_flash_attention_hopper  examples/hopper/experimental/flash_attention_hopper.py:44-465
  *   dims = {batch*heads, M_q, N_seq, head_dim}   fparams = {sm_scale}
- *   flags: PB200_F_CAUSAL, PB200_F_OUT_BF16, PB200_F_K_TRANSPOSED
+ *   flags: PB200_F_CAUSAL, PB200_F_OUT_BF16, PB200_F_K_TRANSPOSED, PB200_F_RETURN_LSE
  *   buffers: Q[BH,M_q,d] bf16, K[BH,N_seq,d] bf16 (or K_t[BH,d,N_seq] with
  *            PB200_F_K_TRANSPOSED, the reference's layout), V[BH,N_seq,d] bf16
  *            -> O[BH,M_q,d] f32 (or bf16)                                         */
@@ -156,6 +156,10 @@ extern "C" {
 #define PB200_F_ACT_GELU       (2ull << 4)  /* 0.5 x (1 + erf(x / sqrt 2))                 */
 #define PB200_F_ACT_SILU       (3ull << 4)
 #define PB200_F_ACT_MASK       (3ull << 4)
+/* Attention: second output lse[BH, S_q] f32 = log(sum_j exp(scale * q_i . k_j)) over the visible keys,
+ * the row statistic a backward pass needs (the reference's kernel keeps it in registers only,
+ * examples/hopper/experimental/flash_attention_hopper.py:213-256).                              */
+#define PB200_F_RETURN_LSE     (1ull << 6)
 
 /* Launch geometry of a handle, as the reference's Kernel object exposes it
  * (pyptx/kernel.py:402-447: grid, block, cluster, smem). */

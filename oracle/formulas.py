@@ -110,6 +110,20 @@ def attention_ref(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: 
     return torch.softmax(s, dim=-1) @ v
 
 
+def attention_lse_ref(q: torch.Tensor, k: torch.Tensor, *, causal: bool = False,
+                      sm_scale: float | None = None) -> torch.Tensor:
+    """Row-wise ``logsumexp`` of the scaled (and causally masked) scores of :func:`attention_ref`:
+    the statistic the reference's kernel keeps per row as running max and sum
+    (examples/hopper/experimental/flash_attention_hopper.py:213-256)."""
+    q, k = q.float(), k.float()
+    scale = (1.0 / math.sqrt(q.shape[-1])) if sm_scale is None else sm_scale
+    s = q @ k.transpose(-1, -2) * scale
+    if causal:
+        m, n = s.shape[-2], s.shape[-1]
+        s = s.masked_fill(~torch.ones(m, n, dtype=torch.bool).tril(diagonal=n - m), float("-inf"))
+    return torch.logsumexp(s, dim=-1)
+
+
 def rms_norm_bwd_ref(x, w, dy, eps: float = 1e-6):
     """(dx, dw) by autograd through the forward formula (float64 internally, returned as float32)."""
     x64, w64 = x.double().requires_grad_(), w.double().requires_grad_()

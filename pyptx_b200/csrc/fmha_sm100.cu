@@ -40,10 +40,18 @@ constexpr int kKvTile = 128;      // keys per K/V tile
 constexpr int kFmhaThreads = 384; // 3 warpgroups: {TMA, MMA, 2 idle}, softmax tile 0, softmax tile 1
 constexpr uint32_t kDebugPSmem = 1u << 17;   // create flag: keep P in shared memory (head_dim 64)
 constexpr float kRescaleThreshold = 8.0f;    // log2 units
+#ifndef PB200_FMHA_SPLIT_P
+#define PB200_FMHA_SPLIT_P 1
+#endif
 #ifndef PB200_FMA_EXP_PAIRS
 #define PB200_FMA_EXP_PAIRS 3
 #endif
-constexpr int kFmaExpPairsOf8 = PB200_FMA_EXP_PAIRS;   // of every 8 score pairs, how many take the FMA-pipe exp2
+#ifndef PB200_FMA_EXP_PAIRS_D64
+#define PB200_FMA_EXP_PAIRS_D64 3
+#endif
+// Of every 8 score pairs, how many take the FMA-pipe exp2 (by tile width: the narrower tile has
+// half the MMA time per exponential, so the MUFU unit is further from balance there).
+template <int HD> constexpr int kFmaExpPairsOf8 = HD == 64 ? PB200_FMA_EXP_PAIRS_D64 : PB200_FMA_EXP_PAIRS;
 
 struct FmhaParams {
     int bh;            // batch * heads
@@ -136,7 +144,7 @@ __global__ void __launch_bounds__(kFmhaThreads, 1)
 fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v,
-                OutT* __restrict__ out, FmhaParams prm, int* status) {
+                OutT* __restrict__ out, float* __restrict__ lse, FmhaParams prm, int* status) {
     using L = FmhaSmem<HD, P_SMEM>;
     constexpr int kStages = L::kStages;
     constexpr int kDBlocks = HD / 64;                  // 64-element (128-byte) blocks along head_dim
@@ -157,7 +165,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const uint32_t bar_sfull = bar_vempty + 8 * kStages;   // [2]
     const uint32_t bar_pfull = bar_sfull + 16;             // [2]
     const uint32_t bar_ofull = bar_pfull + 16;             // [2]
-    const uint32_t s_tmem_slot = bar_ofull + 16;
+    const uint32_t bar_pvdone = bar_ofull + 16;            // [2] (split-P only)
+    const uint32_t s_tmem_slot = bar_pvdone + 16;
     const uint32_t s_abort = s_tmem_slot + 8;
     volatile uint32_t* tmem_slot_gen = (volatile uint32_t*)(gen + (s_tmem_slot - base));
     volatile int* abort_gen = (volatile int*)(gen + (s_abort - base));
@@ -197,6 +206,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
             mbar_init(bar_sfull + 8 * t, 1);
             mbar_init(bar_pfull + 8 * t, 4);     // one arrival per softmax warp
             mbar_init(bar_ofull + 8 * t, 1);
+            mbar_init(bar_pvdone + 8 * t, 1);
         }
         fence_mbarrier_init();
         fence_proxy_async_smem();
@@ -212,6 +222,11 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const uint32_t tmem_base = *tmem_slot_gen;
     const uint32_t tmem_s[2] = {tmem_base, tmem_base + 128u};
     const uint32_t tmem_o[2] = {tmem_base + 256u, tmem_base + 384u};
+    // Head dimension 64 leaves 64 free columns behind each O: P gets columns of its own there, so
+    // that the next S of a tile no longer has to wait for the P V product that reads P (with P
+    // aliased over S it must), and S(j+1) is issued ahead of P(j) V(j).
+    constexpr bool kSplitP = PB200_FMHA_SPLIT_P && HD == 64 && !P_SMEM;
+    const uint32_t tmem_p[2] = {kSplitP ? tmem_o[0] + 64u : tmem_s[0], kSplitP ? tmem_o[1] + 64u : tmem_s[1]};
 
     if (warp == 0) {
         // ------------------------------- TMA producer -------------------------------
@@ -286,7 +301,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                         umma_f16_ss_lohi(tmem_o[t], p_lo[t] + (uint32_t)((k >> 2) * (kQTile * 8) + (k & 3) * 2), p_hi,
                                          vl + (uint32_t)(k * 128), v_hi, kIdescPV, acc);
                     else
-                        umma_f16_ts_lohi(tmem_o[t], tmem_s[t] + (uint32_t)(k * 8), vl + (uint32_t)(k * 128), v_hi, kIdescPV, acc);
+                        umma_f16_ts_lohi(tmem_o[t], tmem_p[t] + (uint32_t)(k * 8), vl + (uint32_t)(k * 128), v_hi, kIdescPV, acc);
                 }
             };
             int kstage = 0; uint32_t kphase = 0;     // ring position of K(j+1) being consumed by S
@@ -311,9 +326,16 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     if (j < n_kv[t]) {
                         if (!(ok = mbar_wait(bar_pfull + 8 * t, jpar, ctx, 25 + t))) break;
                         tc_fence_after_sync();
-                        issue_pv(t, vstage, j == 0);
-                        if (j + 1 < n_kv[t]) { issue_s(t, kstage); umma_commit<1>(bar_sfull + 8 * t); }
-                        else umma_commit<1>(bar_ofull + 8 * t);
+                        if (kSplitP) {
+                            if (j + 1 < n_kv[t]) { issue_s(t, kstage); umma_commit<1>(bar_sfull + 8 * t); }
+                            issue_pv(t, vstage, j == 0);
+                            if (j + 1 < n_kv[t]) umma_commit<1>(bar_pvdone + 8 * t);
+                            else umma_commit<1>(bar_ofull + 8 * t);
+                        } else {
+                            issue_pv(t, vstage, j == 0);
+                            if (j + 1 < n_kv[t]) { issue_s(t, kstage); umma_commit<1>(bar_sfull + 8 * t); }
+                            else umma_commit<1>(bar_ofull + 8 * t);
+                        }
                     }
                 }
                 if (!ok) break;
@@ -334,6 +356,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const uint32_t lane_off = (uint32_t)(q * 32) << 16;
         const uint32_t ts = tmem_s[t] + lane_off;
         const uint32_t to = tmem_o[t] + lane_off;
+        const uint32_t tp = tmem_p[t] + lane_off;
         const int n = n_kv[t];
         float m_used = -INFINITY;     // reference maximum currently baked into O and l (log2 units)
         float l = 0.f;
@@ -370,6 +393,13 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     mx4[2] = fmax3(mx4[2], __uint_as_float(sc[i + 4]), __uint_as_float(sc[i + 5]));
                     mx4[3] = fmax3(mx4[3], __uint_as_float(sc[i + 6]), __uint_as_float(sc[i + 7]));
                 }
+            }
+            if (kSplitP && j > 0) {
+                // P(j-1) V(j-1) must have retired before O is rescaled or P is overwritten
+                ok = mbar_wait(bar_pvdone + 8 * t, (uint32_t)(j - 1) & 1u, ctx, 35 + t);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after_sync();
             }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             const float m_new = fmaxf(m_used, mx * prm.scale_log2);
@@ -413,7 +443,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                             fma2(t0, t1, __uint_as_float(v[cc * 32 + 2 * i]), __uint_as_float(v[cc * 32 + 2 * i + 1]),
                                  prm.scale_log2, neg_m);
                             float p0, p1;
-                            if ((i & 7) < kFmaExpPairsOf8) exp2_fma_pair(p0, p1, t0, t1);   // compile-time choice per pair
+                            if ((i & 7) < kFmaExpPairsOf8<HD>) exp2_fma_pair(p0, p1, t0, t1);   // compile-time choice per pair
                             else { p0 = fast_exp2(t0); p1 = fast_exp2(t1); }
                             add2(sum4[2 * (i & 1)], sum4[2 * (i & 1) + 1], p0, p1);
                             __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);    // .x = p0 in the low half
@@ -441,7 +471,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                                          packed[4 * jj], packed[4 * jj + 1], packed[4 * jj + 2], packed[4 * jj + 3]);
                         }
                     } else {
-                        tmem_st_32x32b_x16(ts + (uint32_t)(c * 16), packed);
+                        tmem_st_32x32b_x16(tp + (uint32_t)(c * 16), packed);
                     }
                 }
             }
@@ -464,6 +494,10 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
             // prm.hd apart and only the first prm.hd columns exist.
             OutT* dst = out + ((size_t)bh * prm.s_q + row) * prm.hd;
             const bool row_exists = row < prm.s_q;          // a partial last query tile computes padding rows
+            // log-sum-exp of the scaled scores (natural log), for callers that run a backward pass:
+            // m_used is in log2 units and l = sum 2^(x - m_used).
+            if (lse != nullptr && row_exists)
+                lse[(size_t)bh * prm.s_q + row] = (m_used + log2f(l)) * 0.6931471805599453f;
 #pragma unroll 1
             for (int c = 0; c < HD / 32; ++c) {
                 uint32_t o[32];
@@ -559,7 +593,8 @@ int launch_fmha(const Record& r, cudaStream_t stream, void** p, char* err) {
     prm.causal_offset = (int)(SKV - SQ);
     prm.hd = (int)hd;
     dim3 grid(r.geom.grid[0], r.geom.grid[1], 1);
-    kernel<<<grid, kFmhaThreads, L::kTotal, stream>>>(tq, tk, tv, (OutT*)p[3], prm, device_status_ptr());
+    float* lse = (r.flags & PB200_F_RETURN_LSE) ? (float*)p[4] : nullptr;
+    kernel<<<grid, kFmhaThreads, L::kTotal, stream>>>(tq, tk, tv, (OutT*)p[3], lse, prm, device_status_ptr());
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { set_err(err, "attention launch failed (HD=%d smem=%d): %s", HD, L::kTotal, cudaGetErrorString(e)); return PB200_ERR_LAUNCH; }
     return PB200_OK;
@@ -589,7 +624,7 @@ int plan_attention(Record& r, char* err) {
     g.cluster[0] = g.cluster[1] = g.cluster[2] = 1;
     g.smem_bytes = tile_hd == 64 ? ((r.flags & kDebugPSmem) ? FmhaSmem<64, true>::kTotal : FmhaSmem<64, false>::kTotal)
                             : FmhaSmem<128, false>::kTotal;
-    g.n_inputs = 3; g.n_outputs = 1;
+    g.n_inputs = 3; g.n_outputs = (r.flags & PB200_F_RETURN_LSE) ? 2 : 1;
     return PB200_OK;
 }
 

@@ -13,7 +13,7 @@ from __future__ import annotations
 
 import math
 
-from ..._ids import F_CAUSAL, F_K_TRANSPOSED, F_OUT_BF16, K_FLASH_ATTN
+from ..._ids import F_CAUSAL, F_K_TRANSPOSED, F_OUT_BF16, F_RETURN_LSE, K_FLASH_ATTN
 from ...kernel import NativeKernel
 from ...specs import Layout, Tile
 from ...types import PtxType, bf16, f32
@@ -32,7 +32,7 @@ def _check(seq_q: int, seq_kv: int, head_dim: int, causal: bool) -> None:
 
 def build_flash_attention(batch: int, heads: int, seq_q: int, seq_kv: int | None = None,
                           head_dim: int = 64, *, causal: bool = False, sm_scale: float | None = None,
-                          out_dtype: PtxType = bf16, arch: str = "sm_100a",
+                          out_dtype: PtxType = bf16, arch: str = "sm_100a", return_lse: bool = False,
                           _debug_flags: int = 0) -> NativeKernel:
     """Kernel ``k(Q[B,H,Sq,d], K[B,H,Skv,d], V[B,H,Skv,d]) -> O[B,H,Sq,d]`` (bf16 in).
 
@@ -40,6 +40,8 @@ def build_flash_attention(batch: int, heads: int, seq_q: int, seq_kv: int | None
     ``1/sqrt(head_dim)``.  ``out_dtype`` is bf16 (default) or f32.  Sequence lengths need not be
     multiples of the 128-wide tiles: partial tiles are zero-filled by TMA and masked.  The kernel's
     tiles are 64 (``head_dim <= 64``) or 128 columns wide; narrower heads are zero-filled the same way.
+    With ``return_lse`` the kernel returns ``(O, lse)``, ``lse[B,H,Sq]`` (f32) being the natural-log
+    sum-exp of the scaled, masked scores of each query row.
     """
     assert arch.startswith("sm_100"), "Blackwell attention is only implemented for sm_100*"
     seq_kv = seq_q if seq_kv is None else seq_kv
@@ -47,13 +49,15 @@ def build_flash_attention(batch: int, heads: int, seq_q: int, seq_kv: int | None
     assert batch >= 1 and heads >= 1 and batch * heads <= 65535, "batch*heads must be in [1, 65535]"
     assert out_dtype in (f32, bf16), f"out_dtype must be f32 or bf16, got {out_dtype}"
     scale = 1.0 / math.sqrt(head_dim) if sm_scale is None else float(sm_scale)
-    flags = (F_CAUSAL if causal else 0) | (F_OUT_BF16 if out_dtype == bf16 else 0) | _debug_flags
+    flags = ((F_CAUSAL if causal else 0) | (F_OUT_BF16 if out_dtype == bf16 else 0) |
+             (F_RETURN_LSE if return_lse else 0) | _debug_flags)
+    lse_spec = (Tile(batch, heads, seq_q, f32, Layout.ROW),) if return_lse else ()
     return NativeKernel(
         "flash_attn_fwd", K_FLASH_ATTN, (batch * heads, seq_q, seq_kv, head_dim),
         in_specs=(Tile(batch, heads, seq_q, head_dim, bf16, Layout.TMA_128B, tma_box=(BLOCK_M, 64)),
                   Tile(batch, heads, seq_kv, head_dim, bf16, Layout.TMA_128B, tma_box=(BLOCK_N, 64)),
                   Tile(batch, heads, seq_kv, head_dim, bf16, Layout.TMA_128B, tma_box=(BLOCK_N, 64))),
-        out_specs=(Tile(batch, heads, seq_q, head_dim, out_dtype, Layout.ROW),),
+        out_specs=(Tile(batch, heads, seq_q, head_dim, out_dtype, Layout.ROW),) + lse_spec,
         fparams=(scale,), flags=flags, arch=arch,
         meta={"causal": causal, "sm_scale": scale, "block_m": BLOCK_M, "block_n": BLOCK_N},
     )

@@ -211,3 +211,22 @@ def test_benchmark_configuration(d, causal):
 def test_no_device_wait_gave_up():
     from pyptx_b200 import _native
     _native.device_status()
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("d", [32, 64, 128])
+def test_log_sum_exp_output(d, causal):
+    B, H, Sq, Skv = 2, 2, 300, 456
+    q, k, v = _inputs(B, H, Sq, Skv, d)
+    kern = build_flash_attention(B, H, Sq, Skv, d, causal=causal, out_dtype=f32, return_lse=True)
+    o, lse = kern(q.cuda(), k.cuda(), v.cuda())
+    plain = build_flash_attention(B, H, Sq, Skv, d, causal=causal, out_dtype=f32)(q.cuda(), k.cuda(), v.cuda())
+    assert torch.equal(o, plain)
+    ref = formulas.attention_lse_ref(q, k, causal=causal)
+    assert lse.shape == ref.shape and lse.dtype == torch.float32
+    assert torch.allclose(lse.cpu(), ref, atol=2e-3, rtol=0)      # ex2.approx / cubic exp2 in the row sum
+    # softmax rebuilt from lse reproduces the output: exp(s - lse) @ v
+    s = (q.float() @ k.float().transpose(-1, -2)) * d ** -0.5
+    if causal:
+        s = s.masked_fill(~torch.ones(Sq, Skv, dtype=torch.bool).tril(diagonal=Skv - Sq), float("-inf"))
+    check_bf16_matmul(o.cpu(), torch.exp(s - lse.cpu()[..., None]) @ v.float())

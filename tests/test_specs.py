@@ -61,3 +61,10 @@ def test_unify_envs():
     assert unify_envs([{"M": 1, "K": 2}, {"K": 2, "N": 3}]) == {"M": 1, "K": 2, "N": 3}
     with pytest.raises(ValueError, match="conflicting values"):
         unify_envs([{"K": 2}, {"K": 4}])
+
+
+def test_host_pipeline_rejects_bad_depth_before_touching_cuda():
+    from pyptx_b200.host_pipeline import HostPipeline
+
+    with pytest.raises(ValueError, match="depth"):
+        HostPipeline(lambda *a: None, depth=0)

@@ -123,3 +123,34 @@ def test_push_gather_is_bit_identical_to_nccl_gather():
     via_push = PushGatherGemm(M_local, N, K)(a_local, b_dev)
     torch.cuda.synchronize()
     assert torch.equal(via_push, via_nccl)
+
+
+def test_push_gather_replays_from_a_cuda_graph():
+    """The barrier keeps its call counter on the device, so a captured call (barrier, GEMM with
+    peer stores, barrier) can be replayed: every replay must leave the full product on every rank."""
+    from pyptx_b200 import _native
+    from pyptx_b200.peer import PushGatherGemm
+
+    world, rank = _wr()
+    M_local, N, K = 512, 512, 256
+    a, bt = inputs.gemm_inputs(world * M_local, N, K)
+    ref = formulas.gemm_ref(a, bt)
+    gemm = PushGatherGemm(M_local, N, K)
+    a_local = a[rank * M_local:(rank + 1) * M_local].cuda().contiguous()
+    b_dev = bt.cuda()
+    gemm(a_local, b_dev)                       # warm-up outside the capture
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            out = gemm(a_local, b_dev)
+    for _ in range(3):
+        out.zero_()
+        torch.cuda.synchronize()
+        if dist.is_initialized():
+            dist.barrier()                     # nobody replays while a peer is still clearing its buffer
+        graph.replay()
+        torch.cuda.synchronize()
+        assert formulas.rel_fro(out.cpu(), ref) < 1e-4
+    _native.device_status()

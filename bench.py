@@ -432,6 +432,70 @@ def gather_table(torch, dist, world: int, peak_tflops: float, iters: int = 10) -
     return table
 
 
+def sharded_table(torch, dist, world: int, rank: int) -> dict:
+    """Context for N > 1: the other benchmark configurations split over the ranks the way
+    ``pyptx_b200.dist`` partitions them (rows, experts, batch x head), no collective.  Each rank
+    times its share under CUDA-graph replay; the figure is whole-problem work over the slowest rank."""
+    from pyptx_b200 import dist as pdist
+    from pyptx_b200.examples.blackwell.flash_attention import attention_flops, build_flash_attention
+    from pyptx_b200.examples.blackwell.grouped_gemm import build_grouped_gemm
+    from pyptx_b200.examples.blackwell.rms_norm import build_rms_norm
+    from pyptx_b200.examples.blackwell.swiglu import build_fused_silu_mul
+
+    def slowest(ms: float) -> float:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    table = {}
+    B, N = 2048, 8192
+    sh = pdist.shard_rows(build_rms_norm, B, N, world=world, rank=rank)
+    if sh.kernel is not None:
+        xs = [torch.randn(sh.local, N, device="cuda") for _ in range(4)]
+        w = torch.randn(N, device="cuda")
+        it = iter(range(10 ** 9))
+        ms = time_graph(lambda: sh.kernel(xs[next(it) % 4], w), 40, torch)
+    else:
+        ms = 0.0
+    ms = slowest(ms)
+    table["rms_norm_2048x8192_rows_split"] = {"ms": ms, "GB/s": (2 * B * N * 4 + N * 4) / (ms * 1e-3) / 1e9}
+    sh = pdist.shard_rows(build_fused_silu_mul, B, N, world=world, rank=rank)
+    if sh.kernel is not None:
+        gs = [torch.randn(sh.local, N, device="cuda") for _ in range(4)]
+        it2 = iter(range(10 ** 9))
+
+        def swiglu_call():
+            i = next(it2)
+            return sh.kernel(gs[i % 4], gs[(i + 1) % 4])
+
+        ms = time_graph(swiglu_call, 40, torch)
+    else:
+        ms = 0.0
+    ms = slowest(ms)
+    table["swiglu_2048x8192_rows_split"] = {"ms": ms, "GB/s": 3 * B * N * 4 / (ms * 1e-3) / 1e9}
+    G, M, Ng, K = 8, 2048, 256, 2048
+    sh = pdist.shard_grouped_gemm(build_grouped_gemm, G, M, Ng, K, world=world, rank=rank)
+    if sh.kernel is not None:
+        g_local = sh.local // M
+        a = (torch.randn(g_local * M, K, device="cuda") / K ** 0.5).to(torch.bfloat16)
+        bw = (torch.randn(g_local * Ng, K, device="cuda") / K ** 0.5).to(torch.bfloat16)
+        ms = time_graph(lambda: sh.kernel(a, bw), 40, torch)
+    else:
+        ms = 0.0
+    ms = slowest(ms)
+    table["grouped_G8_experts_split"] = {"ms": ms, "TFLOP/s": 2.0 * G * M * Ng * K / (ms * 1e-3) / 1e12}
+    Bq, H, Sq, d = 4, 16, 4096, 128
+    sh = pdist.shard_attention(build_flash_attention, Bq, H, Sq, Sq, d, world=world, rank=rank)
+    if sh.kernel is not None:
+        q, k, v = (torch.randn(1, sh.local, Sq, d, device="cuda").to(torch.bfloat16) for _ in range(3))
+        ms = time_graph(lambda: sh.kernel(q, k, v), 10, torch)
+    else:
+        ms = 0.0
+    ms = slowest(ms)
+    table["attention_d128_S4096_batch_head_split"] = {"ms": ms, "TFLOP/s": attention_flops(Bq, H, Sq, Sq, d) / (ms * 1e-3) / 1e12}
+    return table
+
+
 def run_ours(args) -> None:
     import torch
     import torch.distributed as dist
@@ -545,6 +609,7 @@ def run_ours(args) -> None:
         # every rank takes part; a failure on any rank is reported, not fatal to the headline
         try:
             gather = gather_table(torch, dist, world, peaks["bf16_tflops"])
+            gather["other_kernels_split_over_ranks"] = sharded_table(torch, dist, world, rank)
             _native.device_status()
         except Exception as exc:  # noqa: BLE001 - context only
             gather = {"error": str(exc)[:300]}

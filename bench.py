@@ -435,12 +435,41 @@ def gather_table(torch, dist, world: int, peak_tflops: float, iters: int = 10) -
 def sharded_table(torch, dist, world: int, rank: int) -> dict:
     """Context for N > 1: the other benchmark configurations split over the ranks the way
     ``pyptx_b200.dist`` partitions them (rows, experts, batch x head), no collective.  Each rank
-    times its share under CUDA-graph replay; the figure is whole-problem work over the slowest rank."""
+    times its share under CUDA-graph replay (inputs rotate over at least 512 MiB and every launch
+    of the graph writes its own output buffer, so neither side is served by L2); the figure is
+    whole-problem work over the slowest rank."""
     from pyptx_b200 import dist as pdist
     from pyptx_b200.examples.blackwell.flash_attention import attention_flops, build_flash_attention
     from pyptx_b200.examples.blackwell.grouped_gemm import build_grouped_gemm
     from pyptx_b200.examples.blackwell.rms_norm import build_rms_norm
     from pyptx_b200.examples.blackwell.swiglu import build_fused_silu_mul
+
+    def graph_ms(call, iters: int) -> float:
+        for i in range(3):
+            call(i)
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        keep = []
+        with torch.cuda.stream(side):
+            call(0)
+            side.synchronize()
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(iters):
+                    keep.append(call(i))
+        graph.replay()
+        torch.cuda.synchronize()
+        best = float("inf")
+        for _ in range(3):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1) / iters)
+        del graph, keep
+        return best
 
     def slowest(ms: float) -> float:
         t = torch.tensor([ms], device="cuda")
@@ -450,47 +479,42 @@ def sharded_table(torch, dist, world: int, rank: int) -> dict:
     table = {}
     B, N = 2048, 8192
     sh = pdist.shard_rows(build_rms_norm, B, N, world=world, rank=rank)
+    ms = 0.0
     if sh.kernel is not None:
-        xs = [torch.randn(sh.local, N, device="cuda") for _ in range(4)]
+        sets = max(4, (512 << 20) // (sh.local * N * 4))
+        xs = [torch.randn(sh.local, N, device="cuda") for _ in range(sets)]
         w = torch.randn(N, device="cuda")
-        it = iter(range(10 ** 9))
-        ms = time_graph(lambda: sh.kernel(xs[next(it) % 4], w), 40, torch)
-    else:
-        ms = 0.0
+        ms = graph_ms(lambda i: sh.kernel(xs[i % sets], w), 32)
+        del xs
     ms = slowest(ms)
     table["rms_norm_2048x8192_rows_split"] = {"ms": ms, "GB/s": (2 * B * N * 4 + N * 4) / (ms * 1e-3) / 1e9}
     sh = pdist.shard_rows(build_fused_silu_mul, B, N, world=world, rank=rank)
+    ms = 0.0
     if sh.kernel is not None:
-        gs = [torch.randn(sh.local, N, device="cuda") for _ in range(4)]
-        it2 = iter(range(10 ** 9))
-
-        def swiglu_call():
-            i = next(it2)
-            return sh.kernel(gs[i % 4], gs[(i + 1) % 4])
-
-        ms = time_graph(swiglu_call, 40, torch)
-    else:
-        ms = 0.0
+        sets = max(4, (512 << 20) // (sh.local * N * 4))
+        gs = [torch.randn(sh.local, N, device="cuda") for _ in range(sets)]
+        ms = graph_ms(lambda i: sh.kernel(gs[i % sets], gs[(i + 1) % sets]), 32)
+        del gs
     ms = slowest(ms)
     table["swiglu_2048x8192_rows_split"] = {"ms": ms, "GB/s": 3 * B * N * 4 / (ms * 1e-3) / 1e9}
     G, M, Ng, K = 8, 2048, 256, 2048
     sh = pdist.shard_grouped_gemm(build_grouped_gemm, G, M, Ng, K, world=world, rank=rank)
+    ms = 0.0
     if sh.kernel is not None:
         g_local = sh.local // M
-        a = (torch.randn(g_local * M, K, device="cuda") / K ** 0.5).to(torch.bfloat16)
+        sets = max(2, (512 << 20) // (g_local * M * K * 2))
+        a = [(torch.randn(g_local * M, K, device="cuda") / K ** 0.5).to(torch.bfloat16) for _ in range(sets)]
         bw = (torch.randn(g_local * Ng, K, device="cuda") / K ** 0.5).to(torch.bfloat16)
-        ms = time_graph(lambda: sh.kernel(a, bw), 40, torch)
-    else:
-        ms = 0.0
+        ms = graph_ms(lambda i: sh.kernel(a[i % sets], bw), 32)
+        del a
     ms = slowest(ms)
     table["grouped_G8_experts_split"] = {"ms": ms, "TFLOP/s": 2.0 * G * M * Ng * K / (ms * 1e-3) / 1e12}
     Bq, H, Sq, d = 4, 16, 4096, 128
     sh = pdist.shard_attention(build_flash_attention, Bq, H, Sq, Sq, d, world=world, rank=rank)
+    ms = 0.0
     if sh.kernel is not None:
         q, k, v = (torch.randn(1, sh.local, Sq, d, device="cuda").to(torch.bfloat16) for _ in range(3))
-        ms = time_graph(lambda: sh.kernel(q, k, v), 10, torch)
-    else:
-        ms = 0.0
+        ms = graph_ms(lambda i: sh.kernel(q, k, v), 10)
     ms = slowest(ms)
     table["attention_d128_S4096_batch_head_split"] = {"ms": ms, "TFLOP/s": attention_flops(Bq, H, Sq, Sq, d) / (ms * 1e-3) / 1e12}
     return table

@@ -491,6 +491,20 @@ int cta_group_of(const Record& r) {
     return r.kernel_id == PB200_K_GEMM_2SM ? 2 : 1;
 }
 
+constexpr uint32_t kForceBn256 = 1u << 20;        // create flag: the grouped kernel keeps 256-column tiles
+
+// Tile width.  A fixed-size grouped problem whose 128 x 256 tiles would leave more than half of the
+// SMs idle runs on 128 x 128 tiles, one per CTA on twice as many SMs (measured at G=4, M=2048,
+// N=256, K=2048: 13.9 us against 15.3 us).  With more tiles than that the wider tile wins: the
+// N=128 MMA needs 128 B/clk of shared-memory reads and runs below the N=256 rate.
+int choose_bn(const Record& r) {
+    const int64_t N = r.dims[r.n_dims - 2];
+    const int bn = pick_bn(N);
+    if (bn != 256 || r.kernel_id != PB200_K_GROUPED_GEMM || (r.flags & (kForceBn256 | kDebugDirectStore))) return bn;
+    const int64_t tiles = r.dims[0] * (r.dims[1] / BM) * (N / 256);
+    return 2 * tiles <= sm_count() ? 128 : 256;
+}
+
 bool is_grouped(int32_t kid) {
     return kid == PB200_K_GROUPED_GEMM || kid == PB200_K_GROUPED_GEMM_SWIGLU || kid == PB200_K_GROUPED_GEMM_VARLEN;
 }
@@ -658,7 +672,7 @@ int plan_gemm(Record& r, char* err) {
     if (M % (BM * cta_group) != 0) { set_err(err, "M=%lld must be divisible by %d", (long long)M, BM * cta_group); return PB200_ERR_BAD_SHAPE; }
     if (K % BK != 0) { set_err(err, "K=%lld must be divisible by %d", (long long)K, BK); return PB200_ERR_BAD_SHAPE; }
     if (swiglu && N % 128 != 0) { set_err(err, "F=%lld must be divisible by 128", (long long)N); return PB200_ERR_BAD_SHAPE; }
-    const int bn = swiglu ? 256 : pick_bn(N);
+    const int bn = swiglu ? 256 : choose_bn(r);
     if (bn == 0 || (!grouped && bn != 256)) {
         set_err(err, "N=%lld must be divisible by %d", (long long)N, grouped ? 64 : 256);
         return PB200_ERR_BAD_SHAPE;
@@ -682,7 +696,7 @@ int plan_gemm(Record& r, char* err) {
 int launch_gemm(const Record& r, cudaStream_t stream, void** p, char* err) {
     const int64_t N = r.dims[r.n_dims - 2];
     const bool swiglu = r.kernel_id == PB200_K_GROUPED_GEMM_SWIGLU;
-    const int bn = swiglu ? 256 : pick_bn(N);
+    const int bn = swiglu ? 256 : choose_bn(r);
     const int cta_group = cta_group_of(r);
     const bool bf16_out = (r.flags & PB200_F_OUT_BF16) != 0;
     const bool direct = (r.flags & kDebugDirectStore) != 0;

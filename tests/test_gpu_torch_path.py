@@ -201,3 +201,53 @@ def test_dispatch_overhead_is_reported(capsys):
     torch.cuda.synchronize()
     print(f"eager dispatch: {host_us:.1f} us per call (ext={'yes' if k._launcher.ext else 'no'})")
     assert host_us < 200
+
+
+def test_concurrent_launches_from_threads_on_their_own_streams():
+    """Host threads launch different kernels at once, each on its own stream: the launch path
+    (handle lookup under a shared lock, per-launch tensor maps, per-call error buffers, one-time
+    function attributes) must give every thread its own correct results."""
+    import threading
+
+    from oracle import formulas, inputs
+    from pyptx_b200.examples.blackwell.flash_attention import build_flash_attention
+    from pyptx_b200.examples.blackwell.gemm_highperf_blackwell import build_gemm, build_gemm_2sm
+    from pyptx_b200.examples.blackwell.rms_norm import build_rms_norm
+    from pyptx_b200.examples.blackwell.softmax import build_softmax
+    from pyptx_b200.types import f32
+
+    a, bt = inputs.gemm_inputs(512, 512, 256)
+    x, w = inputs.rms_norm_inputs(256, 2048)
+    q, k, v = (t.view(1, 2, 256, 64) for t in inputs.attention_inputs(2, 256, 256, 64))
+    jobs = {
+        "gemm_1sm": (build_gemm(512, 512, 256), (a.cuda(), bt.cuda()), formulas.gemm_ref(a, bt), 1e-4),
+        "gemm_2sm": (build_gemm_2sm(512, 512, 256), (a.cuda(), bt.cuda()), formulas.gemm_ref(a, bt), 1e-4),
+        "rms_norm": (build_rms_norm(256, 2048), (x.cuda(), w.cuda()), formulas.rms_norm_ref(x, w), 1e-5),
+        "softmax": (build_softmax(256, 2048), (x.cuda(),), torch.softmax(x, -1), 1e-5),
+        "attention": (build_flash_attention(1, 2, 256, 256, 64, out_dtype=f32), (q.cuda(), k.cuda(), v.cuda()),
+                      formulas.attention_ref(q, k, v), 1e-2),
+    }
+    torch.cuda.synchronize()
+    errors: list[str] = []
+
+    def worker(name):
+        kernel, args, ref, tol = jobs[name]
+        try:
+            stream = torch.cuda.Stream()
+            with torch.cuda.stream(stream):
+                outs = [kernel(*args) for _ in range(25)]
+            stream.synchronize()
+            for o in outs:
+                err = formulas.rel_fro(o.float().cpu(), ref)
+                if not err <= tol:
+                    errors.append(f"{name}: rel_fro {err:.3e}")
+                    return
+        except Exception as exc:  # noqa: BLE001
+            errors.append(f"{name}: {exc!r}")
+
+    threads = [threading.Thread(target=worker, args=(n,)) for n in jobs for _ in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors[:3]

@@ -731,7 +731,9 @@ def run_ours(args) -> None:
                        "per_gpu": "M=N=K=8192, A,B~N(0,1)/sqrt(K) seeded, B_T replicated, M-block per rank",
                        "l2": "operands (256 MiB) + output (256 MiB) exceed the 126 MB L2",
                        "vs_baseline_ref": "reference README.md:54: its 1-SM kernel 1240 TFLOPS at 8192^3 on B200 (per GPU)"},
-            "clocks": clocks,
+            "clocks": dict(clocks or {}, note=("NVML samples taken during the timed region; NVML shows the requested SM clock, "
+                                               "while ncu's sm__cycles_elapsed.max.per_second inside this kernel reads 1.45-1.51 GHz "
+                                               "(power-limited; profiles/gemm_2sm_8192.md)")),
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms, "steps": e2e_steps, "calls_in_flight": depth,
                     "api": "pyptx_b200.host_pipeline.HostPipeline(build_gemm_2sm(...)).submit(pinned A, pinned B_T, out=pinned D)"},

@@ -111,6 +111,18 @@ def build_gemm_2sm(M: int, N: int, K: int, *, arch: str = "sm_100a", stages: int
     )
 
 
+def build_gemm_persistent(M: int, N: int, K: int, *, arch: str = "sm_100a", stages: int = STAGES,
+                          grid_minor_dim: str = "n", grid_tile_width: int = 8, num_ctas: int | None = None,
+                          out_dtype: PtxType = f32) -> NativeKernel:
+    """The reference's persistent 1-SM entry point (gemm_highperf_blackwell.py:316-326), same call
+    convention as :func:`build_gemm`.  Every kernel of this library is persistent (one CTA per SM
+    walks a static tile list), so this is :func:`build_gemm` with the reference's default band of 8;
+    ``num_ctas`` is accepted and validated, the grid is always one CTA per SM (or per tile if fewer)."""
+    assert num_ctas is None or num_ctas >= 1, "num_ctas must be positive"
+    return build_gemm(M, N, K, arch=arch, stages=stages, grid_minor_dim=grid_minor_dim,
+                      grid_tile_width=grid_tile_width, out_dtype=out_dtype)
+
+
 def gemm_flops(M: int, N: int, K: int) -> int:
     """benchmarks/bench_blackwell_gemm.py:56."""
     return 2 * M * N * K

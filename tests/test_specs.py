@@ -68,3 +68,30 @@ def test_host_pipeline_rejects_bad_depth_before_touching_cuda():
 
     with pytest.raises(ValueError, match="depth"):
         HostPipeline(lambda *a: None, depth=0)
+
+
+def test_reference_entry_points_exist_with_their_signatures():
+    """Names and keyword sets of the reference's builders on this path (its example modules), so
+    that a caller switching imports finds every one of them."""
+    import inspect
+
+    from pyptx_b200.examples.blackwell import gemm_highperf_blackwell as g, grouped_gemm, layer_norm, rms_norm, swiglu
+    from pyptx_b200.examples.hopper import softmax
+    from pyptx_b200.examples.hopper.experimental import flash_attention_hopper as fa
+
+    want = {
+        g.build_gemm: ["M", "N", "K", "arch", "stages", "grid_minor_dim", "grid_tile_width"],
+        g.build_gemm_persistent: ["M", "N", "K", "arch", "stages", "grid_minor_dim", "grid_tile_width", "num_ctas"],
+        g.build_gemm_2sm: ["M", "N", "K", "arch", "stages", "grid_minor_dim", "grid_tile_width"],
+        grouped_gemm.build_grouped_gemm: ["G", "M", "N", "K", "arch"],
+        rms_norm.build_rms_norm: ["B", "N", "eps"],
+        layer_norm.build_layer_norm: ["B", "N", "eps", "rows_per_cta"],
+        swiglu.build_fused_silu_mul: ["M", "F", "rows_per_cta"],
+        softmax.build_softmax: ["B", "N", "arch"],
+        fa.build_flash_attention_hopper: ["M_q", "N_seq", "head_dim", "sm_scale"],
+    }
+    for fn, names in want.items():
+        params = list(inspect.signature(fn).parameters)
+        assert params[:len(names)] == names or all(n in params for n in names), (fn.__name__, params)
+    assert inspect.signature(g.build_gemm_persistent).parameters["grid_tile_width"].default == 8
+    assert inspect.signature(g.build_gemm_2sm).parameters["stages"].default == 5

@@ -1,6 +1,6 @@
 """Stages the reference's own kernels for the GPU-side comparison.
 
-    python baseline/prepare_ref.py [/path/to/reference]
+    python baseline/prepare_ref.py /path/to/reference   (or set PYPTX_REFERENCE_DIR)
 
 Copies the reference's ``pyptx/`` package and ``examples/`` tree into ``baseline/_ref/`` (a
 git-ignored folder that still travels to the GPU box) and builds its launch shim there with
@@ -20,7 +20,10 @@ DEST = os.path.join(HERE, "_ref")
 
 
 def main() -> int:
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("PYPTX_REFERENCE_DIR", "")
+    if not ref:
+        print("usage: prepare_ref.py <reference tree>  (or set PYPTX_REFERENCE_DIR); nothing staged")
+        return 0
     if not os.path.isdir(os.path.join(ref, "pyptx")):
         print(f"no reference tree at {ref}; nothing staged")
         return 0

@@ -217,7 +217,7 @@ def run_reference(args) -> None:
     }))
 
 
-def row_kernel_table(torch, peaks, steps: int, warmup: int) -> dict:
+def row_kernel_table(torch, peaks, steps: int, warmup: int, errors: list) -> dict:
     """GB/s of the four row kernels at 2048 x 8192 f32, rotating over buffer sets whose total
     footprint exceeds L2 several times so that every launch streams from HBM."""
     from pyptx_b200.examples.blackwell.layer_norm import build_layer_norm, layer_norm_bytes
@@ -278,8 +278,8 @@ def row_kernel_table(torch, peaks, steps: int, warmup: int) -> dict:
             table[name] = {"ms": ms, "GB/s": gbs, "bytes": nbytes, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
                            "timing": "cuda-graph replay, 6 rotating buffer sets"}
             del outs
-    except Exception as exc:  # noqa: BLE001 - context only
-        table["backward_error"] = str(exc)[:200]
+    except Exception as exc:  # noqa: BLE001 - reported in "errors"
+        errors.append(f"row backward: {exc}"[:300])
     # torch's own GPU kernels for the same formulas, same buffers, same method (what the
     # reference's kernel benchmark prints next to its kernels, bench_blackwell_kernels.py:61-62, 85-86, 108-109)
     F = torch.nn.functional
@@ -303,15 +303,106 @@ def row_kernel_table(torch, peaks, steps: int, warmup: int) -> dict:
         try:
             ms = time_graph(fn, 24, torch)
             table[name]["torch_gpu_GB/s"] = table[name]["bytes"] / (ms * 1e-3) / 1e9
-        except Exception as exc:  # noqa: BLE001 - context only
-            table[name]["torch_gpu_error"] = str(exc)[:120]
+        except Exception as exc:  # noqa: BLE001 - reported in "errors"
+            errors.append(f"torch {name}: {exc}"[:300])
     return table
+
+
+def rotating_graph_ms(torch, call, n_sets: int, iters: int) -> float:
+    """Milliseconds per launch of ``call(i)`` (``i`` = buffer set) under CUDA-graph replay, with
+    every launch's result kept in a slot of its own so that neither operands nor outputs are
+    served from L2 when the sets together exceed it several times."""
+    outs = [None] * n_sets
+    counter = [0]
+
+    def fn():
+        i = counter[0] % n_sets
+        outs[i] = call(i)
+        counter[0] += 1
+
+    return time_graph(fn, iters, torch)
+
+
+def grouped_table(torch, peaks) -> dict:
+    """Grouped GEMM at the benchmark configurations, cold: operands and outputs rotate over buffer
+    sets that together exceed L2 at least four times, so the time is an HBM time; ``torch.bmm``
+    (bf16 out) is timed the same way on the same operands."""
+    from oracle import inputs
+    from pyptx_b200.examples.blackwell.grouped_gemm import build_grouped_gemm
+    table = {}
+    l2 = 126e6
+    for (G, M, N, K) in ((8, 2048, 256, 2048), (4, 2048, 256, 2048), (8, 512, 128, 512), (8, 1024, 128, 1024)):
+        nbytes = G * (M * K * 2 + N * K * 2 + M * N * 4)
+        sets = max(4, int(4 * l2 // nbytes) + 1)
+        base_a, base_b = inputs.grouped_gemm_inputs(G, M, N, K)
+        ga = [base_a.cuda().roll(i, 0) for i in range(sets)]
+        gb = [base_b.cuda().roll(i, 0) for i in range(sets)]
+        k = build_grouped_gemm(G, M, N, K)
+        flops = 2.0 * G * M * N * K
+        iters = 4 * sets if sets <= 16 else sets
+        ms = rotating_graph_ms(torch, lambda i: k(ga[i], gb[i]), sets, iters)
+        ms_warm = time_graph(lambda: k(ga[0], gb[0]), 20, torch)
+        a3 = [x.view(G, M, K) for x in ga]
+        b3 = [x.view(G, N, K).transpose(1, 2) for x in gb]
+        ms_bmm = rotating_graph_ms(torch, lambda i: torch.bmm(a3[i], b3[i]), sets, iters)
+        roof_ms = nbytes / (peaks["hbm_gbs"] * 1e9) * 1e3
+        table[f"G{G}_M{M}_N{N}_K{K}"] = {
+            "tflops": flops / (ms * 1e-3) / 1e12, "ms": ms, "bytes": nbytes, "hbm_roof_ms": roof_ms,
+            "frac_of_hbm_roof": roof_ms / ms, "buffer_sets": sets,
+            "tflops_one_buffer_set_l2_warm": flops / (ms_warm * 1e-3) / 1e12,
+            "torch_bmm_bf16_out_tflops": flops / (ms_bmm * 1e-3) / 1e12,
+            "timing": "cuda-graph replay over rotating operand/output sets (> 4x L2 in total)",
+        }
+        del ga, gb, a3, b3
+    return table
+
+
+def moe_table(torch) -> dict:
+    """MoE up-projection + activation: one fused kernel against grouped GEMM followed by SwiGLU."""
+    from oracle import inputs
+    from pyptx_b200.examples.blackwell.grouped_gemm import build_grouped_gemm, build_grouped_gemm_swiglu
+    from pyptx_b200.examples.blackwell.swiglu import build_fused_silu_mul
+    from pyptx_b200.types import bf16 as _bf16
+    G, M, F, K = 8, 2048, 1024, 2048
+    ga, gw = inputs.grouped_gemm_inputs(G, M, 2 * F, K)
+    ga, gw = ga.cuda(), gw.cuda()
+    fused = build_grouped_gemm_swiglu(G, M, F, K, out_dtype=_bf16)
+    two_a, two_b = build_grouped_gemm(G, M, 2 * F, K), build_fused_silu_mul(G * M, F, out_dtype=_bf16)
+
+    def two_kernels():
+        c = two_a(ga, gw)
+        return two_b(c[:, :F].contiguous(), c[:, F:].contiguous())
+
+    fl = 2.0 * G * M * 2 * F * K
+    ms = time_graph(lambda: fused(ga, gw), 10, torch)
+    ms2 = time_graph(two_kernels, 10, torch)
+    return {"moe_up_swiglu_fused_G8_M2048_F1024_K2048_tflops": fl / (ms * 1e-3) / 1e12,
+            "moe_up_swiglu_two_kernels_tflops": fl / (ms2 * 1e-3) / 1e12}
+
+
+def attention_table(torch) -> dict:
+    """Attention forward at B=4, H=16, S=4096 against torch SDPA on the same operands."""
+    import torch.nn.functional as F
+    from oracle import inputs
+    from pyptx_b200.examples.blackwell.flash_attention import attention_flops, build_flash_attention
+    out = {}
+    for d in (64, 128):
+        q, kk, v = (t.view(4, 16, 4096, d).cuda() for t in inputs.attention_inputs(64, 4096, 4096, d))
+        for causal in (False, True):
+            k = build_flash_attention(4, 16, 4096, 4096, d, causal=causal)
+            fl = attention_flops(4, 16, 4096, 4096, d, causal)
+            tag = f"attention_d{d}_{'causal' if causal else 'full'}"
+            ms = time_cuda(lambda: k(q, kk, v), 20, 5, torch)
+            out[tag + "_tflops"] = fl / (ms * 1e-3) / 1e12
+            ms = time_cuda(lambda: F.scaled_dot_product_attention(q, kk, v, is_causal=causal), 20, 5, torch)
+            out[tag + "_torch_sdpa_tflops"] = fl / (ms * 1e-3) / 1e12
+        del q, kk, v
+    return out
 
 
 def run_case(args) -> None:
     """``--case NAME``: launch one kernel of the library ``warmup + steps`` times on its benchmark
-    configuration and print its device time.  This is the small, single-kernel command that the
-    ncu summaries under profiles/ were captured from."""
+    configuration and print its device time: a small, single-kernel command to profile."""
     import torch
     from oracle import inputs
     from pyptx_b200 import _native
@@ -603,7 +694,7 @@ def run_ours(args) -> None:
     pipe = HostPipeline(kernel, depth=depth)
     d_pins = [torch.empty(S, S, dtype=torch.float32).pin_memory() for _ in range(depth)]
     d_pin = d_pins[0]
-    e2e_steps = max(4, min(args.steps, 10))
+    e2e_steps = args.steps
 
     def e2e_run(n):
         for i in range(n):
@@ -629,86 +720,57 @@ def run_ours(args) -> None:
     d2h = d_pin.numel() * 4
 
     gather = None
+    gather_error = None
     if world > 1 and not args.no_extras:
         # every rank takes part; a failure on any rank is reported, not fatal to the headline
         try:
             gather = gather_table(torch, dist, world, peaks["bf16_tflops"])
             gather["other_kernels_split_over_ranks"] = sharded_table(torch, dist, world, rank)
             _native.device_status()
-        except Exception as exc:  # noqa: BLE001 - context only
-            gather = {"error": str(exc)[:300]}
+        except Exception as exc:  # noqa: BLE001 - reported in "errors"
+            gather, gather_error = None, f"gather: {exc}"[:300]
 
     extras, cpu_baseline = None, None
-    if rank == 0 and world == 1 and args.no_extras:
+    errors: list[str] = []          # a context measurement that failed is named here, at the top level
+    if gather_error:
+        errors.append(gather_error)
+    if rank == 0 and (world > 1 or args.no_extras):
         torch.set_num_threads(host_cores())
         tflops, spent, _ = cpu_gemm_tflops(torch, a_host, bt_host, CPU_SAMPLE_ROWS, repeats=1)
         cpu_baseline = {"value": tflops, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
                         "host_cpus": os.cpu_count(), "sample": f"{CPU_SAMPLE_ROWS} of {S} rows of A, one pass"}
-    elif rank == 0 and world == 1:
+    elif rank == 0:
         # ---- context numbers: other variant, cuBLAS, smaller sizes, grouped, row kernels ----------------
         extras = {}
         other = "2sm" if args.variant == "1sm" else "1sm"
+        shapes = [(2048, 2048, 2048), (4096, 4096, 4096), (4096, 8192, 8192), (8192, 4096, 8192), (8192, 8192, 8192)]
+
+        def shape_tag(m, n, k):
+            return str(m) if m == n == k else f"{m}x{n}x{k}"
+
         for name in (args.variant, other):
-            for size in (2048, 4096, 8192):
-                k = builders[name](size, size, size)
-                x, y = a[:size, :size].contiguous(), bt[:size, :size].contiguous()
+            for (m, n, k_) in shapes:
+                k = builders[name](m, n, k_)
+                x, y = a[:m, :k_].contiguous(), bt[:n, :k_].contiguous()
                 ms = time_cuda(lambda: k(x, y), 20, 5, torch)
-                extras[f"gemm_{name}_{size}_tflops"] = 2.0 * size ** 3 / (ms * 1e-3) / 1e12
-        for size in (2048, 4096, 8192):
-            x, y = a[:size, :size].contiguous(), bt[:size, :size].t().contiguous()
+                extras[f"gemm_{name}_{shape_tag(m, n, k_)}_tflops"] = 2.0 * m * n * k_ / (ms * 1e-3) / 1e12
+        for (m, n, k_) in shapes:
+            x, y = a[:m, :k_].contiguous(), bt[:n, :k_].t().contiguous()
             ms = time_cuda(lambda: torch.matmul(x, y), 20, 5, torch)
-            extras[f"cublas_{size}_tflops"] = 2.0 * size ** 3 / (ms * 1e-3) / 1e12
+            extras[f"cublas_{shape_tag(m, n, k_)}_tflops"] = 2.0 * m * n * k_ / (ms * 1e-3) / 1e12
         try:
-            from pyptx_b200.examples.blackwell.grouped_gemm import build_grouped_gemm
-            for G in (8, 4):
-                ga, gb = inputs.grouped_gemm_inputs(G, 2048, 256, 2048)
-                ga, gb = ga.cuda(), gb.cuda()
-                k = build_grouped_gemm(G, 2048, 256, 2048)
-                ms = time_graph(lambda: k(ga, gb), 20, torch)
-                extras[f"grouped_G{G}_tflops"] = 2.0 * G * 2048 * 256 * 2048 / (ms * 1e-3) / 1e12
-                a3 = ga.view(G, 2048, 2048)
-                b3 = gb.view(G, 256, 2048).transpose(1, 2)
-                ms = time_graph(lambda: torch.bmm(a3, b3), 20, torch)
-                extras[f"grouped_G{G}_torch_bmm_bf16_tflops"] = 2.0 * G * 2048 * 256 * 2048 / (ms * 1e-3) / 1e12
-            # MoE up-projection + activation: one fused kernel against grouped GEMM followed by SwiGLU
-            from pyptx_b200.examples.blackwell.grouped_gemm import build_grouped_gemm_swiglu
-            from pyptx_b200.examples.blackwell.swiglu import build_fused_silu_mul
-            from pyptx_b200.types import bf16 as _bf16
-            G, M, F, K = 8, 2048, 1024, 2048
-            ga, gw = inputs.grouped_gemm_inputs(G, M, 2 * F, K)
-            ga, gw = ga.cuda(), gw.cuda()
-            fused = build_grouped_gemm_swiglu(G, M, F, K, out_dtype=_bf16)
-            two_a, two_b = build_grouped_gemm(G, M, 2 * F, K), build_fused_silu_mul(G * M, F, out_dtype=_bf16)
-
-            def two_kernels():
-                c = two_a(ga, gw)
-                return two_b(c[:, :F].contiguous(), c[:, F:].contiguous())
-
-            fl = 2.0 * G * M * 2 * F * K
-            ms = time_graph(lambda: fused(ga, gw), 10, torch)
-            extras["moe_up_swiglu_fused_G8_M2048_F1024_K2048_tflops"] = fl / (ms * 1e-3) / 1e12
-            ms2 = time_graph(two_kernels, 10, torch)
-            extras["moe_up_swiglu_two_kernels_tflops"] = fl / (ms2 * 1e-3) / 1e12
-            del ga, gw
-        except Exception as exc:  # noqa: BLE001 - context only
-            extras["grouped_error"] = str(exc)[:200]
+            extras["grouped"] = grouped_table(torch, peaks)
+        except Exception as exc:  # noqa: BLE001 - reported in "errors"
+            errors.append(f"grouped: {exc}"[:300])
         try:
-            from pyptx_b200.examples.blackwell.flash_attention import attention_flops, build_flash_attention
-            import torch.nn.functional as F
-            for d in (64, 128):
-                q, kk, v = (t.view(4, 16, 4096, d).cuda() for t in inputs.attention_inputs(64, 4096, 4096, d))
-                for causal in (False, True):
-                    k = build_flash_attention(4, 16, 4096, 4096, d, causal=causal)
-                    fl = attention_flops(4, 16, 4096, 4096, d, causal)
-                    tag = f"attention_d{d}_{'causal' if causal else 'full'}"
-                    ms = time_cuda(lambda: k(q, kk, v), 20, 5, torch)
-                    extras[tag + "_tflops"] = fl / (ms * 1e-3) / 1e12
-                    ms = time_cuda(lambda: F.scaled_dot_product_attention(q, kk, v, is_causal=causal), 20, 5, torch)
-                    extras[tag + "_torch_sdpa_tflops"] = fl / (ms * 1e-3) / 1e12
-                del q, kk, v
-        except Exception as exc:  # noqa: BLE001 - context only
-            extras["attention_error"] = str(exc)[:200]
-        extras["row_kernels_2048x8192_f32"] = row_kernel_table(torch, peaks, 200, 20)
+            extras.update(moe_table(torch))
+        except Exception as exc:  # noqa: BLE001
+            errors.append(f"moe_up_swiglu: {exc}"[:300])
+        try:
+            extras.update(attention_table(torch))
+        except Exception as exc:  # noqa: BLE001
+            errors.append(f"attention: {exc}"[:300])
+        extras["row_kernels_2048x8192_f32"] = row_kernel_table(torch, peaks, 200, 20, errors)
         _native.device_status()
         # ---- CPU baseline: the oracle formula on a bounded row block -----------------------------
         torch.set_num_threads(host_cores())
@@ -727,24 +789,25 @@ def run_ours(args) -> None:
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": value / world / 1240.0,
             "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"gemm_bf16_8192x8192x8192_f32out_{args.variant}",
+            "config": {"workload": "gemm_bf16_8192x8192x8192_f32out", "variant": args.variant,
                        "per_gpu": "M=N=K=8192, A,B~N(0,1)/sqrt(K) seeded, B_T replicated, M-block per rank",
                        "l2": "operands (256 MiB) + output (256 MiB) exceed the 126 MB L2",
                        "vs_baseline_ref": "reference README.md:54: its 1-SM kernel 1240 TFLOPS at 8192^3 on B200 (per GPU)"},
-            "clocks": dict(clocks or {}, note=("NVML samples taken during the timed region; NVML shows the requested SM clock, "
-                                               "while ncu's sm__cycles_elapsed.max.per_second inside this kernel reads 1.45-1.51 GHz "
-                                               "(power-limited; profiles/gemm_2sm_8192.md)")),
+            "clocks": dict(clocks or {}, note="NVML samples taken during the timed region (NVML reports the requested SM clock)"),
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms, "steps": e2e_steps, "calls_in_flight": depth,
                     "api": "pyptx_b200.host_pipeline.HostPipeline(build_gemm_2sm(...)).submit(pinned A, pinned B_T, out=pinned D)"},
             "gpu_launches": args.steps,
             "roofline": {"bound": "tensor", "achieved": kernel_tflops, "peak": peak, "unit": "TFLOP/s",
                          "frac": kernel_tflops / peak,
-                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this size
-                         # (ncu capture summarised in profiles/gemm_2sm_8192.md)
-                         "traffic": 1060119808 if args.variant == "2sm" else 1121270784, "peak_kind": f"{peak_kind} burst cuBLAS bf16",
+                         "traffic": 1060119808 if args.variant == "2sm" else 1121270784,
+                         "traffic_source": ("dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this "
+                                            "size from a separate ncu capture; a constant, not measured by this run"),
+                         "algorithmic_bytes": 2 * S * S * 2 + S * S * 4,
+                         "peak_kind": f"{peak_kind} burst cuBLAS bf16",
                          "frac_of_nominal_2250": kernel_tflops / 2250.0},
             "cpu_baseline": cpu_baseline,
+            "errors": errors,
         }
         if gather is not None:
             line["gather"] = gather

@@ -57,6 +57,7 @@ extern "C" {
 #define PB200_ERR_MISALIGNED      -10  /* a buffer pointer is NULL or not 16-B aligned */
 #define PB200_ERR_DEVICE_TIMEOUT  -11  /* a bounded device-side wait gave up      */
 #define PB200_ERR_BAD_KERNEL      -12  /* unknown kernel id                       */
+#define PB200_ERR_WRONG_DEVICE    -13  /* a buffer lives on another GPU or in pageable host memory */
 
 /* ---- kernel ids: each names one reference entry point ------------------ */
 /* build_rms_norm            examples/blackwell/rms_norm.py:26 (body examples/hopper/rms_norm.py:63-182)
@@ -143,6 +144,15 @@ extern "C" {
  *                pb200_device_status() reports PB200_ERR_DEVICE_TIMEOUT.                       */
 #define PB200_K_GEMM_PUSH      14
 #define PB200_K_PEER_BARRIER   15
+/* Attention backward: the half that pairs with PB200_K_FLASH_ATTN (built with PB200_F_RETURN_LSE)
+ * under the reference's autograd hook differentiable_kernel (pyptx/torch_support.py:446-519); the
+ * reference has no backward kernel.  Row statistics as its forward keeps them
+ * (examples/hopper/experimental/flash_attention_hopper.py:205-256), here read from lse.
+ *   dims = {batch*heads, S_q, S_kv, head_dim}   fparams = {sm_scale (0 -> 1/sqrt(head_dim))}
+ *   flags: PB200_F_CAUSAL, PB200_F_OUT_BF16 (dtype of dQ, dK, dV; default f32)
+ *   buffers: Q[BH,S_q,d], K[BH,S_kv,d], V[BH,S_kv,d], O[BH,S_q,d] bf16, lse[BH,S_q] f32, dO[BH,S_q,d] bf16
+ *            -> dQ[BH,S_q,d], dK[BH,S_kv,d], dV[BH,S_kv,d], then scratch (geometry.scratch_bytes)   */
+#define PB200_K_FLASH_ATTN_BWD 16
 
 /* ---- create-time flags -------------------------------------------------- */
 #define PB200_F_OUT_BF16       (1ull << 0)  /* round the output to bf16            */
@@ -188,7 +198,9 @@ PB200_API int64_t pb200_create(int32_t kernel_id,
  * the inputs in spec order, then the outputs, then (only for handles whose geometry reports
  * scratch_bytes > 0) one scratch buffer of that size.
  * Replaces pyptx_shim_launch_raw (pyptx/_shim/pyptx_launch.cc:484-492);
- * same argument list, same return convention. */
+ * same argument list, same return convention.  The caller makes the buffers' device current; the
+ * first launch of a handle (every launch with PB200_CHECK_POINTERS=1 in the environment) verifies
+ * it and returns PB200_ERR_WRONG_DEVICE otherwise. */
 PB200_API int pb200_launch_raw(int64_t handle, uint64_t stream,
                      void** buffer_ptrs, size_t n_buffers, char* err_out);
 

@@ -124,6 +124,21 @@ def attention_lse_ref(q: torch.Tensor, k: torch.Tensor, *, causal: bool = False,
     return torch.logsumexp(s, dim=-1)
 
 
+def attention_bwd_ref(q, k, v, d_out, *, causal: bool = False, sm_scale: float | None = None):
+    """(dq, dk, dv) by autograd through :func:`attention_ref`'s formula in float64 (returned as
+    float32), the way the row-kernel backward references are formed."""
+    q64, k64, v64 = (t.double().requires_grad_() for t in (q, k, v))
+    d = q.shape[-1]
+    scale = (1.0 / math.sqrt(d)) if sm_scale is None else sm_scale
+    s = q64 @ k64.transpose(-1, -2) * scale
+    if causal:
+        m, n = s.shape[-2], s.shape[-1]
+        s = s.masked_fill(~torch.ones(m, n, dtype=torch.bool).tril(diagonal=n - m), float("-inf"))
+    o = torch.softmax(s, dim=-1) @ v64
+    dq, dk, dv = torch.autograd.grad(o, (q64, k64, v64), d_out.double())
+    return dq.float(), dk.float(), dv.float()
+
+
 def rms_norm_bwd_ref(x, w, dy, eps: float = 1e-6):
     """(dx, dw) by autograd through the forward formula (float64 internally, returned as float32)."""
     x64, w64 = x.double().requires_grad_(), w.double().requires_grad_()

@@ -13,6 +13,7 @@
 
 #include <atomic>
 #include <cstdarg>
+#include <cstdlib>
 #include <mutex>
 #include <shared_mutex>
 #include <unordered_map>
@@ -48,6 +49,45 @@ bool is_row_bwd(int32_t k) {
 bool is_gemm(int32_t k) {
     return k == PB200_K_GEMM_1SM || k == PB200_K_GEMM_2SM || k == PB200_K_GROUPED_GEMM ||
            k == PB200_K_GROUPED_GEMM_SWIGLU || k == PB200_K_GROUPED_GEMM_VARLEN || k == PB200_K_GEMM_PUSH;
+}
+
+// Handles whose buffers were already checked against the current device.
+std::mutex g_checked_mu;
+std::unordered_map<int64_t, bool> g_checked;
+
+// "Assert the current device owns the buffers" of the reference's launch path
+// (pyptx/torch_support.py:189-195 switches to the tensors' device before the launch; the raw entry
+// trusts its caller).  A pointer that belongs to another GPU, or plain pageable host memory, would
+// fault inside the kernel, so the raw entry looks at every buffer on the first launch of a handle,
+// and on every launch when PB200_CHECK_POINTERS=1 is set in the environment.  Kernels that address
+// peer memory on purpose (the push GEMM's outputs, the peer barrier's flag blocks) are exempt there.
+int check_buffer_devices(const Record& r, int64_t handle, void** ptrs, size_t n, char* err) {
+    static const bool always = [] { const char* e = getenv("PB200_CHECK_POINTERS"); return e && e[0] == '1'; }();
+    if (!always) {
+        std::lock_guard<std::mutex> lk(g_checked_mu);
+        if (g_checked.count(handle)) return PB200_OK;
+    }
+    if (r.kernel_id == PB200_K_PEER_BARRIER) return PB200_OK;
+    const int dev = current_device();
+    if (dev < 0) { set_err(err, "no current CUDA device"); return PB200_ERR_NO_CUDA; }
+    const size_t n_check = r.kernel_id == PB200_K_GEMM_PUSH ? (size_t)r.geom.n_inputs : n;
+    for (size_t i = 0; i < n_check; ++i) {
+        cudaPointerAttributes a{};
+        if (cudaPointerGetAttributes(&a, ptrs[i]) != cudaSuccess) { cudaGetLastError(); continue; }
+        if (a.type == cudaMemoryTypeUnregistered) {
+            set_err(err, "buffer %zu (%p) is not device-accessible memory", i, ptrs[i]);
+            return PB200_ERR_WRONG_DEVICE;
+        }
+        if (a.type == cudaMemoryTypeDevice && a.device != dev) {
+            set_err(err, "buffer %zu (%p) lives on device %d, the current device is %d", i, ptrs[i], a.device, dev);
+            return PB200_ERR_WRONG_DEVICE;
+        }
+    }
+    if (!always) {
+        std::lock_guard<std::mutex> lk(g_checked_mu);
+        g_checked[handle] = true;
+    }
+    return PB200_OK;
 }
 
 }  // namespace
@@ -133,6 +173,7 @@ PB200_API int64_t pb200_create(int32_t kernel_id, const int64_t* dims, size_t n_
     else if (is_row_bwd(kernel_id)) rc = plan_row_bwd(r, err_out);
     else if (is_gemm(kernel_id)) rc = plan_gemm(r, err_out);
     else if (kernel_id == PB200_K_FLASH_ATTN) rc = plan_attention(r, err_out);
+    else if (kernel_id == PB200_K_FLASH_ATTN_BWD) rc = plan_attention_bwd(r, err_out);
     else if (kernel_id == PB200_K_PEER_BARRIER) rc = plan_peer_barrier(r, err_out);
     else { set_err(err_out, "unknown kernel id %d", kernel_id); return PB200_ERR_BAD_KERNEL; }
     if (rc != PB200_OK) return rc;
@@ -167,11 +208,13 @@ PB200_API int pb200_launch_raw(int64_t handle, uint64_t stream, void** buffer_pt
             return PB200_ERR_MISALIGNED;
         }
     }
+    if (int rc = check_buffer_devices(r, handle, buffer_ptrs, n_buffers, err_out)) return rc;
     cudaStream_t s = (cudaStream_t)(uintptr_t)stream;
     if (is_row(r.kernel_id)) return launch_row(r, s, buffer_ptrs, err_out);
     if (is_row_bwd(r.kernel_id)) return launch_row_bwd(r, s, buffer_ptrs, err_out);
     if (is_gemm(r.kernel_id)) return launch_gemm(r, s, buffer_ptrs, err_out);
     if (r.kernel_id == PB200_K_PEER_BARRIER) return launch_peer_barrier(r, s, buffer_ptrs, err_out);
+    if (r.kernel_id == PB200_K_FLASH_ATTN_BWD) return launch_attention_bwd(r, s, buffer_ptrs, err_out);
     return launch_attention(r, s, buffer_ptrs, err_out);
 }
 
@@ -197,10 +240,16 @@ PB200_API size_t pb200_registry_size(void) {
 PB200_API void pb200_clear_registry(void) {
     std::unique_lock<std::shared_mutex> lk(g_mu);
     g_registry.clear();
+    std::lock_guard<std::mutex> lk2(g_checked_mu);
+    g_checked.clear();
 }
 
 PB200_API int pb200_destroy(int64_t handle) {
     std::unique_lock<std::shared_mutex> lk(g_mu);
+    {
+        std::lock_guard<std::mutex> lk2(g_checked_mu);
+        g_checked.erase(handle);
+    }
     return g_registry.erase(handle) ? PB200_OK : PB200_ERR_UNKNOWN_HANDLE;
 }
 

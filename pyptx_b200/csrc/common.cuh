@@ -55,6 +55,9 @@ int launch_peer_barrier(const Record& r, cudaStream_t stream, void** ptrs, char*
 int plan_attention(Record& r, char* err);
 int launch_attention(const Record& r, cudaStream_t stream, void** ptrs, char* err);
 
+int plan_attention_bwd(Record& r, char* err);
+int launch_attention_bwd(const Record& r, cudaStream_t stream, void** ptrs, char* err);
+
 // Device-side status word (defined in abi.cu's translation unit of the same
 // library; each .cu that needs it reaches it through report_timeout()).
 // Layout: [0] = code (0 ok), [1] = kernel id, [2] = wait site, [3] = block id.

@@ -1,0 +1,475 @@
+// Flash-attention backward for sm_100a on tcgen05 tensor cores.
+//   given Q, K, V, O, dO (bf16) and the forward's row statistic lse (f32):
+//     P  = exp(scale * Q K^T - lse)            (recomputed, never stored)
+//     dV = P^T dO        dP = dO V^T        dS = P o (dP - delta),  delta_i = sum_c O_ic dO_ic
+//     dQ = scale * dS K  dK = scale * dS^T Q
+// The reference ships the autograd hook for such a pair (pyptx/torch_support.py:446-519) and keeps
+// the row statistics of its forward in registers (examples/hopper/experimental/
+// flash_attention_hopper.py:205-256); it has no backward kernel.  The arithmetic follows the
+// forward here: bf16 operands, fp32 accumulation, P and dS rounded to bf16 before they become
+// MMA operands.
+//
+// Two passes of ONE kernel template, so that no gradient needs atomics or a second accumulation
+// buffer and the result is deterministic:
+//   MODE 0 (dK, dV): a CTA owns 128 keys (K, V tiles stay in shared memory) and streams the query
+//          tiles (Q, dO).  Scores are computed transposed, S^T = K Q^T and dP^T = V dO^T, so that
+//          keys are TMEM lanes and P^T / dS^T can be fed back as the TMEM A operand of
+//          dV += P^T dO and dK += dS^T Q (Q and dO tiles consumed as MN-major B operands).
+//   MODE 1 (dQ):     a CTA owns 128 queries (Q, dO stay) and streams K, V: S = Q K^T, dP = dO V^T,
+//          dS as the TMEM A operand of dQ += dS K.
+// Seven MMAs per tile pair instead of five (S and dP are formed in both passes).
+//   warp 0      TMA producer (stationary pair once, streamed pairs through a ring)
+//   warp 1      MMA issuer (single thread)
+//   warps 4-7   score math for streamed columns 0-63    (one TMEM lane per thread)
+//   warps 8-11  score math for streamed columns 64-127
+// TMEM: X1 (S) | X2 (dP) | acc A | acc B, 128 columns each.  P overwrites the first half of each
+// warpgroup's own S columns, dS the same of dP, so no warpgroup writes where the other still reads.
+// A small row kernel first writes delta and lse * log2(e) into scratch, padded to whole tiles
+// (padding rows get lse = +inf, i.e. P = 0).  Every mbarrier wait is bounded.
+#include "common.cuh"
+#include "ptx.cuh"
+
+#include <cuda_bf16.h>
+
+#include <atomic>
+#include <cmath>
+
+namespace pb200 {
+namespace {
+
+using namespace ptx;
+
+constexpr int kTile = 128;            // rows of a stationary tile = rows of a streamed tile
+constexpr int kBwdThreads = 384;
+
+struct BwdParams {
+    int bh, s_q, s_kv, sq_pad;
+    int causal, causal_offset;        // query i sees keys j <= i + offset
+    float scale, scale_log2;
+    int hd;                            // head dimension of the tensors (multiple of 8, <= HD)
+};
+
+template <int HD>
+struct BwdSmem {
+    static constexpr int kStages = HD == 64 ? 3 : 2;
+    static constexpr int kTileBytes = kTile * HD * 2;
+    static constexpr int kOffStat = 0;                                  // two stationary tiles
+    static constexpr int kOffRing = 2 * kTileBytes;                     // kStages x two streamed tiles
+    static constexpr int kOffBar = kOffRing + kStages * 2 * kTileBytes;
+    static constexpr int kTotal = kOffBar + 512 + 1024;
+    static_assert(kTotal <= 227 * 1024, "shared memory budget exceeded");
+};
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);      // .x = a in the low half
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// delta[bh, i] = sum_c O[bh, i, c] * dO[bh, i, c];  lse2[bh, i] = lse[bh, i] * log2(e).
+// One warp per row; rows in [s_q, sq_pad) are written as (0, +inf).
+__global__ void __launch_bounds__(256)
+fmha_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                     const float* __restrict__ lse, float* __restrict__ delta, float* __restrict__ lse2,
+                     int bh, int s_q, int sq_pad, int hd) {
+    const int warp = (int)((blockIdx.x * blockDim.x + threadIdx.x) >> 5);
+    const int lane = threadIdx.x & 31;
+    if (warp >= bh * sq_pad) return;
+    const int b = warp / sq_pad, i = warp - b * sq_pad;
+    if (i >= s_q) {
+        if (lane == 0) { delta[warp] = 0.f; lse2[warp] = INFINITY; }
+        return;
+    }
+    const size_t row = ((size_t)b * s_q + i) * hd;
+    float acc = 0.f;
+    for (int c = lane * 8; c < hd; c += 256) {          // hd is a multiple of 8: 16-byte loads
+        const uint4 a = *reinterpret_cast<const uint4*>(o + row + c);
+        const uint4 g = *reinterpret_cast<const uint4*>(d_o + row + c);
+        const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
+        const __nv_bfloat162* pg = reinterpret_cast<const __nv_bfloat162*>(&g);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 fa = __bfloat1622float2(pa[k]), fg = __bfloat1622float2(pg[k]);
+            acc = fmaf(fa.x, fg.x, acc);
+            acc = fmaf(fa.y, fg.y, acc);
+        }
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+    if (lane == 0) {
+        delta[warp] = acc;
+        lse2[warp] = lse[(size_t)b * s_q + i] * 1.4426950408889634f;
+    }
+}
+
+// MODE 0: stationary = (K, V), streamed = (Q, dO), outputs dV (acc A) and dK (acc B).
+// MODE 1: stationary = (Q, dO), streamed = (K, V), output dQ (acc B).
+template <int HD, int MODE, typename OutT>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_constant__ CUtensorMap tmap_s2,
+                const __grid_constant__ CUtensorMap tmap_m1, const __grid_constant__ CUtensorMap tmap_m2,
+                const float* __restrict__ lse2, const float* __restrict__ delta,
+                OutT* __restrict__ out_a, OutT* __restrict__ out_b, BwdParams prm, int* status) {
+    using L = BwdSmem<HD>;
+    constexpr int kStages = L::kStages;
+    constexpr int kDBlocks = HD / 64;
+    constexpr uint32_t kIdescX = make_idesc_f16(kTile, kTile, true, 0, 0);      // both operands K-major
+    constexpr uint32_t kIdescAcc = make_idesc_f16(kTile, HD, true, 0, 1);       // B operand MN-major
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t s_stat = base + L::kOffStat, s_ring = base + L::kOffRing;
+    const uint32_t bars = base + L::kOffBar;
+    const uint32_t bar_stat = bars;                       // [1]
+    const uint32_t bar_full = bars + 8;                   // [kStages]
+    const uint32_t bar_empty = bar_full + 8 * kStages;    // [kStages]
+    const uint32_t bar_xfull = bar_empty + 8 * kStages;   // [1] S and dP of a streamed tile are in TMEM
+    const uint32_t bar_pready = bar_xfull + 8;            // [1] P and dS written (8 warps)
+    const uint32_t bar_outfull = bar_pready + 8;          // [1] accumulators complete
+    const uint32_t s_tmem_slot = bar_outfull + 8;
+    const uint32_t s_abort = s_tmem_slot + 8;
+    volatile uint32_t* tmem_slot_gen = (volatile uint32_t*)(gen + (s_tmem_slot - base));
+    volatile int* abort_gen = (volatile int*)(gen + (s_abort - base));
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int bh = (int)blockIdx.y;
+    // Stationary tile: MODE 0 counts key tiles, MODE 1 query tiles (heaviest causal tiles first).
+    const int st = MODE == 0 ? (int)blockIdx.x : (int)gridDim.x - 1 - (int)blockIdx.x;
+    const int st0 = st * kTile;
+    // Range of streamed tiles [m_begin, m_end).
+    int m_begin = 0, m_end;
+    if (MODE == 0) {
+        m_end = (prm.s_q + kTile - 1) / kTile;
+        if (prm.causal) m_begin = min(max(st0 - prm.causal_offset, 0) / kTile, m_end);   // first query that sees key st0
+    } else {
+        m_end = (prm.s_kv + kTile - 1) / kTile;
+        if (prm.causal) m_end = min(m_end, max((st0 + kTile - 1 + prm.causal_offset) / kTile + 1, 1));
+    }
+    const int n_iter = m_end - m_begin;
+
+    WaitCtx ctx{status, abort_gen, PB200_K_FLASH_ATTN_BWD};
+
+    if (threadIdx.x == 0) {
+        *abort_gen = 0;
+        mbar_init(bar_stat, 1);
+        for (int s = 0; s < kStages; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+        mbar_init(bar_xfull, 1);
+        mbar_init(bar_pready, 8);
+        mbar_init(bar_outfull, 1);
+        fence_mbarrier_init();
+        fence_proxy_async_smem();
+        prefetch_tmap(&tmap_s1); prefetch_tmap(&tmap_s2); prefetch_tmap(&tmap_m1); prefetch_tmap(&tmap_m2);
+    }
+    if (warp == 1) {
+        tmem_alloc<1>(s_tmem_slot, 512);
+        tmem_relinquish<1>();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot_gen;
+    const uint32_t tmem_x1 = tmem_base, tmem_x2 = tmem_base + 128u;
+    const uint32_t tmem_acc_a = tmem_base + 256u, tmem_acc_b = tmem_base + 384u;
+
+    if (warp == 0) {
+        // ------------------------------- TMA producer -------------------------------
+        if (lane == 0 && n_iter > 0) {
+            mbar_arrive_expect_tx(bar_stat, (uint32_t)(2 * L::kTileBytes));
+            for (int db = 0; db < kDBlocks; ++db) {
+                tma_load_3d(s_stat + db * (kTile * 128), &tmap_s1, bar_stat, db * 64, st0, bh);
+                tma_load_3d(s_stat + L::kTileBytes + db * (kTile * 128), &tmap_s2, bar_stat, db * 64, st0, bh);
+            }
+            int stage = 0; uint32_t phase = 0;
+            for (int it = 0; it < n_iter; ++it) {
+                if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, ctx, 11)) break;
+                const uint32_t dst = s_ring + stage * 2 * L::kTileBytes;
+                mbar_arrive_expect_tx(bar_full + 8 * stage, (uint32_t)(2 * L::kTileBytes));
+                for (int db = 0; db < kDBlocks; ++db) {
+                    tma_load_3d(dst + db * (kTile * 128), &tmap_m1, bar_full + 8 * stage, db * 64, (m_begin + it) * kTile, bh);
+                    tma_load_3d(dst + L::kTileBytes + db * (kTile * 128), &tmap_m2, bar_full + 8 * stage, db * 64,
+                                (m_begin + it) * kTile, bh);
+                }
+                if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------- MMA issuer ---------------------------------
+        if (lane == 0 && n_iter > 0) {
+            bool ok = mbar_wait(bar_stat, 0, ctx, 21);
+            const uint64_t sd = make_desc_kmajor_sw128(s_stat);
+            const uint64_t md = make_desc_kmajor_sw128(s_ring);
+            const uint64_t bd = make_smem_desc(s_ring, kTile * 128, 1024, 2);       // streamed tile as MN-major B
+            const uint32_t s_lo = (uint32_t)sd, s_hi = (uint32_t)(sd >> 32);
+            const uint32_t m_lo = (uint32_t)md, m_hi = (uint32_t)(md >> 32);
+            const uint32_t b_lo = (uint32_t)bd, b_hi = (uint32_t)(bd >> 32);
+            constexpr uint32_t kTileDesc = (uint32_t)(L::kTileBytes >> 4);
+            // X_t = stationary tile t . (streamed tile t of the stage)^T, contraction over head_dim
+            auto issue_x = [&](int t, int stage) {
+                const uint32_t a = s_lo + (uint32_t)t * kTileDesc;
+                const uint32_t b = m_lo + (uint32_t)(stage * 2 + t) * kTileDesc;
+#pragma unroll
+                for (int k = 0; k < HD / 16; ++k) {
+                    const uint32_t off = (uint32_t)((k >> 2) * (kTile * 8) + (k & 3) * 2);
+                    umma_f16_ss_lohi(t == 0 ? tmem_x1 : tmem_x2, a + off, s_hi, b + off, m_hi, kIdescX, k != 0 ? 1u : 0u);
+                }
+            };
+            // acc += (P or dS from TMEM) . streamed tile t, contraction over the 128 streamed rows.
+            // The operand of each warpgroup sits at the start of that warpgroup's own 64 columns.
+            auto issue_acc = [&](uint32_t acc, uint32_t a_tmem, int t, int stage, bool first) {
+                const uint32_t b = b_lo + (uint32_t)(stage * 2 + t) * kTileDesc;
+#pragma unroll
+                for (int k = 0; k < kTile / 16; ++k)
+                    umma_f16_ts_lohi(acc, a_tmem + (uint32_t)((k >> 2) * 64 + (k & 3) * 8), b + (uint32_t)(k * 128), b_hi,
+                                     kIdescAcc, (first && k == 0) ? 0u : 1u);
+            };
+            int stage = 0; uint32_t phase = 0;
+            if (ok) ok = mbar_wait(bar_full, 0, ctx, 22);
+            if (ok) {
+                tc_fence_after_sync();
+                issue_x(0, 0); issue_x(1, 0);
+                umma_commit<1>(bar_xfull);
+            }
+            for (int it = 0; it < n_iter && ok; ++it) {
+                int nstage = stage + 1; uint32_t nphase = phase;
+                if (nstage == kStages) { nstage = 0; nphase ^= 1u; }
+                const bool more = it + 1 < n_iter;
+                if (!(ok = mbar_wait(bar_pready, (uint32_t)it & 1u, ctx, 23))) break;
+                if (more && !(ok = mbar_wait(bar_full + 8 * nstage, nphase, ctx, 24))) break;
+                tc_fence_after_sync();
+                // P lives over X1, dS over X2: the next X1 may only follow the MMA that reads P, the
+                // next X2 the one that reads dS (MMAs of one thread execute in issue order).
+                if (MODE == 0) issue_acc(tmem_acc_a, tmem_x1, 1, stage, it == 0);       // dV += P^T dO
+                if (more) issue_x(0, nstage);
+                issue_acc(tmem_acc_b, tmem_x2, 0, stage, it == 0);                      // dK += dS^T Q  /  dQ += dS K
+                umma_commit<1>(bar_empty + 8 * stage);
+                if (more) { issue_x(1, nstage); umma_commit<1>(bar_xfull); }
+                stage = nstage; phase = nphase;
+            }
+            if (ok) umma_commit<1>(bar_outfull);
+        }
+    } else if (warp >= 4) {
+        // ------------------------------- score math + epilogue -----------------------
+        const int wg = (warp - 4) >> 2;                  // which 64 streamed columns
+        const int q4 = warp & 3;                         // TMEM lane quarter
+        const int row_in_tile = q4 * 32 + lane;
+        const int srow = st0 + row_in_tile;              // key (MODE 0) or query (MODE 1) of this thread
+        const uint32_t lane_off = (uint32_t)(q4 * 32) << 16;
+        const uint32_t col0 = (uint32_t)(wg * 64);
+        const uint32_t tx1 = tmem_x1 + lane_off + col0, tx2 = tmem_x2 + lane_off + col0;
+        const float* lse2_bh = lse2 + (size_t)bh * prm.sq_pad;
+        const float* delta_bh = delta + (size_t)bh * prm.sq_pad;
+        float my_lse2 = 0.f, my_delta = 0.f;
+        if (MODE == 1) { my_lse2 = lse2_bh[srow]; my_delta = delta_bh[srow]; }     // srow < sq_pad always
+        bool ok = true;
+        for (int it = 0; it < n_iter && ok; ++it) {
+            ok = mbar_wait(bar_xfull, (uint32_t)it & 1u, ctx, 31);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const int m0 = (m_begin + it) * kTile + wg * 64;      // first streamed row of this thread's columns
+            // Causal: key <= query + offset.  MODE 0: row = key, column = query; MODE 1 the other way.
+            // Whole-tile shortcut: no element of these 64 columns is hidden when the smallest query
+            // of the pairing still sees the largest key.
+            bool masked = false;
+            if (prm.causal) {
+                if (MODE == 0) masked = st0 + q4 * 32 + 31 > m0 + prm.causal_offset;
+                else masked = m0 + 63 > st0 + q4 * 32 + prm.causal_offset;
+            }
+#pragma unroll 1
+            for (int h = 0; h < 2; ++h) {                      // 32 columns at a time
+                uint32_t sx[32], dp[32];
+                tmem_ld_32x32b_x32(tx1 + (uint32_t)(h * 32), sx);
+                tmem_ld_32x32b_x32(tx2 + (uint32_t)(h * 32), dp);
+                tmem_ld_wait();
+                reg_fence(sx); reg_fence(dp);
+                uint32_t pp[16], ds[16];
+#pragma unroll
+                for (int c4 = 0; c4 < 8; ++c4) {
+                    float l4[4], d4[4];
+                    if (MODE == 0) {
+                        const float4 lv = __ldg(reinterpret_cast<const float4*>(lse2_bh + m0 + h * 32) + c4);
+                        const float4 dv = __ldg(reinterpret_cast<const float4*>(delta_bh + m0 + h * 32) + c4);
+                        l4[0] = lv.x; l4[1] = lv.y; l4[2] = lv.z; l4[3] = lv.w;
+                        d4[0] = dv.x; d4[1] = dv.y; d4[2] = dv.z; d4[3] = dv.w;
+                    } else {
+                        l4[0] = l4[1] = l4[2] = l4[3] = my_lse2;
+                        d4[0] = d4[1] = d4[2] = d4[3] = my_delta;
+                    }
+                    float p4[4], g4[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int c = c4 * 4 + e;                 // column inside this half
+                        float p = ex2(fmaf(__uint_as_float(sx[c]), prm.scale_log2, -l4[e]));
+                        if (masked) {
+                            const int mrow = m0 + h * 32 + c;     // streamed row (query in MODE 0, key in MODE 1)
+                            const bool hidden = MODE == 0 ? (srow > mrow + prm.causal_offset) : (mrow > srow + prm.causal_offset);
+                            if (hidden) p = 0.f;
+                        }
+                        p4[e] = p;
+                        g4[e] = p * (__uint_as_float(dp[c]) - d4[e]);
+                    }
+                    pp[c4 * 2] = pack_bf16(p4[0], p4[1]); pp[c4 * 2 + 1] = pack_bf16(p4[2], p4[3]);
+                    ds[c4 * 2] = pack_bf16(g4[0], g4[1]); ds[c4 * 2 + 1] = pack_bf16(g4[2], g4[3]);
+                }
+                // P over the head of this warpgroup's own S columns, dS over the head of its dP columns:
+                // half h writes columns [16h, 16h+16), all of which this thread has already read.
+                if (MODE == 0) tmem_st_32x32b_x16(tx1 + (uint32_t)(h * 16), pp);
+                tmem_st_32x32b_x16(tx2 + (uint32_t)(h * 16), ds);
+            }
+            tmem_st_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_pready);
+        }
+        // epilogue: accumulators -> global, one row per thread, each warpgroup half of head_dim
+        if (ok && n_iter > 0) {
+            ok = mbar_wait(bar_outfull, 0, ctx, 41);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        const int s_rows = MODE == 0 ? prm.s_kv : prm.s_q;
+        const bool row_exists = srow < s_rows;
+        const size_t row_off = ((size_t)bh * s_rows + srow) * prm.hd;
+#pragma unroll 1
+        for (int which = (MODE == 0 ? 0 : 1); which < 2; ++which) {
+            OutT* dst = (which == 0 ? out_a : out_b) + row_off;
+            const uint32_t acc = (which == 0 ? tmem_acc_a : tmem_acc_b) + lane_off;
+            const float mul = which == 0 ? 1.0f : prm.scale;
+#pragma unroll 1
+            for (int c = wg * (HD / 64); c < (wg + 1) * (HD / 64); ++c) {       // 32-column chunks of this warpgroup
+                uint32_t o[32];
+                if (ok && n_iter > 0) {
+                    tc_fence_after_sync();
+                    tmem_ld_32x32b_x32(acc + (uint32_t)(c * 32), o);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = 0u;                      // a tile that nothing attends to
+                }
+                if (!ok || !row_exists || c * 32 >= prm.hd) continue;
+                const int cols_here = prm.hd - c * 32;
+                if (sizeof(OutT) == 4) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        if (4 * i < cols_here)
+                            reinterpret_cast<float4*>(dst + c * 32)[i] =
+                                make_float4(__uint_as_float(o[4 * i]) * mul, __uint_as_float(o[4 * i + 1]) * mul,
+                                            __uint_as_float(o[4 * i + 2]) * mul, __uint_as_float(o[4 * i + 3]) * mul);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        if (8 * i < cols_here)
+                            reinterpret_cast<uint4*>(dst + c * 32)[i] =
+                                make_uint4(pack_bf16(__uint_as_float(o[8 * i]) * mul, __uint_as_float(o[8 * i + 1]) * mul),
+                                           pack_bf16(__uint_as_float(o[8 * i + 2]) * mul, __uint_as_float(o[8 * i + 3]) * mul),
+                                           pack_bf16(__uint_as_float(o[8 * i + 4]) * mul, __uint_as_float(o[8 * i + 5]) * mul),
+                                           pack_bf16(__uint_as_float(o[8 * i + 6]) * mul, __uint_as_float(o[8 * i + 7]) * mul));
+                }
+            }
+        }
+    }
+
+    // ------------------------------- teardown ---------------------------------------
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after_sync();
+        tmem_dealloc<1>(tmem_base, 512);
+    }
+}
+
+int tile_map(CUtensorMap* m, const void* p, int64_t hd, int64_t rows, int64_t bh, char* err) {
+    uint64_t dims[3] = {(uint64_t)hd, (uint64_t)rows, (uint64_t)bh};
+    uint64_t str[2] = {(uint64_t)hd * 2, (uint64_t)rows * hd * 2};
+    uint32_t box[3] = {64, kTile, 1};
+    return make_tensor_map(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, p, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, err);
+}
+
+template <int HD, int MODE, typename OutT>
+int launch_pass(const CUtensorMap& s1, const CUtensorMap& s2, const CUtensorMap& m1, const CUtensorMap& m2,
+                const float* lse2, const float* delta, void* out_a, void* out_b, const BwdParams& prm, int tiles,
+                cudaStream_t stream, char* err) {
+    using L = BwdSmem<HD>;
+    auto kernel = fmha_bwd_kernel<HD, MODE, OutT>;
+    static std::atomic<uint64_t> attr_set{0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!(attr_set.load(std::memory_order_relaxed) & (1ull << (dev & 63)))) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
+        if (e != cudaSuccess) { set_err(err, "cudaFuncSetAttribute(smem=%d): %s", L::kTotal, cudaGetErrorString(e)); return PB200_ERR_LAUNCH; }
+        attr_set.fetch_or(1ull << (dev & 63), std::memory_order_relaxed);
+    }
+    dim3 grid((unsigned)tiles, (unsigned)prm.bh, 1);
+    kernel<<<grid, kBwdThreads, L::kTotal, stream>>>(s1, s2, m1, m2, lse2, delta, (OutT*)out_a, (OutT*)out_b, prm, device_status_ptr());
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { set_err(err, "attention backward launch failed (HD=%d mode=%d): %s", HD, MODE, cudaGetErrorString(e)); return PB200_ERR_LAUNCH; }
+    return PB200_OK;
+}
+
+template <int HD, typename OutT>
+int launch_bwd(const Record& r, cudaStream_t stream, void** p, char* err) {
+    const int64_t BH = r.dims[0], SQ = r.dims[1], SKV = r.dims[2], hd = r.dims[3];
+    BwdParams prm;
+    prm.bh = (int)BH; prm.s_q = (int)SQ; prm.s_kv = (int)SKV;
+    prm.sq_pad = (int)((SQ + kTile - 1) / kTile * kTile);
+    prm.causal = (r.flags & PB200_F_CAUSAL) ? 1 : 0;
+    prm.causal_offset = (int)(SKV - SQ);
+    prm.scale = (float)r.fparams[0];
+    prm.scale_log2 = (float)(r.fparams[0] * 1.4426950408889634);
+    prm.hd = (int)hd;
+    // buffers: q, k, v, o, lse, do | dq, dk, dv | scratch (delta, then lse2; sq_pad floats per head each)
+    CUtensorMap tq, tk, tv, tdo;
+    if (int rc = tile_map(&tq, p[0], hd, SQ, BH, err)) return rc;
+    if (int rc = tile_map(&tk, p[1], hd, SKV, BH, err)) return rc;
+    if (int rc = tile_map(&tv, p[2], hd, SKV, BH, err)) return rc;
+    if (int rc = tile_map(&tdo, p[5], hd, SQ, BH, err)) return rc;
+    float* delta = (float*)p[9];
+    float* lse2 = delta + (size_t)BH * prm.sq_pad;
+    const int rows = (int)(BH * prm.sq_pad);
+    fmha_bwd_prep_kernel<<<(rows + 7) / 8, 256, 0, stream>>>((const __nv_bfloat16*)p[3], (const __nv_bfloat16*)p[5],
+                                                            (const float*)p[4], delta, lse2, (int)BH, (int)SQ, prm.sq_pad, (int)hd);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { set_err(err, "attention backward (row pass) launch failed: %s", cudaGetErrorString(e)); return PB200_ERR_LAUNCH; }
+    const int kv_tiles = (int)((SKV + kTile - 1) / kTile), q_tiles = (int)((SQ + kTile - 1) / kTile);
+    if (int rc = launch_pass<HD, 0, OutT>(tk, tv, tq, tdo, lse2, delta, p[8], p[7], prm, kv_tiles, stream, err)) return rc;   // dV, dK
+    return launch_pass<HD, 1, OutT>(tq, tdo, tk, tv, lse2, delta, nullptr, p[6], prm, q_tiles, stream, err);                 // dQ
+}
+
+}  // namespace
+
+// dims = {batch*heads, S_q, S_kv, head_dim}; fparams = {sm_scale} (0 -> 1/sqrt(head_dim))
+int plan_attention_bwd(Record& r, char* err) {
+    if (r.n_dims != 4) { set_err(err, "attention backward needs dims = {batch*heads, S_q, S_kv, head_dim}, got %d dims", r.n_dims); return PB200_ERR_BAD_SHAPE; }
+    const int64_t BH = r.dims[0], SQ = r.dims[1], SKV = r.dims[2], HD = r.dims[3];
+    if (BH < 1 || SQ < 1 || SKV < 1) { set_err(err, "batch*heads, S_q, S_kv must be positive"); return PB200_ERR_BAD_SHAPE; }
+    if (HD < 8 || HD > 128 || HD % 8 != 0) { set_err(err, "head_dim=%lld must be a multiple of 8 in [8, 128]", (long long)HD); return PB200_ERR_BAD_SHAPE; }
+    if (SQ > 0x7fffffffLL / 256 || SKV > 0x7fffffffLL / 256) { set_err(err, "sequence length too large"); return PB200_ERR_BAD_SHAPE; }
+    if ((r.flags & PB200_F_CAUSAL) && SKV < SQ) { set_err(err, "causal attention needs S_kv >= S_q"); return PB200_ERR_BAD_SHAPE; }
+    if (BH > 65535) { set_err(err, "batch*heads=%lld exceeds 65535", (long long)BH); return PB200_ERR_BAD_SHAPE; }
+    if (r.n_fparams < 1 || r.fparams[0] == 0.0) { r.fparams[0] = 1.0 / std::sqrt((double)HD); r.n_fparams = 1; }
+    pb200_geometry& g = r.geom;
+    const int64_t sq_pad = (SQ + kTile - 1) / kTile * kTile;
+    // geometry of the dK/dV pass (the dQ pass has one CTA per query tile)
+    g.grid[0] = (uint32_t)((SKV + kTile - 1) / kTile); g.grid[1] = (uint32_t)BH; g.grid[2] = 1;
+    g.block[0] = kBwdThreads; g.block[1] = g.block[2] = 1;
+    g.cluster[0] = g.cluster[1] = g.cluster[2] = 1;
+    g.smem_bytes = HD <= 64 ? BwdSmem<64>::kTotal : BwdSmem<128>::kTotal;
+    g.n_inputs = 6; g.n_outputs = 3;
+    g.scratch_bytes = (uint64_t)(2 * BH * sq_pad * sizeof(float));
+    return PB200_OK;
+}
+
+int launch_attention_bwd(const Record& r, cudaStream_t stream, void** p, char* err) {
+    const int64_t HD = r.dims[3];
+    const bool bf16_out = (r.flags & PB200_F_OUT_BF16) != 0;
+    if (HD <= 64) return bf16_out ? launch_bwd<64, __nv_bfloat16>(r, stream, p, err) : launch_bwd<64, float>(r, stream, p, err);
+    return bf16_out ? launch_bwd<128, __nv_bfloat16>(r, stream, p, err) : launch_bwd<128, float>(r, stream, p, err);
+}
+
+}  // namespace pb200

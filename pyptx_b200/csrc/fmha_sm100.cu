@@ -139,6 +139,32 @@ __device__ __forceinline__ void add2(float& acc0, float& acc1, float p0, float p
         : "+f"(acc0), "+f"(acc1) : "f"(p0), "f"(p1));
 }
 
+// 32 raw scores -> 16 packed bf16 pairs of P = 2^(s * scale - m), row sums into sum4.  Per pair of
+// scores: one FFMA2, two exponentials (MUFU, or the FMA-pipe form for FMA_OF8 of every 8 pairs),
+// one FADD2, one pack.
+template <int FMA_OF8>
+__device__ __forceinline__ void exp_chunk(const uint32_t (&v)[32], uint32_t* packed, float (&sum4)[4],
+                                          float scale_log2, float neg_m) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        float t0, t1;
+        fma2(t0, t1, __uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]), scale_log2, neg_m);
+        float p0, p1;
+        if ((i & 7) < FMA_OF8) exp2_fma_pair(p0, p1, t0, t1);   // compile-time choice per pair
+        else { p0 = fast_exp2(t0); p1 = fast_exp2(t1); }
+        add2(sum4[2 * (i & 1)], sum4[2 * (i & 1) + 1], p0, p1);
+        __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);        // .x = p0 in the low half
+        packed[i] = *reinterpret_cast<uint32_t*>(&b);
+    }
+}
+
+#ifndef PB200_FMHA_SETMAXNREG
+#define PB200_FMHA_SETMAXNREG 1
+#endif
+#ifndef PB200_FMHA_SPEC_MAX
+#define PB200_FMHA_SPEC_MAX 1
+#endif
+
 template <int HD, typename OutT, bool P_SMEM>
 __global__ void __launch_bounds__(kFmhaThreads, 1)
 fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
@@ -228,6 +254,13 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     constexpr bool kSplitP = PB200_FMHA_SPLIT_P && HD == 64 && !P_SMEM;
     const uint32_t tmem_p[2] = {kSplitP ? tmem_o[0] + 64u : tmem_s[0], kSplitP ? tmem_o[1] + 64u : tmem_s[1]};
 
+    // Registers move from the TMA / MMA warpgroup (two single-thread roles) to the softmax
+    // warpgroups; each setmaxnreg sits at the head of its own branch so that the compiler sees which
+    // budget governs which code.
+    if (warp < 4) {
+#if PB200_FMHA_SETMAXNREG
+    reg_dealloc<96>();
+#endif
     if (warp == 0) {
         // ------------------------------- TMA producer -------------------------------
         if (lane == 0) {
@@ -347,7 +380,11 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 }
             }
         }
-    } else if (warp >= 4) {
+    }
+    } else {
+#if PB200_FMHA_SETMAXNREG
+        reg_alloc<208>();
+#endif
         // ------------------------------- softmax + epilogue --------------------------
         const int t = (warp - 4) >> 2;                   // query tile of this warp group
         const int q = warp & 3;                          // TMEM lane quarter
@@ -372,27 +409,34 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
             // Tiles that cross the diagonal (for any row of this warp) or the end of K/V take the masked path.
             const bool diag = (prm.causal && (key0 + kKvTile - 1 > q0 + t * kQTile + q * 32 + prm.causal_offset)) ||
                               (key0 + kKvTile > prm.s_kv);
-            // The whole score row (128 fp32) comes out of TMEM once: four loads in flight, one wait.
-            uint32_t sc[kKvTile];
-#pragma unroll
-            for (int c = 0; c < kKvTile / 32; ++c)
-                tmem_ld_32x32b_x32(ts + (uint32_t)(c * 32), *reinterpret_cast<uint32_t(*)[32]>(&sc[c * 32]));
-            tmem_ld_wait();
-            reg_fence(sc);
-            // row maximum of the raw scores: four independent chains of 3-input max
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-            if (diag) {
-#pragma unroll
-                for (int i = 0; i < kKvTile; ++i)
-                    if (key0 + i <= last_visible) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sc[i]));
-            } else {
-#pragma unroll
-                for (int i = 0; i < kKvTile; i += 8) {
-                    mx4[0] = fmax3(mx4[0], __uint_as_float(sc[i]), __uint_as_float(sc[i + 1]));
-                    mx4[1] = fmax3(mx4[1], __uint_as_float(sc[i + 2]), __uint_as_float(sc[i + 3]));
-                    mx4[2] = fmax3(mx4[2], __uint_as_float(sc[i + 4]), __uint_as_float(sc[i + 5]));
-                    mx4[3] = fmax3(mx4[3], __uint_as_float(sc[i + 6]), __uint_as_float(sc[i + 7]));
-                }
+            // Fast path (every tile but the first, the diagonal and the ragged ones): the exponentials
+            // are taken against the reference maximum already in use, without a maximum pass and so
+            // without its serial dependency.  P stays in registers until the row sums say it is valid:
+            // every P <= 2^8 is implied by a tile sum <= 2^8, which is the lazy-rescale invariant.  A
+            // larger sum (the running maximum moved, or many scores sit just below 2^8) sends the
+            // whole warp to the exact path below, which reads S again (nothing was stored yet).
+            bool slow = (j == 0) || diag || !PB200_FMHA_SPEC_MAX;
+            bool forced = false;
+            uint32_t packed[kKvTile / 2];
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            if (!slow) {
+                const float neg_m = -m_used;
+                uint32_t v0[32], v1[32];
+                tmem_ld_32x32b_x32(ts, v0);
+                tmem_ld_32x32b_x32(ts + 32u, v1);
+                tmem_ld_wait();
+                reg_fence(v0); reg_fence(v1);
+                exp_chunk<kFmaExpPairsOf8<HD>>(v0, &packed[0], sum4, prm.scale_log2, neg_m);
+                tmem_ld_32x32b_x32(ts + 64u, v0);
+                exp_chunk<kFmaExpPairsOf8<HD>>(v1, &packed[16], sum4, prm.scale_log2, neg_m);
+                tmem_ld_32x32b_x32(ts + 96u, v1);
+                tmem_ld_wait();
+                reg_fence(v0); reg_fence(v1);
+                exp_chunk<kFmaExpPairsOf8<HD>>(v0, &packed[32], sum4, prm.scale_log2, neg_m);
+                exp_chunk<kFmaExpPairsOf8<HD>>(v1, &packed[48], sum4, prm.scale_log2, neg_m);
+                const float tile_sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+                slow = __any_sync(0xffffffffu, !(tile_sum <= 256.0f));
+                forced = slow;
             }
             if (kSplitP && j > 0) {
                 // P(j-1) V(j-1) must have retired before O is rescaled or P is overwritten
@@ -401,77 +445,113 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 if (!ok) break;
                 tc_fence_after_sync();
             }
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            const float m_new = fmaxf(m_used, mx * prm.scale_log2);
-            if (j == 0) {
-                m_used = m_new;
-            } else if (__any_sync(0xffffffffu, m_new - m_used > kRescaleThreshold)) {
-                const float alpha = fast_exp2(m_used - m_new);     // 1 for lanes whose maximum did not move
-                m_used = m_new;
-                l *= alpha;
-#pragma unroll 1
-                for (int c = 0; c < HD / 32; ++c) {
-                    uint32_t o[32];
-                    tmem_ld_32x32b_x32(to + (uint32_t)(c * 32), o);
-                    tmem_ld_wait();
+            if (!slow) {
+                if (P_SMEM) {
+                    const uint32_t rowp = s_p + t * L::kPBytes + (uint32_t)row_in_tile * 128u;
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                    tmem_st_32x32b_x32(to + (uint32_t)(c * 32), o);
+                    for (int c8 = 0; c8 < 16; ++c8)      // 16-byte chunks of 8 keys: 8 per 64-key block
+                        st_shared_v4(rowp + (uint32_t)(c8 >> 3) * (kQTile * 128) + (((uint32_t)(c8 & 7) ^ (uint32_t)(row_in_tile & 7)) << 4),
+                                     packed[4 * c8], packed[4 * c8 + 1], packed[4 * c8 + 2], packed[4 * c8 + 3]);
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        tmem_st_32x32b_x16(tp + (uint32_t)(c * 16), *reinterpret_cast<uint32_t(*)[16]>(&packed[c * 16]));
                 }
-                tmem_st_wait();
-            }
-            // P = exp2(S * scale - m_used): the scores are read again in two halves of 64 (two loads in
-            // flight per wait), exponentiated, summed and written back as bf16 P to TMEM (or shared memory).
-            const float neg_m = -m_used;
-            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 1
-            for (int h = 0; h < 2; ++h) {
-                uint32_t v[64];
-                tmem_ld_32x32b_x32(ts + (uint32_t)(h * 64), *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
-                tmem_ld_32x32b_x32(ts + (uint32_t)(h * 64 + 32), *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+            } else {
+                sum4[0] = sum4[1] = sum4[2] = sum4[3] = 0.f;
+                // The whole score row (128 fp32) comes out of TMEM once: four loads in flight, one wait.
+                uint32_t sc[kKvTile];
+#pragma unroll
+                for (int c = 0; c < kKvTile / 32; ++c)
+                    tmem_ld_32x32b_x32(ts + (uint32_t)(c * 32), *reinterpret_cast<uint32_t(*)[32]>(&sc[c * 32]));
                 tmem_ld_wait();
-                reg_fence(v);
+                reg_fence(sc);
+                // row maximum of the raw scores: four independent chains of 3-input max
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                if (diag) {
 #pragma unroll
-                for (int cc = 0; cc < 2; ++cc) {
-                    const int c = h * 2 + cc;          // 32-key chunk index
-                    uint32_t packed[16];
-                    if (!diag) {
-                        // Common case, no mask: per pair of scores one FFMA2, two EX2, one FADD2, one pack.
+                    for (int i = 0; i < kKvTile; ++i)
+                        if (key0 + i <= last_visible) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sc[i]));
+                } else {
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            float t0, t1;
-                            fma2(t0, t1, __uint_as_float(v[cc * 32 + 2 * i]), __uint_as_float(v[cc * 32 + 2 * i + 1]),
-                                 prm.scale_log2, neg_m);
-                            float p0, p1;
-                            if ((i & 7) < kFmaExpPairsOf8<HD>) exp2_fma_pair(p0, p1, t0, t1);   // compile-time choice per pair
-                            else { p0 = fast_exp2(t0); p1 = fast_exp2(t1); }
-                            add2(sum4[2 * (i & 1)], sum4[2 * (i & 1) + 1], p0, p1);
-                            __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);    // .x = p0 in the low half
-                            packed[i] = *reinterpret_cast<uint32_t*>(&b);
-                        }
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            float p0 = fast_exp2(fmaf(__uint_as_float(v[cc * 32 + 2 * i]), prm.scale_log2, neg_m));
-                            float p1 = fast_exp2(fmaf(__uint_as_float(v[cc * 32 + 2 * i + 1]), prm.scale_log2, neg_m));
-                            if (key0 + c * 32 + 2 * i > last_visible) p0 = 0.f;
-                            if (key0 + c * 32 + 2 * i + 1 > last_visible) p1 = 0.f;
-                            sum4[i & 3] += p0 + p1;
-                            __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
-                            packed[i] = *reinterpret_cast<uint32_t*>(&b);
-                        }
+                    for (int i = 0; i < kKvTile; i += 8) {
+                        mx4[0] = fmax3(mx4[0], __uint_as_float(sc[i]), __uint_as_float(sc[i + 1]));
+                        mx4[1] = fmax3(mx4[1], __uint_as_float(sc[i + 2]), __uint_as_float(sc[i + 3]));
+                        mx4[2] = fmax3(mx4[2], __uint_as_float(sc[i + 4]), __uint_as_float(sc[i + 5]));
+                        mx4[3] = fmax3(mx4[3], __uint_as_float(sc[i + 6]), __uint_as_float(sc[i + 7]));
                     }
-                    if (P_SMEM) {
-                        // K-major SWIZZLE_128B image: 64-key blocks of [128 rows][128 bytes]
-                        const uint32_t rowp = s_p + t * L::kPBytes + (uint32_t)h * (kQTile * 128) + (uint32_t)row_in_tile * 128u;
+                }
+                const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+                const float m_new = fmaxf(m_used, mx * prm.scale_log2);
+                if (j == 0) {
+                    m_used = m_new;
+                } else if (__any_sync(0xffffffffu, m_new - m_used > (forced ? 0.0f : kRescaleThreshold))) {
+                    const float alpha = fast_exp2(m_used - m_new);     // 1 for lanes whose maximum did not move
+                    m_used = m_new;
+                    l *= alpha;
+#pragma unroll 1
+                    for (int c = 0; c < HD / 32; ++c) {
+                        uint32_t o[32];
+                        tmem_ld_32x32b_x32(to + (uint32_t)(c * 32), o);
+                        tmem_ld_wait();
 #pragma unroll
-                        for (int jj = 0; jj < 4; ++jj) {
-                            const uint32_t chunk = (uint32_t)(cc * 4 + jj);
-                            st_shared_v4(rowp + ((chunk ^ (uint32_t)(row_in_tile & 7)) << 4),
-                                         packed[4 * jj], packed[4 * jj + 1], packed[4 * jj + 2], packed[4 * jj + 3]);
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st_32x32b_x32(to + (uint32_t)(c * 32), o);
+                    }
+                    tmem_st_wait();
+                }
+                // P = exp2(S * scale - m_used): the scores are read again in two halves of 64 (two loads in
+                // flight per wait), exponentiated, summed and written back as bf16 P to TMEM (or shared memory).
+                const float neg_m = -m_used;
+#pragma unroll 1
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t v[64];
+                    tmem_ld_32x32b_x32(ts + (uint32_t)(h * 64), *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+                    tmem_ld_32x32b_x32(ts + (uint32_t)(h * 64 + 32), *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+                    tmem_ld_wait();
+                    reg_fence(v);
+#pragma unroll
+                    for (int cc = 0; cc < 2; ++cc) {
+                        const int c = h * 2 + cc;          // 32-key chunk index
+                        uint32_t pk[16];
+                        if (!diag) {
+                            // Common case, no mask: per pair of scores one FFMA2, two EX2, one FADD2, one pack.
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                float t0, t1;
+                                fma2(t0, t1, __uint_as_float(v[cc * 32 + 2 * i]), __uint_as_float(v[cc * 32 + 2 * i + 1]),
+                                     prm.scale_log2, neg_m);
+                                float p0, p1;
+                                if ((i & 7) < kFmaExpPairsOf8<HD>) exp2_fma_pair(p0, p1, t0, t1);   // compile-time choice per pair
+                                else { p0 = fast_exp2(t0); p1 = fast_exp2(t1); }
+                                add2(sum4[2 * (i & 1)], sum4[2 * (i & 1) + 1], p0, p1);
+                                __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);    // .x = p0 in the low half
+                                pk[i] = *reinterpret_cast<uint32_t*>(&b);
+                            }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                float p0 = fast_exp2(fmaf(__uint_as_float(v[cc * 32 + 2 * i]), prm.scale_log2, neg_m));
+                                float p1 = fast_exp2(fmaf(__uint_as_float(v[cc * 32 + 2 * i + 1]), prm.scale_log2, neg_m));
+                                if (key0 + c * 32 + 2 * i > last_visible) p0 = 0.f;
+                                if (key0 + c * 32 + 2 * i + 1 > last_visible) p1 = 0.f;
+                                sum4[i & 3] += p0 + p1;
+                                __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
+                                pk[i] = *reinterpret_cast<uint32_t*>(&b);
+                            }
                         }
-                    } else {
-                        tmem_st_32x32b_x16(tp + (uint32_t)(c * 16), packed);
+                        if (P_SMEM) {
+                            // K-major SWIZZLE_128B image: 64-key blocks of [128 rows][128 bytes]
+                            const uint32_t rowp = s_p + t * L::kPBytes + (uint32_t)h * (kQTile * 128) + (uint32_t)row_in_tile * 128u;
+#pragma unroll
+                            for (int jj = 0; jj < 4; ++jj) {
+                                const uint32_t chunk = (uint32_t)(cc * 4 + jj);
+                                st_shared_v4(rowp + ((chunk ^ (uint32_t)(row_in_tile & 7)) << 4),
+                                             pk[4 * jj], pk[4 * jj + 1], pk[4 * jj + 2], pk[4 * jj + 3]);
+                            }
+                        } else {
+                            tmem_st_32x32b_x16(tp + (uint32_t)(c * 16), pk);
+                        }
                     }
                 }
             }

@@ -65,7 +65,7 @@ peer_barrier_kernel(FlagBlocks flags, int world, int rank, uint64_t timeout_ns, 
     while ((int32_t)(ld_acquire_sys(mine + p) - epoch) < 0) {
         __nanosleep(64);
         if ((++spins & 255u) == 0 && global_timer_ns() - t0 > timeout_ns) {
-            if (atomicCAS(status, 0, PB200_ERR_DEVICE_TIMEOUT) == 0) {
+            if (status != nullptr && atomicCAS(status, 0, PB200_ERR_DEVICE_TIMEOUT) == 0) {
                 status[1] = kernel_id;
                 status[2] = p;
                 status[3] = rank;
@@ -100,7 +100,10 @@ int launch_peer_barrier(const Record& r, cudaStream_t stream, void** p, char* er
     const int world = (int)r.dims[0];
     for (int i = 0; i < world; ++i) f.block[i] = (uint32_t*)p[i];
     const uint64_t timeout_ns = (uint64_t)(r.fparams[0] * 1e9);
-    peer_barrier_kernel<<<1, 32, 0, stream>>>(f, world, (int)r.dims[1], timeout_ns, device_status_ptr(), r.kernel_id);
+    int* status = device_status_ptr();
+    // Without the status word a timed-out wait could not be reported: refuse to launch.
+    if (status == nullptr) { set_err(err, "peer barrier: the device status word is not available on this device"); return PB200_ERR_NO_CUDA; }
+    peer_barrier_kernel<<<1, 32, 0, stream>>>(f, world, (int)r.dims[1], timeout_ns, status, r.kernel_id);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { set_err(err, "peer barrier launch failed: %s", cudaGetErrorString(e)); return PB200_ERR_LAUNCH; }
     return PB200_OK;

@@ -369,6 +369,9 @@ RowConfig pick_row_config(int64_t n4, int threads = 0) {
     return {1024, 0};  // long-row kernel
 }
 
+// Return code of this thread's last cudaLaunchKernelEx (launch_row reads it after the dispatch).
+thread_local cudaError_t t_launch_rc = cudaSuccess;
+
 // Launch with the programmatic-serialization attribute (see pdl_prologue).
 template <typename... KArgs, typename... Args>
 void launch_pdl(void (*kernel)(KArgs...), dim3 grid, int threads, cudaStream_t s, Args... args) {
@@ -382,7 +385,7 @@ void launch_pdl(void (*kernel)(KArgs...), dim3 grid, int threads, cudaStream_t s
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+    t_launch_rc = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
 template <int THREADS, int VPT, typename OutT>
@@ -465,6 +468,7 @@ int launch_row(const Record& r, cudaStream_t s, void** p, char* err) {
     const float eps = (float)r.fparams[0];
     dim3 grid(r.geom.grid[0]);
     const bool bf16_out = (r.flags & PB200_F_OUT_BF16) != 0;
+    t_launch_rc = cudaSuccess;
     if (r.kernel_id == PB200_K_SWIGLU) {
         const int tune = (int)r.dims[7];
         const size_t total4 = (size_t)rows * n4;
@@ -490,6 +494,7 @@ int launch_row(const Record& r, cudaStream_t s, void** p, char* err) {
 #undef PB200_ROW_CASE
     }
     cudaError_t e = cudaGetLastError();
+    if (t_launch_rc != cudaSuccess) e = t_launch_rc;
     if (e != cudaSuccess) { set_err(err, "row kernel launch failed: %s", cudaGetErrorString(e)); return PB200_ERR_LAUNCH; }
     return PB200_OK;
 }

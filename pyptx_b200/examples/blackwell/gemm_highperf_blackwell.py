@@ -47,7 +47,8 @@ def _out_flags(out_dtype: PtxType) -> int:
 def build_gemm(M: int, N: int, K: int, *, arch: str = "sm_100a", stages: int = STAGES,
                grid_minor_dim: str = GRID_MINOR_DIM, grid_tile_width: int = GRID_TILE_WIDTH,
                out_dtype: PtxType = f32, tile: str = "auto", bias: bool = False,
-               activation: str | None = None) -> NativeKernel:
+               activation: str | None = None, _name: str = "blackwell_gemm",
+               _meta: dict | None = None) -> NativeKernel:
     """Kernel ``k(A[M,K] bf16, B_T[N,K] bf16) -> D[M,N]``.
 
     ``stages`` and ``grid_minor_dim`` are accepted and validated as in the
@@ -71,12 +72,13 @@ def build_gemm(M: int, N: int, K: int, *, arch: str = "sm_100a", stages: int = S
     dims = (M, N, K) if grid_tile_width == GRID_TILE_WIDTH else (M, N, K, grid_tile_width)
     epi_flags, epi_inputs = _epilogue(N, bias, activation)
     return NativeKernel(
-        "blackwell_gemm", K_GEMM_1SM, dims,
+        _name, K_GEMM_1SM, dims,
         in_specs=(Tile(M, K, bf16, Layout.TMA_128B, tma_box=(BM, BK)),
                   Tile(N, K, bf16, Layout.TMA_128B, tma_box=(BN, BK))) + epi_inputs,
         out_specs=(Tile(M, N, out_dtype, Layout.ROW),),
         flags=_out_flags(out_dtype) | _TILE_FLAGS[tile] | epi_flags, arch=arch,
-        meta={"stages": stages, "grid_minor_dim": grid_minor_dim, "grid_tile_width": grid_tile_width, "tile": tile},
+        meta=dict({"stages": stages, "grid_minor_dim": grid_minor_dim, "grid_tile_width": grid_tile_width,
+                   "tile": tile}, **(_meta or {})),
     )
 
 
@@ -116,11 +118,14 @@ def build_gemm_persistent(M: int, N: int, K: int, *, arch: str = "sm_100a", stag
                           out_dtype: PtxType = f32) -> NativeKernel:
     """The reference's persistent 1-SM entry point (gemm_highperf_blackwell.py:316-326), same call
     convention as :func:`build_gemm`.  Every kernel of this library is persistent (one CTA per SM
-    walks a static tile list), so this is :func:`build_gemm` with the reference's default band of 8;
-    ``num_ctas`` is accepted and validated, the grid is always one CTA per SM (or per tile if fewer)."""
+    walks a static tile list), so this is an alias of :func:`build_gemm` with the reference's default
+    band of 8 and the reference's kernel name (``blackwell_gemm_persistent``, :370).  ``num_ctas`` and
+    ``stages`` are validated and recorded in ``meta`` but do not shape the launch: the grid is always
+    one CTA per SM (or per tile if fewer) and the ring depth follows from the tile shape."""
     assert num_ctas is None or num_ctas >= 1, "num_ctas must be positive"
     return build_gemm(M, N, K, arch=arch, stages=stages, grid_minor_dim=grid_minor_dim,
-                      grid_tile_width=grid_tile_width, out_dtype=out_dtype)
+                      grid_tile_width=grid_tile_width, out_dtype=out_dtype,
+                      _name="blackwell_gemm_persistent", _meta={"num_ctas": num_ctas})
 
 
 def gemm_flops(M: int, N: int, K: int) -> int:

@@ -20,6 +20,7 @@ anything is enqueued.
 from __future__ import annotations
 
 import ctypes
+import threading
 from typing import Any, Sequence
 
 from . import _native
@@ -84,8 +85,9 @@ def extract_input_shapes(inputs) -> list[tuple[int, ...]]:
 # ---------------------------------------------------------------------------
 
 class _Launcher:
-    """Per-kernel cached state for the eager path: ctypes objects are reused so a
-    steady-state call does no Python allocation beyond the output tensors."""
+    """Per-kernel cached state for the eager path.  The ctypes pointer array and error buffer
+    are reused between calls, but each host thread has its own pair: ctypes releases the GIL
+    around the call, so a shared array could be refilled by another thread mid-launch."""
 
     def __init__(self, kernel) -> None:
         self.lib = _native.load()
@@ -93,9 +95,7 @@ class _Launcher:
         self.n_in = len(kernel.in_specs)
         self.scratch_bytes = kernel.scratch_bytes
         self.n = self.n_in + len(kernel.out_specs) + (1 if self.scratch_bytes else 0)
-        self.ptrs = (ctypes.c_void_p * self.n)()
-        self.ptrs_ref = ctypes.cast(self.ptrs, ctypes.c_void_p)
-        self.err = ctypes.create_string_buffer(_native.ERR_LEN)
+        self._tls = threading.local()
         self.in_dtypes = [_ptx_type_to_torch_dtype(s.dtype) for s in kernel.in_specs]
         self.out_dtypes = [_ptx_type_to_torch_dtype(s.dtype) for s in kernel.out_specs]
         self.static_out_shapes = None
@@ -109,6 +109,16 @@ class _Launcher:
                  torch.float16: 5, torch.float32: 6, torch.float64: 7, torch.bool: 11, torch.bfloat16: 15}
         self.out_dtype_codes = [codes[d] for d in self.out_dtypes]
         self.handle_int = int(kernel.handle)
+
+
+    def call_buffers(self):
+        """This thread's (pointer array, its address, error buffer)."""
+        tls = self._tls
+        if not hasattr(tls, "ptrs"):
+            tls.ptrs = (ctypes.c_void_p * self.n)()
+            tls.ptrs_ref = ctypes.cast(tls.ptrs, ctypes.c_void_p)
+            tls.err = ctypes.create_string_buffer(_native.ERR_LEN)
+        return tls.ptrs, tls.ptrs_ref, tls.err
 
 
 def _check_inputs(kernel, launcher: _Launcher, inputs) -> dict[str, int]:
@@ -168,7 +178,7 @@ def call_kernel_via_torch(kernel, inputs: Sequence[Any]):
         return res[:-1] if launcher.scratch_bytes else res
     dtypes = launcher.out_dtypes + ([torch.uint8] if launcher.scratch_bytes else [])
     outs = [torch.empty(shp, dtype=dt, device=dev) for shp, dt in zip(shapes, dtypes)]
-    ptrs = launcher.ptrs
+    ptrs, ptrs_ref, err = launcher.call_buffers()
     for i, t in enumerate(inputs):
         ptrs[i] = t.data_ptr()
     for i, t in enumerate(outs):
@@ -176,12 +186,12 @@ def call_kernel_via_torch(kernel, inputs: Sequence[Any]):
     if torch.cuda.current_device() != dev.index:
         with torch.cuda.device(dev):
             stream = torch.cuda.current_stream(dev).cuda_stream
-            rc = launcher.lib.pb200_launch_raw(launcher.handle, stream, launcher.ptrs_ref, launcher.n, launcher.err)
+            rc = launcher.lib.pb200_launch_raw(launcher.handle, stream, ptrs_ref, launcher.n, err)
     else:
         stream = torch.cuda.current_stream(dev).cuda_stream
-        rc = launcher.lib.pb200_launch_raw(launcher.handle, stream, launcher.ptrs_ref, launcher.n, launcher.err)
+        rc = launcher.lib.pb200_launch_raw(launcher.handle, stream, ptrs_ref, launcher.n, err)
     if rc != 0:
-        msg = launcher.err.value.decode("utf-8", errors="replace")
+        msg = err.value.decode("utf-8", errors="replace")
         raise RuntimeError(f"pyptx_b200: pb200_launch_raw failed (code {rc}): {msg}")
     return outs[:-1] if launcher.scratch_bytes else outs
 
@@ -245,24 +255,38 @@ def call_kernel_via_torch_compile(kernel, inputs: Sequence[Any]):
 
 def differentiable_kernel(forward_kernel, backward_kernel, *,
                           save_for_backward: Sequence[int] | None = None,
-                          num_grad_inputs: int | None = None):
+                          num_grad_inputs: int | None = None,
+                          save_outputs: Sequence[int] | None = None,
+                          visible_outputs: Sequence[int] | None = None):
     """Wrap a forward / backward kernel pair in a ``torch.autograd.Function``.
 
     ``backward_kernel`` is called with ``(*saved_inputs, *grad_outputs)`` and
     returns one gradient per differentiable input; missing trailing gradients
     are filled with ``None`` (pyptx/torch_support.py:446-519).
+
+    Two additions for forwards that emit statistics next to their result (attention's
+    log-sum-exp): ``save_outputs`` lists forward outputs to keep for the backward pass, which then
+    receives ``(*saved_inputs, *saved_outputs, *grad_outputs)``; ``visible_outputs`` lists the
+    forward outputs the caller gets back (default: all), and gradients arrive for those only.
     """
     torch = _torch()
     saved_idx = None if save_for_backward is None else list(save_for_backward)
+    out_keep = [] if save_outputs is None else list(save_outputs)
+    out_show = None if visible_outputs is None else list(visible_outputs)
 
     class _Fn(torch.autograd.Function):
         @staticmethod
         def forward(ctx, *inputs):
             keep = inputs if saved_idx is None else tuple(inputs[i] for i in saved_idx)
-            ctx.save_for_backward(*keep)
             ctx.n_inputs = len(inputs)
             with torch.no_grad():
-                return forward_kernel(*inputs)
+                outs = forward_kernel(*inputs)
+            all_outs = outs if isinstance(outs, tuple) else (outs,)
+            ctx.save_for_backward(*keep, *(all_outs[i] for i in out_keep))
+            if out_show is None:
+                return outs
+            shown = tuple(all_outs[i] for i in out_show)
+            return shown[0] if len(shown) == 1 else shown
 
         @staticmethod
         def backward(ctx, *grad_outputs):

@@ -2,7 +2,7 @@
 
 Run in a container that has the reference checked out (read-only is enough):
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference   (or set PYPTX_REFERENCE_DIR)
 
 What it records:
 
@@ -160,7 +160,9 @@ def matmul_refs() -> dict:
 
 
 def main() -> None:
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("PYPTX_REFERENCE_DIR", "")
+    if not os.path.isdir(os.path.join(ref_root, "pyptx")):
+        raise SystemExit("usage: make_golden.py <reference tree>  (or set PYPTX_REFERENCE_DIR)")
     install_jax_stand_in()
     sys.path.insert(0, ref_root)
     with open(os.path.join(HERE, "encodings.json"), "w") as f:

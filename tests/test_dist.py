@@ -127,3 +127,68 @@ def test_two_rank_gloo_shard_and_gather(rows):
         ok_local, ok_full, tmax, local = got[r]
         assert ok_local and ok_full and tmax == 2.0
     assert got[0][3] + got[1][3] == rows
+
+
+def _worker_empty_rank_and_attention(rank: int, world: int, port: int, results):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from pyptx_b200.types import bf16, f32
+        torch.manual_seed(0)
+        # GEMM whose M holds one 256-row unit: rank 1 owns nothing and must still enter the
+        # collective with D's trailing shape and dtype (f32 [., N]), not A's (bf16 [., K]).
+        M, N, K = 256, 48, 32
+        a = torch.randn(M, K).to(torch.bfloat16)
+        bt = torch.randn(N, K).to(torch.bfloat16)
+
+        def build_gemm_2sm(m, n, k, **kw):
+            return lambda x, y: x.float() @ y.float().t()
+
+        sh = pdist.shard_gemm(build_gemm_2sm, M, N, K, gather=True)
+        full = sh(sh.slice(a), bt)
+        ok_gemm = (sh.local == (256 if rank == 0 else 0) and full.dtype == torch.float32
+                   and torch.equal(full, a.float() @ bt.float().t()))
+        # zero rows everywhere: nothing to gather, no collective, an empty result
+        none = pdist.Shard(None, 0, 0, 0, world, rank, 1, True, None, (5,), f32)(torch.empty(0, 3))
+        ok_none = tuple(none.shape) == (0, 5)
+        # attention: local outputs are [1, local, S, d]; the gathered one is [1, B*H, S, d]
+        B, H, S, d = 1, 3, 4, 8
+        q = torch.randn(B * H, S, d).to(torch.bfloat16)
+
+        def build_attn(batch, heads, sq, skv, hd, **kw):
+            return lambda qq: (qq.float() * 2).to(torch.bfloat16)
+
+        sa = pdist.shard_attention(build_attn, B, H, S, None, d, gather=True, out_dtype=bf16)
+        o = sa(sa.slice(q).unsqueeze(0))
+        ok_attn = tuple(o.shape) == (1, B * H, S, d) and torch.equal(o[0], (q.float() * 2).to(torch.bfloat16))
+
+        # a kernel with two outputs (O, lse): the first is gathered, the second stays local
+        def build_attn_lse(batch, heads, sq, skv, hd, **kw):
+            return lambda qq: ((qq.float() * 2).to(torch.bfloat16), qq.float().sum(-1))
+
+        sl = pdist.shard_attention(build_attn_lse, B, H, S, None, d, gather=True)
+        o2, lse = sl(sl.slice(q).unsqueeze(0))
+        ok_lse = tuple(o2.shape) == (1, B * H, S, d) and tuple(lse.shape) == (1, sl.local, S)
+        results[rank] = (ok_gemm, ok_none, ok_attn, ok_lse)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_gloo_empty_rank_and_attention_gather():
+    world = 2
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        results = mgr.dict()
+        procs = [ctx.Process(target=_worker_empty_rank_and_attention, args=(r, world, port, results))
+                 for r in range(world)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(timeout=120)
+            assert p.exitcode == 0
+        got = dict(results)
+    assert set(got) == {0, 1}
+    for r in range(world):
+        assert got[r] == (True, True, True, True), got[r]

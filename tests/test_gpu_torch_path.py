@@ -57,6 +57,30 @@ def test_raw_c_abi_call():
     lib.pb200_destroy(h)
 
 
+def test_raw_c_abi_call_rejects_memory_the_gpu_cannot_reach():
+    """The first launch of a handle looks at where its buffers live: pageable host memory is
+    refused with a code and a message, before any kernel could fault on it."""
+    import numpy as np
+
+    lib = _native.load()
+    x, w = inputs.rms_norm_inputs(8, 256)
+    xc, wc = x.cuda(), w.cuda()
+    host = np.zeros(8 * 256 + 8, dtype=np.float32)
+    addr = (host.ctypes.data + 15) & ~15            # the entry point also wants 16-byte alignment
+    h = _native.create_handle(_ids.K_RMS_NORM, (8, 256), (1e-6,))
+    ptrs = (ctypes.c_void_p * 3)(xc.data_ptr(), wc.data_ptr(), addr)
+    err = ctypes.create_string_buffer(_native.ERR_LEN)
+    rc = lib.pb200_launch_raw(h, torch.cuda.current_stream().cuda_stream, ptrs, 3, err)
+    assert rc == _ids.ERR_WRONG_DEVICE and b"not device-accessible" in err.value
+    # the same handle with proper buffers still works
+    y = torch.empty_like(xc)
+    ptrs = (ctypes.c_void_p * 3)(xc.data_ptr(), wc.data_ptr(), y.data_ptr())
+    assert lib.pb200_launch_raw(h, torch.cuda.current_stream().cuda_stream, ptrs, 3, err) == 0, err.value
+    torch.cuda.synchronize()
+    check_f32(y.cpu(), formulas.rms_norm_ref(x, w))
+    lib.pb200_destroy(h)
+
+
 def test_torch_compile_through_custom_op():
     x, w = inputs.rms_norm_inputs(16, 512)
     k = build_rms_norm(16, 512)
@@ -69,6 +93,47 @@ def test_torch_compile_through_custom_op():
     ref = formulas.rms_norm_ref(x * 2.0, w) + 1.0
     check_f32(out.cpu(), ref)
     assert k.handle in torch_support._REGISTERED_OPS
+
+
+def test_torch_compile_matrix_kernels():
+    """GEMM, grouped GEMM and attention inside ``torch.compile(fullgraph=True)`` graphs, next to
+    ordinary torch ops (the reference compiles a grouped GEMM and an attention call the same way,
+    tests/test_torch_dispatch.py:161-204)."""
+    from pyptx_b200.examples.blackwell.flash_attention import build_flash_attention
+    from pyptx_b200.examples.blackwell.grouped_gemm import build_grouped_gemm
+    from pyptx_b200.types import f32
+
+    a, bt = inputs.gemm_inputs(256, 256, 128)
+    kg = build_gemm(256, 256, 128)
+
+    @torch.compile(fullgraph=True)
+    def f_gemm(x, y):
+        return torch.relu(kg(x, y)) * 0.5
+
+    ref = torch.relu(formulas.gemm_ref(a, bt)) * 0.5
+    assert formulas.rel_fro(f_gemm(a.cuda(), bt.cuda()).cpu(), ref) < 1e-4
+
+    G, M, N, K = 2, 128, 256, 128
+    ga, gb = inputs.grouped_gemm_inputs(G, M, N, K)
+    kgg = build_grouped_gemm(G, M, N, K)
+
+    @torch.compile(fullgraph=True)
+    def f_grouped(x, y):
+        return kgg(x, y) + 1.0
+
+    assert formulas.rel_fro(f_grouped(ga.cuda(), gb.cuda()).cpu(), formulas.grouped_gemm_ref(ga, gb, G) + 1.0) < 1e-4
+
+    q, k, v = (t.view(1, 2, 256, 64) for t in inputs.attention_inputs(2, 256, 256, 64))
+    ka = build_flash_attention(1, 2, 256, 256, 64, causal=True, out_dtype=f32)
+
+    @torch.compile(fullgraph=True)
+    def f_attn(qq, kk, vv):
+        return ka(qq, kk, vv) * 2.0
+
+    ref = formulas.attention_ref(q, k, v, causal=True) * 2.0
+    assert formulas.rel_fro(f_attn(q.cuda(), k.cuda(), v.cuda()).cpu(), ref) < 1e-2
+    for kern in (kg, kgg, ka):
+        assert kern.handle in torch_support._REGISTERED_OPS
 
 
 def test_custom_op_fake_shapes():
@@ -203,10 +268,12 @@ def test_dispatch_overhead_is_reported(capsys):
     assert host_us < 200
 
 
-def test_concurrent_launches_from_threads_on_their_own_streams():
-    """Host threads launch different kernels at once, each on its own stream: the launch path
-    (handle lookup under a shared lock, per-launch tensor maps, per-call error buffers, one-time
-    function attributes) must give every thread its own correct results."""
+@pytest.mark.parametrize("path", ["pybind11", "ctypes"])
+def test_concurrent_launches_from_threads_on_their_own_streams(path):
+    """Host threads launch kernels at once (two threads per kernel), each on its own stream: the
+    launch path (handle lookup under a shared lock, per-launch tensor maps, per-thread pointer
+    arrays and error buffers, one-time function attributes) must give every thread its own correct
+    results, through the pybind11 extension and through plain ctypes."""
     import threading
 
     from oracle import formulas, inputs
@@ -227,6 +294,12 @@ def test_concurrent_launches_from_threads_on_their_own_streams():
         "attention": (build_flash_attention(1, 2, 256, 256, 64, out_dtype=f32), (q.cuda(), k.cuda(), v.cuda()),
                       formulas.attention_ref(q, k, v), 1e-2),
     }
+    for kernel, args, _, _ in jobs.values():
+        kernel(*args)                      # builds the per-kernel launcher
+        if path == "ctypes":
+            kernel._launcher.ext = None    # the same C-ABI call, made through ctypes
+        else:
+            assert kernel._launcher.ext is not None, "the pybind11 extension was not built"
     torch.cuda.synchronize()
     errors: list[str] = []
 

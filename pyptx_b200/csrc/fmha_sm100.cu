@@ -40,14 +40,16 @@ constexpr int kKvTile = 128;      // keys per K/V tile
 constexpr int kFmhaThreads = 384; // 3 warpgroups: {TMA, MMA, 2 idle}, softmax tile 0, softmax tile 1
 constexpr uint32_t kDebugPSmem = 1u << 17;   // create flag: keep P in shared memory (head_dim 64)
 constexpr float kRescaleThreshold = 8.0f;    // log2 units
+constexpr int kRegsIssue = 88;               // registers per thread of the TMA / MMA warpgroup after setmaxnreg
+constexpr int kRegsSoftmax = 208;            // ... of the two softmax warpgroups
 #ifndef PB200_FMHA_SPLIT_P
 #define PB200_FMHA_SPLIT_P 1
 #endif
 #ifndef PB200_FMA_EXP_PAIRS
-#define PB200_FMA_EXP_PAIRS 3
+#define PB200_FMA_EXP_PAIRS 1
 #endif
 #ifndef PB200_FMA_EXP_PAIRS_D64
-#define PB200_FMA_EXP_PAIRS_D64 3
+#define PB200_FMA_EXP_PAIRS_D64 1
 #endif
 // Of every 8 score pairs, how many take the FMA-pipe exp2 (by tile width: the narrower tile has
 // half the MMA time per exponential, so the MUFU unit is further from balance there).
@@ -116,11 +118,13 @@ __device__ __forceinline__ void add2v(float& d0, float& d1, float a0, float a1, 
 // 2^x for two arguments on the FMA pipe instead of the MUFU unit, which is the scarcer resource
 // of this kernel (16 exponentials per clock per SM against 8192 MMA flops).  Round-to-nearest
 // split x = n + f with the 1.5*2^23 trick, cubic minimax for 2^f on [-0.5, 0.5] (relative error
-// 1.0e-4, far below the bf16 rounding of P), n added into the exponent field.  Needs x >= -126.
+// 1.0e-4, far below the bf16 rounding of P), n added into the exponent field.  The argument is
+// clamped to [-126, 127]: below, the result underflows to ~0 as it should; above, it saturates near
+// 2^127 instead of wrapping into the sign bit, so that a caller's overflow check still fires.
 __device__ __forceinline__ void exp2_fma_pair(float& r0, float& r1, float x0, float x1) {
     constexpr float kMagic = 12582912.0f;
-    x0 = fmaxf(x0, -126.0f);
-    x1 = fmaxf(x1, -126.0f);
+    x0 = fminf(fmaxf(x0, -126.0f), 127.0f);
+    x1 = fminf(fmaxf(x1, -126.0f), 127.0f);
     float t0, t1, n0, n1, f0, f1, p0, p1;
     add2v(t0, t1, x0, x1, kMagic, kMagic);
     add2v(n0, n1, t0, t1, -kMagic, -kMagic);
@@ -256,10 +260,12 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
     // Registers move from the TMA / MMA warpgroup (two single-thread roles) to the softmax
     // warpgroups; each setmaxnreg sits at the head of its own branch so that the compiler sees which
-    // budget governs which code.
+    // budget governs which code.  A CTA can only hand around the registers it was launched with
+    // (168 per thread here): an increase beyond what the decrease released would block for ever.
+    static_assert(kRegsIssue * 128 + kRegsSoftmax * 256 <= 168 * kFmhaThreads, "setmaxnreg budget exceeds the launch allocation");
     if (warp < 4) {
 #if PB200_FMHA_SETMAXNREG
-    reg_dealloc<96>();
+    reg_dealloc<kRegsIssue>();
 #endif
     if (warp == 0) {
         // ------------------------------- TMA producer -------------------------------
@@ -383,7 +389,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     }
     } else {
 #if PB200_FMHA_SETMAXNREG
-        reg_alloc<208>();
+        reg_alloc<kRegsSoftmax>();
 #endif
         // ------------------------------- softmax + epilogue --------------------------
         const int t = (warp - 4) >> 2;                   // query tile of this warp group

@@ -34,10 +34,13 @@ def _run(q, k, v, do, *, causal, out_dtype=f32, sm_scale=None):
 
 
 def _check(got, ref, tol=TOL):
+    # A gradient that is exactly zero in the reference (one visible key: P = 1, dS = 0) is measured
+    # against the largest of the three reference norms instead of its own.
+    floor = 1e-2 * max(float(r.norm()) for r in ref)
     for name, g, r in zip(("dq", "dk", "dv"), got, ref):
         assert g.shape == r.shape, (name, g.shape, r.shape)
         assert torch.isfinite(g.float()).all(), name
-        err = formulas.rel_fro(g.float(), r)
+        err = float((g.float() - r).norm()) / max(float(r.norm()), floor, 1e-30)
         assert err < tol, f"{name}: rel_fro {err:.3e}"
 
 

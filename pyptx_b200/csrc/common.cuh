@@ -84,4 +84,23 @@ int make_tensor_map(CUtensorMap* out, CUtensorMapDataType dt, int rank, const vo
 // Address of the device status words on the current device (host-callable).
 int* device_status_ptr();
 
+// Launch with the programmatic-stream-serialization attribute: the kernel's CTAs may be scheduled
+// while the previous kernel of the stream drains; the kernel itself waits (ptx::pdl_wait) before it
+// touches global memory.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_with_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem_bytes, cudaStream_t stream,
+                            Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 }  // namespace pb200

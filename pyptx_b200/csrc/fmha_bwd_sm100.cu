@@ -170,9 +170,11 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
         tmem_alloc<1>(s_tmem_slot, 512);
         tmem_relinquish<1>();
     }
+    pdl_launch_dependents();
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
+    pdl_wait();      // set-up above overlaps the previous kernel's tail; global memory is touched only below
     const uint32_t tmem_base = *tmem_slot_gen;
     const uint32_t tmem_x1 = tmem_base, tmem_x2 = tmem_base + 128u;
     const uint32_t tmem_acc_a = tmem_base + 256u, tmem_acc_b = tmem_base + 384u;
@@ -406,8 +408,8 @@ int launch_pass(const CUtensorMap& s1, const CUtensorMap& s2, const CUtensorMap&
         attr_set.fetch_or(1ull << (dev & 63), std::memory_order_relaxed);
     }
     dim3 grid((unsigned)tiles, (unsigned)prm.bh, 1);
-    kernel<<<grid, kBwdThreads, L::kTotal, stream>>>(s1, s2, m1, m2, lse2, delta, (OutT*)out_a, (OutT*)out_b, prm, device_status_ptr());
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_with_pdl(kernel, grid, dim3(kBwdThreads), L::kTotal, stream, s1, s2, m1, m2, lse2, delta,
+                                    (OutT*)out_a, (OutT*)out_b, prm, device_status_ptr());
     if (e != cudaSuccess) { set_err(err, "attention backward launch failed (HD=%d mode=%d): %s", HD, MODE, cudaGetErrorString(e)); return PB200_ERR_LAUNCH; }
     return PB200_OK;
 }

@@ -246,9 +246,11 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         tmem_alloc<1>(s_tmem_slot, 512);
         tmem_relinquish<1>();
     }
+    pdl_launch_dependents();
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
+    pdl_wait();      // set-up above overlaps the previous kernel's tail; global memory is touched only below
     const uint32_t tmem_base = *tmem_slot_gen;
     const uint32_t tmem_s[2] = {tmem_base, tmem_base + 128u};
     const uint32_t tmem_o[2] = {tmem_base + 256u, tmem_base + 384u};
@@ -680,8 +682,8 @@ int launch_fmha(const Record& r, cudaStream_t stream, void** p, char* err) {
     prm.hd = (int)hd;
     dim3 grid(r.geom.grid[0], r.geom.grid[1], 1);
     float* lse = (r.flags & PB200_F_RETURN_LSE) ? (float*)p[4] : nullptr;
-    kernel<<<grid, kFmhaThreads, L::kTotal, stream>>>(tq, tk, tv, (OutT*)p[3], lse, prm, device_status_ptr());
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_with_pdl(kernel, grid, dim3(kFmhaThreads), L::kTotal, stream, tq, tk, tv, (OutT*)p[3], lse, prm,
+                                    device_status_ptr());
     if (e != cudaSuccess) { set_err(err, "attention launch failed (HD=%d smem=%d): %s", HD, L::kTotal, cudaGetErrorString(e)); return PB200_ERR_LAUNCH; }
     return PB200_OK;
 }

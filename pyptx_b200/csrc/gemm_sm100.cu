@@ -231,10 +231,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         tmem_alloc<CTA_GROUP>(s_tmem_slot, kTmemCols);
         tmem_relinquish<CTA_GROUP>();
     }
+    pdl_launch_dependents();
     tc_fence_before_sync();
     if (CTA_GROUP == 2) cluster_sync_all(); else __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot_gen;
+    // Set-up above overlaps the previous kernel's tail; global memory is touched only below.
+    pdl_wait();
 
     if (warp == 0) {
         // ------------------------- TMA producer -------------------------
@@ -486,9 +489,23 @@ int pick_bn(int64_t n) {
 }
 
 // dims of the push kernel: {n_dest, cta_group, M, N, K}
+//
+// The 2-SM entry point runs a problem whose 128 x 256 tiles fit the SMs in ONE wave, but fill
+// more than half of them, on the 1-SM shape: with one tile per CTA a pair buys no operand reuse
+// worth its cluster set-up and tear-down (2048^3: 16.4 us against 18.3 us).  Every output element
+// is the same fp32 sum over K in the same order either way, so the result bits do not change.
+// tile="narrow" / "wide" (and the direct-store debug path) keep the pair shape.
 int cta_group_of(const Record& r) {
     if (r.kernel_id == PB200_K_GEMM_PUSH) return (int)r.dims[1];
-    return r.kernel_id == PB200_K_GEMM_2SM ? 2 : 1;
+    if (r.kernel_id != PB200_K_GEMM_2SM) return 1;
+    if (r.flags & (kForceNarrowTile | kForceWideTile | kDebugDirectStore)) return 2;
+    if (r.n_dims >= 3) {
+        const int64_t M = r.dims[r.n_dims - 3], N = r.dims[r.n_dims - 2];
+        const int64_t tiles = (M / BM) * (N / 256);
+        const int64_t sms = sm_count();
+        if (M % BM == 0 && N % 256 == 0 && tiles <= sms && 2 * tiles > sms) return 1;
+    }
+    return 2;
 }
 
 constexpr uint32_t kForceBn256 = 1u << 20;        // create flag: the grouped kernel keeps 256-column tiles
@@ -557,13 +574,16 @@ int launch_variant(const Record& r, cudaStream_t stream, void** p, const GemmSha
     cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = Plan::kTotal;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = CTA_GROUP;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    // programmatic dependent launch: see pdl_wait() in the kernel
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     OutT* d_ptr = (OutT*)out_ptr;
     typename PushParam<EPI>::type push{};
     if constexpr (EPI == 2) {
@@ -669,7 +689,8 @@ int plan_gemm(Record& r, char* err) {
         return PB200_ERR_BAD_SHAPE;
     }
     if (G < 1 || M < 1 || N < 1 || K < 1) { set_err(err, "G, M, N, K must be positive"); return PB200_ERR_BAD_SHAPE; }
-    if (M % (BM * cta_group) != 0) { set_err(err, "M=%lld must be divisible by %d", (long long)M, BM * cta_group); return PB200_ERR_BAD_SHAPE; }
+    const int m_unit = r.kernel_id == PB200_K_GEMM_2SM ? 2 * BM : BM * cta_group;     // the 2-SM entry keeps its rule on every shape
+    if (M % m_unit != 0) { set_err(err, "M=%lld must be divisible by %d", (long long)M, m_unit); return PB200_ERR_BAD_SHAPE; }
     if (K % BK != 0) { set_err(err, "K=%lld must be divisible by %d", (long long)K, BK); return PB200_ERR_BAD_SHAPE; }
     if (swiglu && N % 128 != 0) { set_err(err, "F=%lld must be divisible by 128", (long long)N); return PB200_ERR_BAD_SHAPE; }
     const int bn = swiglu ? 256 : choose_bn(r);

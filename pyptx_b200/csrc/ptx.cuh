@@ -104,6 +104,22 @@ __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
 }
 
 // ---------------------------------------------------------------------------
+// Programmatic dependent launch.  A kernel launched with the "programmatic stream serialization"
+// attribute may have its CTAs scheduled while the previous kernel of the stream is still draining;
+// they run their set-up (barriers, TMEM allocation) and then wait in pdl_wait() until that kernel
+// has completed and its writes are visible.  Every access to global memory comes after the wait,
+// so the ordering a stream gives is unchanged; what overlaps is launch latency and set-up.
+// pdl_launch_dependents() lets the next kernel do the same with this one.  Both are no-ops for a
+// launch without the attribute.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;");
+}
+__device__ __forceinline__ void pdl_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// ---------------------------------------------------------------------------
 // mbarrier
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {

@@ -23,6 +23,7 @@
 // near 1e-6), and a two-pass variance (sum of squared deviations from the mean,
 // taken over registers) instead of E[x^2]-mean^2.
 #include "common.cuh"
+#include "ptx.cuh"
 
 #include <cuda_bf16.h>
 
@@ -93,16 +94,10 @@ __device__ __forceinline__ float block_reduce(float v, float* slot) {
 // ---------------------------------------------------------------------------
 // RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w
 // ---------------------------------------------------------------------------
-// Programmatic dependent launch: when a kernel is launched with the "programmatic stream
-// serialization" attribute, its CTAs may be scheduled while the previous kernel of the stream is
-// still draining; they then wait here until that kernel has completed and its writes are
-// visible.  Every access to global memory comes after the wait, so the ordering a stream gives
-// is unchanged; what overlaps is the launch latency (about 2 us between two 20 us kernels).
-// launch_dependents lets the next kernel do the same with this one.  Both are no-ops for a
-// launch without the attribute.
+// Programmatic dependent launch (see ptx.cuh): about 2 us of launch latency between two 20 us kernels.
 __device__ __forceinline__ void pdl_prologue() {
-    asm volatile("griddepcontrol.launch_dependents;");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    ptx::pdl_launch_dependents();
+    ptx::pdl_wait();
 }
 
 template <int THREADS, int VPT, typename OutT>

@@ -375,3 +375,17 @@ def test_bias_epilogue_rejects_wrong_inputs():
         k(a.cuda(), bt.cuda(), torch.zeros(256, dtype=torch.bfloat16, device="cuda"))
     with pytest.raises(AssertionError, match="activation must be one of"):
         build_gemm(256, 256, 64, activation="tanh")
+
+
+def test_2sm_entry_on_a_single_wave_problem_keeps_its_bits():
+    """2048^3 has 128 tiles of 128 x 256: the 2-SM entry point runs it on the 1-SM shape (one CTA
+    per tile, no cluster); tile="narrow" keeps the CTA pairs.  Same sums in the same order."""
+    S = 2048
+    a, bt = inputs.gemm_inputs(S, S, S)
+    auto = build_gemm_2sm(S, S, S)
+    pairs = build_gemm_2sm(S, S, S, tile="narrow")
+    assert auto.cluster == (1, 1, 1) and pairs.cluster == (2, 1, 1)
+    d0, d1, d2 = auto(a.cuda(), bt.cuda()), pairs(a.cuda(), bt.cuda()), build_gemm(S, S, S)(a.cuda(), bt.cuda())
+    assert torch.equal(d0, d1) and torch.equal(d0, d2)
+    # small problems (and anything with more than one wave) stay on CTA pairs
+    assert build_gemm_2sm(512, 512, 256).cluster == (2, 1, 1) and build_gemm_2sm(4096, 4096, 256).cluster == (2, 1, 1)

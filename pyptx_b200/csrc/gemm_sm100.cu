@@ -205,11 +205,59 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // Variable-size grouped GEMM: A and D are one stack of row blocks, expert e owning rows
     // [expert_offsets[e], expert_offsets[e+1]) (multiples of BM, so no tile straddles two experts);
     // only the row blocks below expert_offsets[n_experts] exist, and only the B tile depends on e.
-    const int n_tiles = shape.n_experts > 0
-        ? (min(__ldg(expert_offsets + shape.n_experts), shape.tiles_m * BM) / BM) * shape.tiles_n
-        : shape.groups * shape.tiles_m * shape.tiles_n;
+    // (reads expert_offsets: only after pdl_wait)
+    auto count_tiles = [&]() {
+        return shape.n_experts > 0
+            ? (min(__ldg(expert_offsets + shape.n_experts), shape.tiles_m * BM) / BM) * shape.tiles_n
+            : shape.groups * shape.tiles_m * shape.tiles_n;
+    };
 
     WaitCtx ctx{status, abort_gen, kernel_id};
+
+    // TMA producer (thread 0), written as a resumable routine: with one CTA per tile walker
+    // (CTA_GROUP == 1) the first ring-full of loads is issued before the CTA-wide set-up barrier,
+    // so that the first tiles are in flight while TMEM is being allocated; the rest follows below.
+    int p_tile = unit, p_kt = 0, p_stage = 0, p_row_a = 0, p_row_b = 0, p_tiles = 0;
+    uint32_t p_phase = 0;
+    bool p_ok = true;
+    const uint32_t full_leader = CTA_GROUP == 2 ? map_to_cta(bar_full, 0) : bar_full;
+    auto produce = [&](int max_loads) {
+        for (int n = 0; n < max_loads && p_ok && p_tile < p_tiles; ++n) {
+            if (p_kt == 0) {
+                int g, tm, tn;
+                tile_coords(shape, p_tile, g, tm, tn);
+                p_row_a = g * shape.rows_per_group_a + (tm * CTA_GROUP * kSub + (int)cta_rank) * BM;
+                if (shape.n_experts > 0) {
+                    // which expert owns this row block (a handful of cached 4-byte loads per tile)
+                    while (g + 1 < shape.n_experts && __ldg(expert_offsets + g + 1) <= p_row_a) ++g;
+                }
+                p_row_b = shape.n_experts > 0 ? g * shape.rows_per_group_b + tn * BN : EPI == 1 ? g * shape.rows_per_group_b + tn * (BN / 2)
+                                              : g * shape.rows_per_group_b + tn * BN + (int)cta_rank * Plan::kBRows;
+            }
+            if (!(p_ok = mbar_wait(bar_empty + 8 * p_stage, p_phase ^ 1u, ctx, 1))) break;
+            const uint32_t dst_a = s_a + p_stage * Plan::kABytes;
+            const uint32_t dst_b = s_b + p_stage * Plan::kBBytes;
+            if (CTA_GROUP == 1) {
+                mbar_arrive_expect_tx(bar_full + 8 * p_stage, Plan::kTxBytes);
+                tma_load_2d(dst_a, &tmap_a, bar_full + 8 * p_stage, p_kt * BK, p_row_a);
+                if (WIDE) tma_load_2d(dst_a + BM * BK * 2, &tmap_a, bar_full + 8 * p_stage, p_kt * BK, p_row_a + BM);
+                if (EPI == 1) {
+                    // 128 gate rows, then the 128 up rows of the same feature block
+                    tma_load_2d(dst_b, &tmap_b, bar_full + 8 * p_stage, p_kt * BK, p_row_b);
+                    tma_load_2d(dst_b + (BN / 2) * BK * 2, &tmap_b, bar_full + 8 * p_stage, p_kt * BK, p_row_b + shape.up_row_off);
+                } else {
+                    tma_load_2d(dst_b, &tmap_b, bar_full + 8 * p_stage, p_kt * BK, p_row_b);
+                }
+            } else {
+                if (is_leader) mbar_arrive_expect_tx(bar_full + 8 * p_stage, Plan::kTxBytes);
+                tma_load_2d_pair(dst_a, &tmap_a, full_leader + 8 * p_stage, p_kt * BK, p_row_a);
+                if (WIDE) tma_load_2d_pair(dst_a + BM * BK * 2, &tmap_a, full_leader + 8 * p_stage, p_kt * BK, p_row_a + CTA_GROUP * BM);
+                tma_load_2d_pair(dst_b, &tmap_b, full_leader + 8 * p_stage, p_kt * BK, p_row_b);
+            }
+            if (++p_stage == kStages) { p_stage = 0; p_phase ^= 1u; }
+            if (++p_kt == shape.k_tiles) { p_kt = 0; p_tile += n_units; }
+        }
+    };
 
     if (threadIdx.x == 0) {
         *abort_gen = 0;
@@ -232,53 +280,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         tmem_relinquish<CTA_GROUP>();
     }
     pdl_launch_dependents();
+    if (CTA_GROUP == 1 && threadIdx.x == 0) {
+        // The full barriers were initialised by this very thread, and only the MMA thread waits on
+        // them (after the barrier below), so the first loads need not wait for the other warps.
+        pdl_wait();
+        p_tiles = count_tiles();
+        produce(kStages);
+    }
     tc_fence_before_sync();
     if (CTA_GROUP == 2) cluster_sync_all(); else __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot_gen;
     // Set-up above overlaps the previous kernel's tail; global memory is touched only below.
     pdl_wait();
+    const int n_tiles = count_tiles();
 
     if (warp == 0) {
         // ------------------------- TMA producer -------------------------
         if (lane == 0) {
-            int stage = 0; uint32_t phase = 0;
-            const uint32_t full_leader = CTA_GROUP == 2 ? map_to_cta(bar_full, 0) : bar_full;
-            bool ok = true;
-            for (int t = unit; t < n_tiles && ok; t += n_units) {
-                int g, tm, tn;
-                tile_coords(shape, t, g, tm, tn);
-                const int row_a = g * shape.rows_per_group_a + (tm * CTA_GROUP * kSub + (int)cta_rank) * BM;
-                if (shape.n_experts > 0) {
-                    // which expert owns this row block (a handful of cached 4-byte loads per tile)
-                    while (g + 1 < shape.n_experts && __ldg(expert_offsets + g + 1) <= row_a) ++g;
-                }
-                const int row_b = shape.n_experts > 0 ? g * shape.rows_per_group_b + tn * BN : EPI == 1 ? g * shape.rows_per_group_b + tn * (BN / 2)
-                                           : g * shape.rows_per_group_b + tn * BN + (int)cta_rank * Plan::kBRows;
-                for (int kt = 0; kt < shape.k_tiles; ++kt) {
-                    if (!(ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, ctx, 1))) break;
-                    const uint32_t dst_a = s_a + stage * Plan::kABytes;
-                    const uint32_t dst_b = s_b + stage * Plan::kBBytes;
-                    if (CTA_GROUP == 1) {
-                        mbar_arrive_expect_tx(bar_full + 8 * stage, Plan::kTxBytes);
-                        tma_load_2d(dst_a, &tmap_a, bar_full + 8 * stage, kt * BK, row_a);
-                        if (WIDE) tma_load_2d(dst_a + BM * BK * 2, &tmap_a, bar_full + 8 * stage, kt * BK, row_a + BM);
-                        if (EPI == 1) {
-                            // 128 gate rows, then the 128 up rows of the same feature block
-                            tma_load_2d(dst_b, &tmap_b, bar_full + 8 * stage, kt * BK, row_b);
-                            tma_load_2d(dst_b + (BN / 2) * BK * 2, &tmap_b, bar_full + 8 * stage, kt * BK, row_b + shape.up_row_off);
-                        } else {
-                            tma_load_2d(dst_b, &tmap_b, bar_full + 8 * stage, kt * BK, row_b);
-                        }
-                    } else {
-                        if (is_leader) mbar_arrive_expect_tx(bar_full + 8 * stage, Plan::kTxBytes);
-                        tma_load_2d_pair(dst_a, &tmap_a, full_leader + 8 * stage, kt * BK, row_a);
-                        if (WIDE) tma_load_2d_pair(dst_a + BM * BK * 2, &tmap_a, full_leader + 8 * stage, kt * BK, row_a + CTA_GROUP * BM);
-                        tma_load_2d_pair(dst_b, &tmap_b, full_leader + 8 * stage, kt * BK, row_b);
-                    }
-                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
-                }
-            }
+            p_tiles = n_tiles;
+            produce(0x7fffffff);
         }
     } else if (warp == 1) {
         // ------------------------- MMA issuer ---------------------------

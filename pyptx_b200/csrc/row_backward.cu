@@ -20,6 +20,7 @@
 // against 3*B*N*4 for the main pass.  The scratch buffer is supplied by the caller as one
 // extra trailing pointer (its size is part of the handle's geometry).
 #include "common.cuh"
+#include "ptx.cuh"
 
 #include <atomic>
 
@@ -57,6 +58,22 @@ __device__ __forceinline__ void block_sum2(float& a, float& b, float2* slot) {
     for (int i = 1; i < NW; ++i) { r.x += slot[i].x; r.y += slot[i].y; }
     a = r.x;
     b = r.y;
+}
+
+// The same for a CTA of many warps: every warp reads the per-warp partials once (lane i takes warp
+// i's) and folds them with shuffles, instead of every thread reading all of them.  All warps run
+// the same tree, so every thread ends with the same bits.
+template <int THREADS>
+__device__ __forceinline__ void block_sum2_tree(float& a, float& b, float2* slot) {
+    constexpr int NW = THREADS / kWarp;
+    const int lane = threadIdx.x & (kWarp - 1);
+    a = warp_sum(a);
+    b = warp_sum(b);
+    if (lane == 0) slot[threadIdx.x / kWarp] = make_float2(a, b);
+    __syncthreads();
+    const float2 v = lane < NW ? slot[lane] : make_float2(0.f, 0.f);
+    a = warp_sum(v.x);
+    b = warp_sum(v.y);
 }
 
 // MODE 0 = RMSNorm, 1 = LayerNorm.  partial_w / partial_b: [gridDim.x][4*n4] f32.
@@ -161,6 +178,117 @@ norm_bwd_kernel(const float4* __restrict__ x, const float4* __restrict__ w, cons
     }
 }
 
+// The same pass for rows of 4097 .. 8192 columns (the benchmark's 8192 among them), shaped for
+// streaming: ONE 1024-thread CTA per SM, VPT <= 2 float4 columns per thread, so that within 64
+// registers a thread holds its slice of w for the whole kernel (instead of three cached re-reads
+// per row) and, next to the row it works on, the NEXT row's x and dy, whose loads are issued before
+// the reductions of the current row.  HBM then always has a row in flight per SM while the
+// barrier-separated phases of the current one run.  (Measured alternatives that were not faster:
+// column sums in registers with w in shared memory, and LayerNorm's four row sums in one shifted
+// pass with a single barrier.)
+template <int VPT, int MODE>
+__global__ void __launch_bounds__(1024, 1)
+norm_bwd_stream_kernel(const float4* __restrict__ x, const float4* __restrict__ w, const float4* __restrict__ dy,
+                       float4* __restrict__ dx, float4* __restrict__ partial_w, float4* __restrict__ partial_b,
+                       int rows, int n4, float inv_n, float eps) {
+    constexpr int THREADS = 1024;
+    __shared__ float2 red[3][kWarp];
+    extern __shared__ float4 acc_smem[];              // [MODE + 1][THREADS * VPT]
+    float4* acc_w = acc_smem;
+    float4* acc_b = acc_smem + THREADS * VPT;
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    ptx::pdl_launch_dependents();
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int idx = threadIdx.x + i * THREADS;
+        acc_w[idx] = zero4;
+        if (MODE == 1) acc_b[idx] = zero4;
+    }
+    ptx::pdl_wait();
+    float4 wv[VPT], xv[VPT], gv[VPT];
+    int row = blockIdx.x;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int idx = threadIdx.x + i * THREADS;
+        const bool in = idx < n4;
+        wv[i] = in ? __ldg(w + idx) : zero4;
+        xv[i] = in && row < rows ? ld_stream4(x + (size_t)row * n4 + idx) : zero4;
+        gv[i] = in && row < rows ? ld_stream4(dy + (size_t)row * n4 + idx) : zero4;
+    }
+    int flip = 0;
+    for (; row < rows; row += gridDim.x) {
+        // next row first: its loads fly while this row is reduced, scaled and stored
+        const int nrow = row + (int)gridDim.x;
+        float4 xn[VPT], gn[VPT];
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int idx = threadIdx.x + i * THREADS;
+            const bool in = idx < n4 && nrow < rows;
+            xn[i] = in ? ld_stream4(x + (size_t)nrow * n4 + idx) : zero4;
+            gn[i] = in ? ld_stream4(dy + (size_t)nrow * n4 + idx) : zero4;
+        }
+        float mu = 0.f, c2 = 0.f;
+        if (MODE == 1) {        // RMSNorm needs neither the mean of x nor the mean of w*dy
+            float s_x = 0.f, s_wdy = 0.f;
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) {
+                s_x += (xv[i].x + xv[i].y) + (xv[i].z + xv[i].w);
+                s_wdy += wv[i].x * gv[i].x + wv[i].y * gv[i].y + wv[i].z * gv[i].z + wv[i].w * gv[i].w;
+            }
+            block_sum2_tree<THREADS>(s_x, s_wdy, red[flip]);
+            flip = flip == 2 ? 0 : flip + 1;
+            mu = s_x * inv_n;
+            c2 = s_wdy * inv_n;                               // mean(w*dy)
+        }
+        float s_xx = 0.f, s_xwdy = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            if (threadIdx.x + i * THREADS < n4) {             // padding columns must not see -mu
+                const float cx = xv[i].x - mu, cy = xv[i].y - mu, cz = xv[i].z - mu, cw = xv[i].w - mu;
+                s_xx += cx * cx + cy * cy + cz * cz + cw * cw;
+                s_xwdy += cx * wv[i].x * gv[i].x + cy * wv[i].y * gv[i].y + cz * wv[i].z * gv[i].z + cw * wv[i].w * gv[i].w;
+            }
+        }
+        block_sum2_tree<THREADS>(s_xx, s_xwdy, red[flip]);
+        flip = flip == 2 ? 0 : flip + 1;
+        const float r = rsqrtf(s_xx * inv_n + eps);
+        const float c1 = s_xwdy * r * inv_n;                    // mean(xhat * w*dy)
+        float4* dr = dx + (size_t)row * n4;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int idx = threadIdx.x + i * THREADS;
+            if (idx < n4) {
+                const float hx = (xv[i].x - mu) * r, hy = (xv[i].y - mu) * r, hz = (xv[i].z - mu) * r, hw = (xv[i].w - mu) * r;
+                float4 o;
+                o.x = r * (wv[i].x * gv[i].x - c2 - hx * c1);
+                o.y = r * (wv[i].y * gv[i].y - c2 - hy * c1);
+                o.z = r * (wv[i].z * gv[i].z - c2 - hz * c1);
+                o.w = r * (wv[i].w * gv[i].w - c2 - hw * c1);
+                st_stream4(dr + idx, o);
+                float4 aw = acc_w[idx];
+                aw.x += gv[i].x * hx; aw.y += gv[i].y * hy; aw.z += gv[i].z * hz; aw.w += gv[i].w * hw;
+                acc_w[idx] = aw;
+                if (MODE == 1) {
+                    float4 ab = acc_b[idx];
+                    ab.x += gv[i].x; ab.y += gv[i].y; ab.z += gv[i].z; ab.w += gv[i].w;
+                    acc_b[idx] = ab;
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) { xv[i] = xn[i]; gv[i] = gn[i]; }
+    }
+    // this CTA's partial column sums -> scratch
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int idx = threadIdx.x + i * THREADS;
+        if (idx < n4) {
+            partial_w[(size_t)blockIdx.x * n4 + idx] = acc_w[idx];
+            if (MODE == 1) partial_b[(size_t)blockIdx.x * n4 + idx] = acc_b[idx];
+        }
+    }
+}
+
 // out[c] = sum_p partial[p][c]; blockIdx.y selects the plane (dw, then db).  A CTA folds 32
 // float4 columns with 32 part-lanes: lane j adds parts j, j+32, ... in order, then one warp adds
 // the 32 lane sums in order, so the result depends on `parts` alone, not on timing.  (A column per
@@ -169,6 +297,8 @@ __global__ void __launch_bounds__(1024)
 fold_partials_kernel(const float4* __restrict__ partial, float4* __restrict__ out_w, float4* __restrict__ out_b,
                      int parts, int n4) {
     __shared__ float4 lane_sum[32][32];
+    ptx::pdl_launch_dependents();
+    ptx::pdl_wait();                 // the partial rows come from the kernel launched just before
     const int c = threadIdx.x & 31, j = threadIdx.x >> 5;
     const int col = blockIdx.x * 32 + c;
     const float4* src = partial + (size_t)blockIdx.y * parts * n4;
@@ -227,8 +357,9 @@ swiglu_bwd_kernel(const float4* __restrict__ gate, const float4* __restrict__ up
 
 struct BwdConfig { int threads; int vpt; };
 // Smallest register-resident configuration that covers a row; rows beyond 16384 columns are not supported.
+// 1024-thread configurations run norm_bwd_stream_kernel (one CTA per SM, next row prefetched).
 bool pick_bwd_config(int64_t n4, BwdConfig& c) {
-    const BwdConfig table[] = {{32, 1}, {32, 2}, {64, 2}, {128, 2}, {128, 4}, {256, 4}, {512, 4}, {512, 8}};
+    const BwdConfig table[] = {{32, 1}, {32, 2}, {64, 2}, {128, 2}, {128, 4}, {256, 4}, {1024, 2}, {512, 8}};
     for (const BwdConfig& t : table)
         if ((int64_t)t.threads * t.vpt >= n4) { c = t; return true; }
     return false;
@@ -240,7 +371,7 @@ size_t bwd_acc_bytes(const BwdConfig& c, int mode) { return (size_t)(mode + 1) *
 int bwd_parts(int64_t rows, int64_t n4, int mode) {
     BwdConfig c{256, 4};
     pick_bwd_config(n4, c);
-    const bool two = 2 * c.threads <= 2048 && 2 * bwd_acc_bytes(c, mode) <= 200 * 1024;
+    const bool two = c.threads < 1024 && 2 * c.threads <= 2048 && 2 * bwd_acc_bytes(c, mode) <= 200 * 1024;
     const int64_t p = (two ? 2 : 1) * (int64_t)sm_count();
     return (int)(rows < p ? rows : p);
 }
@@ -264,6 +395,24 @@ void launch_norm(int mode, int parts, cudaStream_t s, const float4* x, const flo
     else norm_bwd_kernel<THREADS, VPT, 1><<<parts, THREADS, smem, s>>>(x, w, dy, dx, pw, pb, rows, n4, inv_n, eps);
 }
 
+template <int VPT>
+void launch_norm_stream(int mode, int parts, cudaStream_t s, const float4* x, const float4* w, const float4* dy, float4* dx,
+                        float4* pw, float4* pb, int rows, int n4, float inv_n, float eps) {
+    const size_t smem = (size_t)(mode + 1) * 1024 * VPT * sizeof(float4);
+    if (smem > 48 * 1024) {
+        static std::atomic<uint64_t> done[2];
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (!(done[mode].load(std::memory_order_relaxed) & (1ull << (dev & 63)))) {
+            if (mode == 0) cudaFuncSetAttribute(norm_bwd_stream_kernel<VPT, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            else cudaFuncSetAttribute(norm_bwd_stream_kernel<VPT, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            done[mode].fetch_or(1ull << (dev & 63), std::memory_order_relaxed);
+        }
+    }
+    if (mode == 0) launch_with_pdl(norm_bwd_stream_kernel<VPT, 0>, dim3(parts), dim3(1024), smem, s, x, w, dy, dx, pw, pb, rows, n4, inv_n, eps);
+    else launch_with_pdl(norm_bwd_stream_kernel<VPT, 1>, dim3(parts), dim3(1024), smem, s, x, w, dy, dx, pw, pb, rows, n4, inv_n, eps);
+}
+
 }  // namespace
 
 // Shared by the generic entry (scratch from the caller) and the allocation-free entry (static scratch).
@@ -279,10 +428,14 @@ int enqueue_norm_bwd(int mode, int rows, int n, float eps, int parts, cudaStream
     if (c.threads == T && c.vpt == V) launch_norm<T, V>(mode, parts, s, (const float4*)x, (const float4*)w, (const float4*)dy, \
                                                         (float4*)dx, pw, pb, rows, n4, inv_n, eps); else
     PB200_BWD_CASE(32, 1) PB200_BWD_CASE(32, 2) PB200_BWD_CASE(64, 2) PB200_BWD_CASE(128, 2)
-    PB200_BWD_CASE(128, 4) PB200_BWD_CASE(256, 4) PB200_BWD_CASE(512, 4) PB200_BWD_CASE(512, 8) {}
+    PB200_BWD_CASE(128, 4) PB200_BWD_CASE(256, 4) PB200_BWD_CASE(512, 8)
+    if (c.threads == 1024) launch_norm_stream<2>(mode, parts, s, (const float4*)x, (const float4*)w, (const float4*)dy,
+                                                 (float4*)dx, pw, pb, rows, n4, inv_n, eps);
 #undef PB200_BWD_CASE
-    fold_partials_kernel<<<dim3((n4 + 31) / 32, mode == 1 ? 2 : 1), 1024, 0, s>>>(pw, (float4*)dw, (float4*)db, parts, n4);
     cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess)
+        e = launch_with_pdl(fold_partials_kernel, dim3((n4 + 31) / 32, mode == 1 ? 2 : 1), dim3(1024), 0, s,
+                            (const float4*)pw, (float4*)dw, (float4*)db, parts, n4);
     if (e != cudaSuccess) { set_err(err, "backward norm launch failed: %s", cudaGetErrorString(e)); return PB200_ERR_LAUNCH; }
     return PB200_OK;
 }

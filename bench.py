@@ -381,10 +381,12 @@ def moe_table(torch) -> dict:
 
 
 def attention_table(torch) -> dict:
-    """Attention forward at B=4, H=16, S=4096 against torch SDPA on the same operands."""
+    """Attention forward and backward at B=4, H=16, S=4096 against torch SDPA on the same operands
+    (the backward counts five products per tile pair, 2.5x the forward's flops)."""
     import torch.nn.functional as F
     from oracle import inputs
-    from pyptx_b200.examples.blackwell.flash_attention import attention_flops, build_flash_attention
+    from pyptx_b200.examples.blackwell.flash_attention import (attention_bwd_flops, attention_flops,
+                                                               build_flash_attention, build_flash_attention_bwd)
     out = {}
     for d in (64, 128):
         q, kk, v = (t.view(4, 16, 4096, d).cuda() for t in inputs.attention_inputs(64, 4096, 4096, d))
@@ -396,7 +398,105 @@ def attention_table(torch) -> dict:
             out[tag + "_tflops"] = fl / (ms * 1e-3) / 1e12
             ms = time_cuda(lambda: F.scaled_dot_product_attention(q, kk, v, is_causal=causal), 20, 5, torch)
             out[tag + "_torch_sdpa_tflops"] = fl / (ms * 1e-3) / 1e12
+            # backward: (dQ, dK, dV) from (Q, K, V, O, lse, dO)
+            fwd = build_flash_attention(4, 16, 4096, 4096, d, causal=causal, return_lse=True)
+            bwd = build_flash_attention_bwd(4, 16, 4096, 4096, d, causal=causal)
+            o, lse = fwd(q, kk, v)
+            d_o = torch.randn_like(o)
+            flb = attention_bwd_flops(4, 16, 4096, 4096, d, causal)
+            ms = time_cuda(lambda: bwd(q, kk, v, o, lse, d_o), 10, 3, torch)
+            out[tag + "_bwd_tflops"] = flb / (ms * 1e-3) / 1e12
+            qg, kg, vg = (t.detach().clone().requires_grad_() for t in (q, kk, v))
+            og = F.scaled_dot_product_attention(qg, kg, vg, is_causal=causal)
+            ms = time_cuda(lambda: torch.autograd.grad(og, (qg, kg, vg), d_o, retain_graph=True), 10, 3, torch)
+            out[tag + "_bwd_torch_sdpa_tflops"] = flb / (ms * 1e-3) / 1e12
+            del fwd, bwd, o, lse, d_o, qg, kg, vg, og
         del q, kk, v
+    return out
+
+
+def gpu_host_placement(torch, local_rank: int, pinned) -> dict:
+    """Where this rank's GPU and pinned buffer sit relative to the host's NUMA nodes (read-only:
+    sysfs attributes of the GPU's PCI function and this process's numa_maps)."""
+    info = {"cpu_affinity": len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else None}
+    try:
+        bdf = torch.cuda.get_device_properties(local_rank).pci_bus_id
+        bdf = f"{torch.cuda.get_device_properties(local_rank).pci_domain_id:04x}:{bdf:02x}:" \
+              f"{torch.cuda.get_device_properties(local_rank).pci_device_id:02x}.0"
+        base = f"/sys/bus/pci/devices/{bdf}"
+        with open(base + "/numa_node") as f:
+            info["gpu_numa_node"] = int(f.read().strip())
+        with open(base + "/local_cpulist") as f:
+            info["gpu_local_cpulist"] = f.read().strip()
+    except Exception as exc:  # noqa: BLE001 - containers often hide sysfs
+        info["gpu_numa_node"] = f"unknown ({type(exc).__name__})"
+    try:
+        ptr = pinned.data_ptr()
+        best = None
+        with open("/proc/self/numa_maps") as f:
+            for line in f:
+                start = int(line.split()[0], 16)
+                if start <= ptr and (best is None or start > best[0]):
+                    best = (start, line)
+        if best:
+            info["pinned_pages_by_node"] = {tok.split("=")[0]: int(tok.split("=")[1])
+                                            for tok in best[1].split() if tok[0] == "N" and "=" in tok}
+    except Exception as exc:  # noqa: BLE001
+        info["pinned_pages_by_node"] = f"unknown ({type(exc).__name__})"
+    return info
+
+
+def host_link_table(torch, dist, world: int, local_rank: int, up_pins, d_pin) -> dict:
+    """Host <-> device copy rate of every rank, all ranks copying at the same time: upload only,
+    download only, and both directions at once, with the end-to-end step's own buffers (A and B_T up,
+    D down).  Each direction is timed with CUDA events on its own stream.  This is the ceiling of
+    the end-to-end leg; at N > 1 the ranks share the host's PCIe root ports and memory controllers."""
+    dev_up = [torch.empty(t.shape, dtype=t.dtype, device="cuda") for t in up_pins]
+    dev_d = torch.empty(d_pin.shape, dtype=d_pin.dtype, device="cuda")
+    up, down = torch.cuda.Stream(), torch.cuda.Stream()
+    up_bytes = sum(t.numel() * t.element_size() for t in up_pins)
+    down_bytes = d_pin.numel() * d_pin.element_size()
+    reps = 3
+
+    def run(do_up: bool, do_down: bool):
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ev = {n: (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for n in ("up", "down")}
+        if do_up:
+            with torch.cuda.stream(up):
+                ev["up"][0].record()
+                for _ in range(reps):
+                    for dst, src in zip(dev_up, up_pins):
+                        dst.copy_(src, non_blocking=True)
+                ev["up"][1].record()
+        if do_down:
+            with torch.cuda.stream(down):
+                ev["down"][0].record()
+                for _ in range(reps):
+                    d_pin.copy_(dev_d, non_blocking=True)
+                ev["down"][1].record()
+        up.synchronize(); down.synchronize()
+        h2d = up_bytes * reps / (ev["up"][0].elapsed_time(ev["up"][1]) * 1e-3) / 1e9 if do_up else 0.0
+        d2h = down_bytes * reps / (ev["down"][0].elapsed_time(ev["down"][1]) * 1e-3) / 1e9 if do_down else 0.0
+        return h2d, d2h
+
+    run(True, True)
+    out = {}
+    for name, (u, d) in (("h2d_only", (True, False)), ("d2h_only", (False, True)), ("both", (True, True))):
+        t = torch.tensor(run(u, d), device="cuda", dtype=torch.float64)
+        if world > 1:
+            gathered = [torch.zeros_like(t) for _ in range(world)]
+            dist.all_gather(gathered, t)
+        else:
+            gathered = [t]
+        ups = [float(g[0]) for g in gathered]
+        downs = [float(g[1]) for g in gathered]
+        out[name] = {"h2d_GBs_per_rank": [round(v, 1) for v in ups], "d2h_GBs_per_rank": [round(v, 1) for v in downs],
+                     "h2d_GBs_total": round(sum(ups), 1), "d2h_GBs_total": round(sum(downs), 1)}
+    out["placement_rank0"] = gpu_host_placement(torch, local_rank, up_pins[0])
+    out["bytes_per_step"] = {"h2d": up_bytes, "d2h": down_bytes}
     return out
 
 
@@ -430,9 +530,16 @@ def run_case(args) -> None:
         d = 64 if "64" in name else 128
         causal = "causal" in name
         q, kk, v = inputs.attention_inputs(64, size, size, d)
-        k = build_flash_attention(4, 16, size, size, d, causal=causal)
         ops = tuple(t.view(4, 16, size, d).cuda() for t in (q, kk, v))
-        work, unit = attention_flops(4, 16, size, size, d, causal), "TFLOP/s"
+        if "bwd" in name:
+            from pyptx_b200.examples.blackwell.flash_attention import attention_bwd_flops, build_flash_attention_bwd
+            o, lse = build_flash_attention(4, 16, size, size, d, causal=causal, return_lse=True)(*ops)
+            k = build_flash_attention_bwd(4, 16, size, size, d, causal=causal)
+            ops = ops + (o, lse, torch.randn_like(o))
+            work, unit = attention_bwd_flops(4, 16, size, size, d, causal), "TFLOP/s"
+        else:
+            k = build_flash_attention(4, 16, size, size, d, causal=causal)
+            work, unit = attention_flops(4, 16, size, size, d, causal), "TFLOP/s"
     elif name == "rms_norm":
         k, ops, work = build_rms_norm(B, N), tuple(t.cuda() for t in inputs.rms_norm_inputs(B, N)), rms_norm_bytes(B, N)
     elif name == "layer_norm":
@@ -718,6 +825,11 @@ def run_ours(args) -> None:
     e2e_value = flops_per_rank * world / (e2e_ms * 1e-3) / 1e12
     h2d = a_pin.numel() * 2 + bt_pin.numel() * 2
     d2h = d_pin.numel() * 4
+    # what the host link gives when nothing but copies runs (every rank at once)
+    host_link = host_link_table(torch, dist, world, local_rank, [a_pin, bt_pin], d_pin)
+    # the e2e step moves h2d + d2h bytes per rank; with both directions busy it cannot beat this
+    both = host_link["both"]
+    link_floor_ms = max(h2d / (min(both["h2d_GBs_per_rank"]) * 1e9), d2h / (min(both["d2h_GBs_per_rank"]) * 1e9)) * 1e3
 
     gather = None
     gather_error = None
@@ -796,6 +908,8 @@ def run_ours(args) -> None:
             "clocks": dict(clocks or {}, note="NVML samples taken during the timed region (NVML reports the requested SM clock)"),
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms, "steps": e2e_steps, "calls_in_flight": depth,
+                    "host_link": host_link, "copy_bound_ms_per_step": link_floor_ms,
+                    "frac_of_copy_bound": link_floor_ms / e2e_ms,
                     "api": "pyptx_b200.host_pipeline.HostPipeline(build_gemm_2sm(...)).submit(pinned A, pinned B_T, out=pinned D)"},
             "gpu_launches": args.steps,
             "roofline": {"bound": "tensor", "achieved": kernel_tflops, "peak": peak, "unit": "TFLOP/s",
@@ -811,6 +925,18 @@ def run_ours(args) -> None:
         }
         if gather is not None:
             line["gather"] = gather
+            # the same 8192^3 product split by rows over the ranks (strong scaling of the headline
+            # kernel): slowest rank's local GEMM against this run's one-GPU step time
+            t_local = gather.get("f32", {}).get("local_gemm_ms")
+            if t_local:
+                line["strong"] = {
+                    "problem": f"one 8192^3 product, M split {world} ways, B_T replicated, no gather",
+                    "local_gemm_ms_max_over_ranks": t_local, "one_gpu_ms": ms_per_step,
+                    "tflops_total": flops_per_rank / (t_local * 1e-3) / 1e12,
+                    "efficiency": ms_per_step / (world * t_local),
+                    "tiles": (f"M_local={S // world}: {(S // world) // 256 * (S // 256)} tiles of 256x256 "
+                              f"(or half as many of 512x256) on 74 CTA pairs"),
+                }
         if extras is not None:
             line["kernels"] = extras
             if not args.no_pyptx:
@@ -837,7 +963,7 @@ def main() -> None:
                     help="calls in flight in the end-to-end leg (1 = upload, multiply, download strictly in turn)")
     ap.add_argument("--no-extras", action="store_true", help="skip the context table (other kernels, cuBLAS)")
     ap.add_argument("--case", default=None,
-                    help="run ONE kernel only: gemm_1sm gemm_2sm grouped attention_d64 attention_d128[_causal] "
+                    help="run ONE kernel only: gemm_1sm gemm_2sm grouped attention_d64 attention_d128[_causal][_bwd] "
                          "rms_norm layer_norm swiglu softmax")
     ap.add_argument("--size", type=int, default=8192, help="M=N=K (gemm cases) or sequence length (attention cases)")
     args = ap.parse_args()

@@ -204,9 +204,25 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int n_qblocks = (int)gridDim.x;
-    // Heaviest causal blocks (largest row index) first.
-    const int qblock = n_qblocks - 1 - (int)blockIdx.x;
-    const int bh = (int)blockIdx.y;
+    // Causal: a query block's cost grows with its row index, and CTAs start in linear block order
+    // (x fastest).  Blocks are therefore dealt out heaviest first across a GROUP of heads at a
+    // time -- within a group all heads' last blocks, then all their second-to-last ones, ... --
+    // so that what runs at the end of the grid is light blocks, not one head's heaviest.  Groups
+    // of kHeadGroup heads keep the K/V working set of the CTAs in flight inside L2.
+#ifndef PB200_FMHA_HEAD_GROUP
+#define PB200_FMHA_HEAD_GROUP 16
+#endif
+    constexpr int kHeadGroup = PB200_FMHA_HEAD_GROUP;
+    int qblock = n_qblocks - 1 - (int)blockIdx.x;
+    int bh = (int)blockIdx.y;
+    if (prm.causal) {
+        const int lin = (int)blockIdx.x + n_qblocks * (int)blockIdx.y;
+        const int grp = lin / (n_qblocks * kHeadGroup);
+        const int rem = lin - grp * (n_qblocks * kHeadGroup);
+        const int heads_here = min(kHeadGroup, (int)gridDim.y - grp * kHeadGroup);
+        qblock = n_qblocks - 1 - rem / heads_here;
+        bh = grp * kHeadGroup + rem % heads_here;
+    }
     const int q0 = qblock * 2 * kQTile;
     const bool has_t1 = q0 + kQTile < prm.s_q;
     // Number of K/V tiles each query tile visits.
@@ -474,19 +490,33 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     tmem_ld_32x32b_x32(ts + (uint32_t)(c * 32), *reinterpret_cast<uint32_t(*)[32]>(&sc[c * 32]));
                 tmem_ld_wait();
                 reg_fence(sc);
+                // On a masked tile every 32-key chunk is, for the 32 rows of this warp, wholly visible,
+                // wholly hidden, or mixed: only mixed chunks pay for per-element masking, hidden ones
+                // are not evaluated at all (on an aligned diagonal tile: q visible, 1 mixed, 3 - q hidden).
+                const int row_lo = q0 + t * kQTile + q * 32;
+                const int vis_lo = prm.causal ? min(row_lo + prm.causal_offset, prm.s_kv - 1) : prm.s_kv - 1;        // first row of the warp
+                const int vis_hi = prm.causal ? min(row_lo + 31 + prm.causal_offset, prm.s_kv - 1) : prm.s_kv - 1;   // last row
+                auto chunk_class = [&](int c) {          // 0 visible, 1 mixed, 2 hidden
+                    const int kc = key0 + c * 32;
+                    return !diag || kc + 31 <= vis_lo ? 0 : kc > vis_hi ? 2 : 1;
+                };
                 // row maximum of the raw scores: four independent chains of 3-input max
                 float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-                if (diag) {
 #pragma unroll
-                    for (int i = 0; i < kKvTile; ++i)
-                        if (key0 + i <= last_visible) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sc[i]));
-                } else {
+                for (int c = 0; c < kKvTile / 32; ++c) {
+                    const int cls = chunk_class(c);
+                    if (cls == 0) {
 #pragma unroll
-                    for (int i = 0; i < kKvTile; i += 8) {
-                        mx4[0] = fmax3(mx4[0], __uint_as_float(sc[i]), __uint_as_float(sc[i + 1]));
-                        mx4[1] = fmax3(mx4[1], __uint_as_float(sc[i + 2]), __uint_as_float(sc[i + 3]));
-                        mx4[2] = fmax3(mx4[2], __uint_as_float(sc[i + 4]), __uint_as_float(sc[i + 5]));
-                        mx4[3] = fmax3(mx4[3], __uint_as_float(sc[i + 6]), __uint_as_float(sc[i + 7]));
+                        for (int i = c * 32; i < c * 32 + 32; i += 8) {
+                            mx4[0] = fmax3(mx4[0], __uint_as_float(sc[i]), __uint_as_float(sc[i + 1]));
+                            mx4[1] = fmax3(mx4[1], __uint_as_float(sc[i + 2]), __uint_as_float(sc[i + 3]));
+                            mx4[2] = fmax3(mx4[2], __uint_as_float(sc[i + 4]), __uint_as_float(sc[i + 5]));
+                            mx4[3] = fmax3(mx4[3], __uint_as_float(sc[i + 6]), __uint_as_float(sc[i + 7]));
+                        }
+                    } else if (cls == 1) {
+#pragma unroll
+                        for (int i = c * 32; i < c * 32 + 32; ++i)
+                            if (key0 + i <= last_visible) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sc[i]));
                     }
                 }
                 const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
@@ -522,21 +552,11 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     for (int cc = 0; cc < 2; ++cc) {
                         const int c = h * 2 + cc;          // 32-key chunk index
                         uint32_t pk[16];
-                        if (!diag) {
-                            // Common case, no mask: per pair of scores one FFMA2, two EX2, one FADD2, one pack.
-#pragma unroll
-                            for (int i = 0; i < 16; ++i) {
-                                float t0, t1;
-                                fma2(t0, t1, __uint_as_float(v[cc * 32 + 2 * i]), __uint_as_float(v[cc * 32 + 2 * i + 1]),
-                                     prm.scale_log2, neg_m);
-                                float p0, p1;
-                                if ((i & 7) < kFmaExpPairsOf8<HD>) exp2_fma_pair(p0, p1, t0, t1);   // compile-time choice per pair
-                                else { p0 = fast_exp2(t0); p1 = fast_exp2(t1); }
-                                add2(sum4[2 * (i & 1)], sum4[2 * (i & 1) + 1], p0, p1);
-                                __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);    // .x = p0 in the low half
-                                pk[i] = *reinterpret_cast<uint32_t*>(&b);
-                            }
-                        } else {
+                        const int cls = chunk_class(c);
+                        if (cls == 0) {
+                            // no mask: per pair of scores one FFMA2, two EX2, one FADD2, one pack
+                            exp_chunk<kFmaExpPairsOf8<HD>>(*reinterpret_cast<uint32_t(*)[32]>(&v[cc * 32]), pk, sum4, prm.scale_log2, neg_m);
+                        } else if (cls == 1) {
 #pragma unroll
                             for (int i = 0; i < 16; ++i) {
                                 float p0 = fast_exp2(fmaf(__uint_as_float(v[cc * 32 + 2 * i]), prm.scale_log2, neg_m));
@@ -547,6 +567,9 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                                 __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
                                 pk[i] = *reinterpret_cast<uint32_t*>(&b);
                             }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) pk[i] = 0u;      // P = 0 for keys no row of this warp sees
                         }
                         if (P_SMEM) {
                             // K-major SWIZZLE_128B image: 64-key blocks of [128 rows][128 bytes]

@@ -138,9 +138,24 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int bh = (int)blockIdx.y;
-    // Stationary tile: MODE 0 counts key tiles, MODE 1 query tiles (heaviest causal tiles first).
-    const int st = MODE == 0 ? (int)blockIdx.x : (int)gridDim.x - 1 - (int)blockIdx.x;
+    // Stationary tile: MODE 0 counts key tiles (tile 0 meets every query tile under the causal mask),
+    // MODE 1 query tiles from the last (which meets every key tile) down: heaviest first.  Causal
+    // launches deal the tiles out heaviest-first across a group of heads at a time (CTAs start in
+    // linear block order, x fastest), so that the grid ends on light tiles; groups of 16 heads keep
+    // the operands of the CTAs in flight inside L2.
+    constexpr int kHeadGroup = 16;
+    int bh = (int)blockIdx.y;
+    int heavy_rank = (int)blockIdx.x;                   // 0 = heaviest
+    if (prm.causal) {
+        const int n_st = (int)gridDim.x;
+        const int lin = (int)blockIdx.x + n_st * (int)blockIdx.y;
+        const int grp = lin / (n_st * kHeadGroup);
+        const int rem = lin - grp * (n_st * kHeadGroup);
+        const int heads_here = min(kHeadGroup, (int)gridDim.y - grp * kHeadGroup);
+        heavy_rank = rem / heads_here;
+        bh = grp * kHeadGroup + rem % heads_here;
+    }
+    const int st = MODE == 0 ? heavy_rank : (int)gridDim.x - 1 - heavy_rank;
     const int st0 = st * kTile;
     // Range of streamed tiles [m_begin, m_end).
     int m_begin = 0, m_end;

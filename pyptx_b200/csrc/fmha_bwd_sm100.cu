@@ -27,6 +27,7 @@
 // A small row kernel first writes delta and lse * log2(e) into scratch, padded to whole tiles
 // (padding rows get lse = +inf, i.e. P = 0).  Every mbarrier wait is bounded.
 #include "common.cuh"
+#include "fmha_math.cuh"
 #include "ptx.cuh"
 
 #include <cuda_bf16.h>
@@ -41,6 +42,14 @@ using namespace ptx;
 
 constexpr int kTile = 128;            // rows of a stationary tile = rows of a streamed tile
 constexpr int kBwdThreads = 384;
+constexpr int kBwdLaunchRegs = 168;     // registers per thread at launch (65536 / 384, multiple of 8)
+constexpr int kBwdRegsIssue = 88;       // TMA / MMA warpgroup after setmaxnreg
+constexpr int kBwdRegsMath = 208;       // the two score-math warpgroups
+static_assert(kBwdRegsIssue * 128 + kBwdRegsMath * 256 <= kBwdLaunchRegs * kBwdThreads,
+              "setmaxnreg may only hand around the registers the CTA was launched with");
+#ifndef PB200_BWD_FMA_EXP_PAIRS
+#define PB200_BWD_FMA_EXP_PAIRS 0       // of every 8 score pairs, how many take the FMA-pipe exp2 (0..3 measured within 3 %)
+#endif
 
 struct BwdParams {
     int bh, s_q, s_kv, sq_pad;
@@ -56,15 +65,11 @@ struct BwdSmem {
     static constexpr int kOffStat = 0;                                  // two stationary tiles
     static constexpr int kOffRing = 2 * kTileBytes;                     // kStages x two streamed tiles
     static constexpr int kOffBar = kOffRing + kStages * 2 * kTileBytes;
-    static constexpr int kTotal = kOffBar + 512 + 1024;
+    static constexpr int kOffStats = kOffBar + 512;                     // MODE 0: lse2 / delta of the streamed queries
+    static constexpr int kTotal = kOffStats + 2 * 2 * 128 * 4 + 1024;
     static_assert(kTotal <= 227 * 1024, "shared memory budget exceeded");
 };
 
-__device__ __forceinline__ float ex2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
     __nv_bfloat162 v = __floats2bfloat162_rn(a, b);      // .x = a in the low half
     return *reinterpret_cast<uint32_t*>(&v);
@@ -131,6 +136,7 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
     const uint32_t bar_xfull = bar_empty + 8 * kStages;   // [1] S and dP of a streamed tile are in TMEM
     const uint32_t bar_pready = bar_xfull + 8;            // [1] P and dS written (8 warps)
     const uint32_t bar_outfull = bar_pready + 8;          // [1] accumulators complete
+    float* stats_gen = reinterpret_cast<float*>(gen + L::kOffStats);    // [parity][warpgroup][64 lse2 | 64 delta]
     const uint32_t s_tmem_slot = bar_outfull + 8;
     const uint32_t s_abort = s_tmem_slot + 8;
     volatile uint32_t* tmem_slot_gen = (volatile uint32_t*)(gen + (s_tmem_slot - base));
@@ -194,6 +200,8 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
     const uint32_t tmem_x1 = tmem_base, tmem_x2 = tmem_base + 128u;
     const uint32_t tmem_acc_a = tmem_base + 256u, tmem_acc_b = tmem_base + 384u;
 
+    if (warp < 4) {
+    reg_dealloc<kBwdRegsIssue>();
     if (warp == 0) {
         // ------------------------------- TMA producer -------------------------------
         if (lane == 0 && n_iter > 0) {
@@ -270,7 +278,9 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
             }
             if (ok) umma_commit<1>(bar_outfull);
         }
-    } else if (warp >= 4) {
+    }
+    } else {
+        reg_alloc<kBwdRegsMath>();
         // ------------------------------- score math + epilogue -----------------------
         const int wg = (warp - 4) >> 2;                  // which 64 streamed columns
         const int q4 = warp & 3;                         // TMEM lane quarter
@@ -284,12 +294,21 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
         float my_lse2 = 0.f, my_delta = 0.f;
         if (MODE == 1) { my_lse2 = lse2_bh[srow]; my_delta = delta_bh[srow]; }     // srow < sq_pad always
         bool ok = true;
+        const int wg_tid = (int)threadIdx.x - 128 - wg * 128;      // 0..127 inside the warpgroup
         for (int it = 0; it < n_iter && ok; ++it) {
+            const int m0 = (m_begin + it) * kTile + wg * 64;      // first streamed row of this thread's columns
+            // MODE 0: the columns are queries, so every thread needs the same 64 (lse2, delta) pairs.
+            // The warpgroup stages them in shared memory (one value per thread, fetched before the
+            // wait for the scores; two buffers by iteration parity) and reads them back as broadcasts.
+            float* stats = stats_gen + ((it & 1) * 2 + wg) * 128;
+            if (MODE == 0) {
+                stats[wg_tid] = wg_tid < 64 ? __ldg(lse2_bh + m0 + wg_tid) : __ldg(delta_bh + m0 + wg_tid - 64);
+                named_barrier_sync(1 + wg, 128);
+            }
             ok = mbar_wait(bar_xfull, (uint32_t)it & 1u, ctx, 31);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after_sync();
-            const int m0 = (m_begin + it) * kTile + wg * 64;      // first streamed row of this thread's columns
             // Causal: key <= query + offset.  MODE 0: row = key, column = query; MODE 1 the other way.
             // Whole-tile shortcut: no element of these 64 columns is hidden when the smallest query
             // of the pairing still sees the largest key.
@@ -298,47 +317,44 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
                 if (MODE == 0) masked = st0 + q4 * 32 + 31 > m0 + prm.causal_offset;
                 else masked = m0 + 63 > st0 + q4 * 32 + prm.causal_offset;
             }
-#pragma unroll 1
-            for (int h = 0; h < 2; ++h) {                      // 32 columns at a time
-                uint32_t sx[32], dp[32];
-                tmem_ld_32x32b_x32(tx1 + (uint32_t)(h * 32), sx);
-                tmem_ld_32x32b_x32(tx2 + (uint32_t)(h * 32), dp);
-                tmem_ld_wait();
-                reg_fence(sx); reg_fence(dp);
-                uint32_t pp[16], ds[16];
+            // All 64 columns of S and dP at once: four TMEM loads in flight, one wait.
+            uint32_t sx[64], dp[64];
+            tmem_ld_32x32b_x32(tx1, *reinterpret_cast<uint32_t(*)[32]>(&sx[0]));
+            tmem_ld_32x32b_x32(tx1 + 32u, *reinterpret_cast<uint32_t(*)[32]>(&sx[32]));
+            tmem_ld_32x32b_x32(tx2, *reinterpret_cast<uint32_t(*)[32]>(&dp[0]));
+            tmem_ld_32x32b_x32(tx2 + 32u, *reinterpret_cast<uint32_t(*)[32]>(&dp[32]));
+            tmem_ld_wait();
+            reg_fence(sx); reg_fence(dp);
+            uint32_t pp[32], ds[32];
+            // Per pair of columns: one FFMA2 (score -> exponent), two exponentials (MUFU, or the
+            // FMA-pipe form for some pairs), one FADD2 (dP - delta), one FMUL2, two packs.
 #pragma unroll
-                for (int c4 = 0; c4 < 8; ++c4) {
-                    float l4[4], d4[4];
-                    if (MODE == 0) {
-                        const float4 lv = __ldg(reinterpret_cast<const float4*>(lse2_bh + m0 + h * 32) + c4);
-                        const float4 dv = __ldg(reinterpret_cast<const float4*>(delta_bh + m0 + h * 32) + c4);
-                        l4[0] = lv.x; l4[1] = lv.y; l4[2] = lv.z; l4[3] = lv.w;
-                        d4[0] = dv.x; d4[1] = dv.y; d4[2] = dv.z; d4[3] = dv.w;
-                    } else {
-                        l4[0] = l4[1] = l4[2] = l4[3] = my_lse2;
-                        d4[0] = d4[1] = d4[2] = d4[3] = my_delta;
-                    }
-                    float p4[4], g4[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int c = c4 * 4 + e;                 // column inside this half
-                        float p = ex2(fmaf(__uint_as_float(sx[c]), prm.scale_log2, -l4[e]));
-                        if (masked) {
-                            const int mrow = m0 + h * 32 + c;     // streamed row (query in MODE 0, key in MODE 1)
-                            const bool hidden = MODE == 0 ? (srow > mrow + prm.causal_offset) : (mrow > srow + prm.causal_offset);
-                            if (hidden) p = 0.f;
-                        }
-                        p4[e] = p;
-                        g4[e] = p * (__uint_as_float(dp[c]) - d4[e]);
-                    }
-                    pp[c4 * 2] = pack_bf16(p4[0], p4[1]); pp[c4 * 2 + 1] = pack_bf16(p4[2], p4[3]);
-                    ds[c4 * 2] = pack_bf16(g4[0], g4[1]); ds[c4 * 2 + 1] = pack_bf16(g4[2], g4[3]);
+            for (int c2 = 0; c2 < 32; ++c2) {
+                float nl0, nl1, nd0, nd1;
+                if (MODE == 0) {
+                    const float2 lv = reinterpret_cast<const float2*>(stats)[c2];
+                    const float2 dv = reinterpret_cast<const float2*>(stats + 64)[c2];
+                    nl0 = -lv.x; nl1 = -lv.y; nd0 = -dv.x; nd1 = -dv.y;
+                } else {
+                    nl0 = nl1 = -my_lse2; nd0 = nd1 = -my_delta;
                 }
-                // P over the head of this warpgroup's own S columns, dS over the head of its dP columns:
-                // half h writes columns [16h, 16h+16), all of which this thread has already read.
-                if (MODE == 0) tmem_st_32x32b_x16(tx1 + (uint32_t)(h * 16), pp);
-                tmem_st_32x32b_x16(tx2 + (uint32_t)(h * 16), ds);
+                float t0, t1, p0, p1, u0, u1, g0, g1;
+                fma2v(t0, t1, __uint_as_float(sx[2 * c2]), __uint_as_float(sx[2 * c2 + 1]), prm.scale_log2, prm.scale_log2, nl0, nl1);
+                if ((c2 & 7) < PB200_BWD_FMA_EXP_PAIRS) exp2_fma_pair(p0, p1, t0, t1);
+                else { p0 = fast_exp2(t0); p1 = fast_exp2(t1); }
+                if (masked) {
+                    const int mrow = m0 + 2 * c2;                 // streamed row (query in MODE 0, key in MODE 1)
+                    if (MODE == 0 ? (srow > mrow + prm.causal_offset) : (mrow > srow + prm.causal_offset)) p0 = 0.f;
+                    if (MODE == 0 ? (srow > mrow + 1 + prm.causal_offset) : (mrow + 1 > srow + prm.causal_offset)) p1 = 0.f;
+                }
+                add2v(u0, u1, __uint_as_float(dp[2 * c2]), __uint_as_float(dp[2 * c2 + 1]), nd0, nd1);
+                mul2v(g0, g1, p0, p1, u0, u1);
+                pp[c2] = pack_bf16(p0, p1);
+                ds[c2] = pack_bf16(g0, g1);
             }
+            // P over the head of this warpgroup's own S columns, dS over the head of its dP columns.
+            if (MODE == 0) tmem_st_32x32b_x32(tx1, pp);
+            tmem_st_32x32b_x32(tx2, ds);
             tmem_st_wait();
             tc_fence_before_sync();
             __syncwarp();

@@ -22,8 +22,12 @@
 //   warp 1      MMA issuer (single thread)
 //   warps 4-7   score math for streamed columns 0-63    (one TMEM lane per thread)
 //   warps 8-11  score math for streamed columns 64-127
-// TMEM: X1 (S) | X2 (dP) | acc A | acc B, 128 columns each.  P overwrites the first half of each
-// warpgroup's own S columns, dS the same of dP, so no warpgroup writes where the other still reads.
+// TMEM: X1 (S) | X2 (dP) | acc A | acc B, 128 columns each.  The two math warpgroups ping-pong: each
+// owns one 64-row half of every streamed tile, with its own score MMAs (N = 64), its own barriers
+// and its own half of the S / dP columns, so that while one warpgroup does its score math the tensor
+// core runs the other's MMAs.  P overwrites the head of a warpgroup's own S columns, dS the same of
+// dP, so no warpgroup writes where the other still reads, and the next scores of a half follow the
+// MMAs that read its P and dS (MMAs of one thread execute in issue order).
 // A small row kernel first writes delta and lse * log2(e) into scratch, padded to whole tiles
 // (padding rows get lse = +inf, i.e. P = 0).  Every mbarrier wait is bounded.
 #include "common.cuh"
@@ -122,7 +126,8 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
     using L = BwdSmem<HD>;
     constexpr int kStages = L::kStages;
     constexpr int kDBlocks = HD / 64;
-    constexpr uint32_t kIdescX = make_idesc_f16(kTile, kTile, true, 0, 0);      // both operands K-major
+    constexpr int kHalf = kTile / 2;                                             // streamed rows per warpgroup
+    constexpr uint32_t kIdescX = make_idesc_f16(kTile, kHalf, true, 0, 0);      // both operands K-major
     constexpr uint32_t kIdescAcc = make_idesc_f16(kTile, HD, true, 0, 1);       // B operand MN-major
 
     extern __shared__ uint8_t smem_raw[];
@@ -133,9 +138,9 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
     const uint32_t bar_stat = bars;                       // [1]
     const uint32_t bar_full = bars + 8;                   // [kStages]
     const uint32_t bar_empty = bar_full + 8 * kStages;    // [kStages]
-    const uint32_t bar_xfull = bar_empty + 8 * kStages;   // [1] S and dP of a streamed tile are in TMEM
-    const uint32_t bar_pready = bar_xfull + 8;            // [1] P and dS written (8 warps)
-    const uint32_t bar_outfull = bar_pready + 8;          // [1] accumulators complete
+    const uint32_t bar_xfull = bar_empty + 8 * kStages;   // [2] S and dP of a warpgroup's half tile are in TMEM
+    const uint32_t bar_pready = bar_xfull + 16;           // [2] its P and dS are written (4 warps)
+    const uint32_t bar_outfull = bar_pready + 16;         // [1] accumulators complete
     float* stats_gen = reinterpret_cast<float*>(gen + L::kOffStats);    // [parity][warpgroup][64 lse2 | 64 delta]
     const uint32_t s_tmem_slot = bar_outfull + 8;
     const uint32_t s_abort = s_tmem_slot + 8;
@@ -180,8 +185,7 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
         *abort_gen = 0;
         mbar_init(bar_stat, 1);
         for (int s = 0; s < kStages; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
-        mbar_init(bar_xfull, 1);
-        mbar_init(bar_pready, 8);
+        for (int w = 0; w < 2; ++w) { mbar_init(bar_xfull + 8 * w, 1); mbar_init(bar_pready + 8 * w, 4); }
         mbar_init(bar_outfull, 1);
         fence_mbarrier_init();
         fence_proxy_async_smem();
@@ -234,46 +238,50 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
             const uint32_t m_lo = (uint32_t)md, m_hi = (uint32_t)(md >> 32);
             const uint32_t b_lo = (uint32_t)bd, b_hi = (uint32_t)(bd >> 32);
             constexpr uint32_t kTileDesc = (uint32_t)(L::kTileBytes >> 4);
-            // X_t = stationary tile t . (streamed tile t of the stage)^T, contraction over head_dim
-            auto issue_x = [&](int t, int stage) {
-                const uint32_t a = s_lo + (uint32_t)t * kTileDesc;
-                const uint32_t b = m_lo + (uint32_t)(stage * 2 + t) * kTileDesc;
+            // X_t[:, 64 w ..] = stationary tile t . (rows 64 w .. of streamed tile t)^T, contraction over head_dim
+            auto issue_x = [&](int w, int stage) {
 #pragma unroll
-                for (int k = 0; k < HD / 16; ++k) {
-                    const uint32_t off = (uint32_t)((k >> 2) * (kTile * 8) + (k & 3) * 2);
-                    umma_f16_ss_lohi(t == 0 ? tmem_x1 : tmem_x2, a + off, s_hi, b + off, m_hi, kIdescX, k != 0 ? 1u : 0u);
+                for (int t = 0; t < 2; ++t) {
+                    const uint32_t a = s_lo + (uint32_t)t * kTileDesc;
+                    const uint32_t b = m_lo + (uint32_t)(stage * 2 + t) * kTileDesc + (uint32_t)(w * ((kHalf * 128) >> 4));
+                    const uint32_t d = (t == 0 ? tmem_x1 : tmem_x2) + (uint32_t)(w * kHalf);
+#pragma unroll
+                    for (int k = 0; k < HD / 16; ++k) {
+                        const uint32_t off = (uint32_t)((k >> 2) * (kTile * 8) + (k & 3) * 2);
+                        umma_f16_ss_lohi(d, a + off, s_hi, b + off, m_hi, kIdescX, k != 0 ? 1u : 0u);
+                    }
                 }
             };
-            // acc += (P or dS from TMEM) . streamed tile t, contraction over the 128 streamed rows.
-            // The operand of each warpgroup sits at the start of that warpgroup's own 64 columns.
-            auto issue_acc = [&](uint32_t acc, uint32_t a_tmem, int t, int stage, bool first) {
-                const uint32_t b = b_lo + (uint32_t)(stage * 2 + t) * kTileDesc;
+            // acc += (P or dS of warpgroup w, from TMEM) . rows 64 w .. of streamed tile t: contraction
+            // over those 64 rows.  The operand sits at the head of the warpgroup's own 64 columns.
+            auto issue_acc = [&](uint32_t acc, uint32_t a_tmem, int t, int w, int stage, bool first) {
+                const uint32_t b = b_lo + (uint32_t)(stage * 2 + t) * kTileDesc + (uint32_t)(w * ((kHalf * 128) >> 4));
 #pragma unroll
-                for (int k = 0; k < kTile / 16; ++k)
-                    umma_f16_ts_lohi(acc, a_tmem + (uint32_t)((k >> 2) * 64 + (k & 3) * 8), b + (uint32_t)(k * 128), b_hi,
+                for (int k = 0; k < kHalf / 16; ++k)
+                    umma_f16_ts_lohi(acc, a_tmem + (uint32_t)(w * kHalf + k * 8), b + (uint32_t)(k * 128), b_hi,
                                      kIdescAcc, (first && k == 0) ? 0u : 1u);
             };
             int stage = 0; uint32_t phase = 0;
             if (ok) ok = mbar_wait(bar_full, 0, ctx, 22);
             if (ok) {
                 tc_fence_after_sync();
-                issue_x(0, 0); issue_x(1, 0);
-                umma_commit<1>(bar_xfull);
+                issue_x(0, 0); umma_commit<1>(bar_xfull);
+                issue_x(1, 0); umma_commit<1>(bar_xfull + 8);
             }
             for (int it = 0; it < n_iter && ok; ++it) {
                 int nstage = stage + 1; uint32_t nphase = phase;
                 if (nstage == kStages) { nstage = 0; nphase ^= 1u; }
                 const bool more = it + 1 < n_iter;
-                if (!(ok = mbar_wait(bar_pready, (uint32_t)it & 1u, ctx, 23))) break;
                 if (more && !(ok = mbar_wait(bar_full + 8 * nstage, nphase, ctx, 24))) break;
-                tc_fence_after_sync();
-                // P lives over X1, dS over X2: the next X1 may only follow the MMA that reads P, the
-                // next X2 the one that reads dS (MMAs of one thread execute in issue order).
-                if (MODE == 0) issue_acc(tmem_acc_a, tmem_x1, 1, stage, it == 0);       // dV += P^T dO
-                if (more) issue_x(0, nstage);
-                issue_acc(tmem_acc_b, tmem_x2, 0, stage, it == 0);                      // dK += dS^T Q  /  dQ += dS K
-                umma_commit<1>(bar_empty + 8 * stage);
-                if (more) { issue_x(1, nstage); umma_commit<1>(bar_xfull); }
+#pragma unroll
+                for (int w = 0; w < 2; ++w) {
+                    if (!(ok = mbar_wait(bar_pready + 8 * w, (uint32_t)it & 1u, ctx, 23))) break;
+                    tc_fence_after_sync();
+                    if (MODE == 0) issue_acc(tmem_acc_a, tmem_x1, 1, w, stage, it == 0 && w == 0);     // dV += P^T dO
+                    issue_acc(tmem_acc_b, tmem_x2, 0, w, stage, it == 0 && w == 0);                    // dK += dS^T Q  /  dQ += dS K
+                    if (w == 1) umma_commit<1>(bar_empty + 8 * stage);
+                    if (more) { issue_x(w, nstage); umma_commit<1>(bar_xfull + 8 * w); }
+                }
                 stage = nstage; phase = nphase;
             }
             if (ok) umma_commit<1>(bar_outfull);
@@ -305,7 +313,7 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
                 stats[wg_tid] = wg_tid < 64 ? __ldg(lse2_bh + m0 + wg_tid) : __ldg(delta_bh + m0 + wg_tid - 64);
                 named_barrier_sync(1 + wg, 128);
             }
-            ok = mbar_wait(bar_xfull, (uint32_t)it & 1u, ctx, 31);
+            ok = mbar_wait(bar_xfull + 8 * wg, (uint32_t)it & 1u, ctx, 31);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after_sync();
@@ -358,7 +366,7 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
             tmem_st_wait();
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_pready);
+            if (lane == 0) mbar_arrive(bar_pready + 8 * wg);
         }
         // epilogue: accumulators -> global, one row per thread, each warpgroup half of head_dim
         if (ok && n_iter > 0) {

@@ -540,6 +540,11 @@ def run_case(args) -> None:
         else:
             k = build_flash_attention(4, 16, size, size, d, causal=causal)
             work, unit = attention_flops(4, 16, size, size, d, causal), "TFLOP/s"
+    elif name in ("rms_norm_bwd", "layer_norm_bwd"):
+        from pyptx_b200.examples.blackwell.backward import build_layer_norm_bwd, build_rms_norm_bwd, norm_bwd_bytes
+        x, w = inputs.rms_norm_inputs(B, N)
+        k = (build_rms_norm_bwd if name == "rms_norm_bwd" else build_layer_norm_bwd)(B, N)
+        ops, work = (x.cuda(), w.cuda(), torch.randn(B, N, device="cuda")), norm_bwd_bytes(B, N)
     elif name == "rms_norm":
         k, ops, work = build_rms_norm(B, N), tuple(t.cuda() for t in inputs.rms_norm_inputs(B, N)), rms_norm_bytes(B, N)
     elif name == "layer_norm":
@@ -860,16 +865,20 @@ def run_ours(args) -> None:
         def shape_tag(m, n, k):
             return str(m) if m == n == k else f"{m}x{n}x{k}"
 
-        for name in (args.variant, other):
-            for (m, n, k_) in shapes:
+        # Shape by shape, the three implementations back to back with a short pause before each, so
+        # that every figure of a row is taken in the same thermal / power state of the GPU.
+        for (m, n, k_) in shapes:
+            x, y = a[:m, :k_].contiguous(), bt[:n, :k_].contiguous()
+            yt = y.t().contiguous()
+            for name in (args.variant, other):
                 k = builders[name](m, n, k_)
-                x, y = a[:m, :k_].contiguous(), bt[:n, :k_].contiguous()
+                time.sleep(0.3)
                 ms = time_cuda(lambda: k(x, y), 20, 5, torch)
                 extras[f"gemm_{name}_{shape_tag(m, n, k_)}_tflops"] = 2.0 * m * n * k_ / (ms * 1e-3) / 1e12
-        for (m, n, k_) in shapes:
-            x, y = a[:m, :k_].contiguous(), bt[:n, :k_].t().contiguous()
-            ms = time_cuda(lambda: torch.matmul(x, y), 20, 5, torch)
+            time.sleep(0.3)
+            ms = time_cuda(lambda: torch.matmul(x, yt), 20, 5, torch)
             extras[f"cublas_{shape_tag(m, n, k_)}_tflops"] = 2.0 * m * n * k_ / (ms * 1e-3) / 1e12
+            del x, y, yt
         try:
             extras["grouped"] = grouped_table(torch, peaks)
         except Exception as exc:  # noqa: BLE001 - reported in "errors"
@@ -964,7 +973,7 @@ def main() -> None:
     ap.add_argument("--no-extras", action="store_true", help="skip the context table (other kernels, cuBLAS)")
     ap.add_argument("--case", default=None,
                     help="run ONE kernel only: gemm_1sm gemm_2sm grouped attention_d64 attention_d128[_causal][_bwd] "
-                         "rms_norm layer_norm swiglu softmax")
+                         "rms_norm layer_norm swiglu softmax rms_norm_bwd layer_norm_bwd")
     ap.add_argument("--size", type=int, default=8192, help="M=N=K (gemm cases) or sequence length (attention cases)")
     args = ap.parse_args()
     if args.case:

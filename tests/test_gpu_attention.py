@@ -141,6 +141,32 @@ def test_large_scores_rescale_path(causal):
     check_bf16_matmul(o, formulas.attention_ref(q, k, v, causal=causal, sm_scale=1.0))
 
 
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("jump", [12.0, 60.0, 140.0, 400.0])
+def test_late_dominant_key_at_every_chunk_position(d, jump):
+    """Interior K/V tiles are exponentiated against the maximum already in use and accepted only if
+    the row sums stay small.  A key far above everything seen so far, placed in a later tile at each
+    position of a 32-key chunk in turn (positions differ in whether the MUFU unit or the FMA-pipe
+    polynomial, whose argument is clamped, evaluates them), must send the rows to the exact path.
+    ``jump`` is the score gap in natural units: around the 2^8 acceptance bound, far above it, and
+    beyond what fp32 can exponentiate.  For the large gaps the output is that key's V row."""
+    B, H, S = 1, 1, 384
+    g = torch.Generator().manual_seed(17)
+    q = torch.zeros(B, H, S, d)
+    q[..., 0] = 1.0                                  # score of any query against key j is k[j, 0]
+    qb = q.to(torch.bfloat16)
+    v = torch.randn(B, H, S, d, generator=g).to(torch.bfloat16)
+    for pos in range(32):
+        hot = 128 + 32 + pos                         # a key of the second tile
+        k = torch.zeros(B, H, S, d)
+        k[0, 0, hot, 0] = jump
+        kb = k.to(torch.bfloat16)
+        o = _run(qb, kb, v, sm_scale=1.0)
+        check_bf16_matmul(o, formulas.attention_ref(qb, kb, v, sm_scale=1.0))
+        if jump >= 60.0:
+            assert formulas.rel_fro(o[0, 0], v[0, 0, hot].float().expand(S, d)) < 1e-2, pos
+
+
 @pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("d", [64, 128])
 @pytest.mark.parametrize("Sq,Skv", [(1, 1), (5, 40), (100, 100), (129, 300), (200, 513), (257, 257), (383, 1000)])

@@ -170,6 +170,9 @@ extern "C" {
  * the row statistic a backward pass needs (the reference's kernel keeps it in registers only,
  * examples/hopper/experimental/flash_attention_hopper.py:213-256).                              */
 #define PB200_F_RETURN_LSE     (1ull << 6)
+/* attention backward: the two-pass form (dQ in a pass of its own, no atomics, bit-reproducible);
+ * the default forms dQ in the dK/dV pass and accumulates it across key tiles with fp32 atomics */
+#define PB200_F_DETERMINISTIC  (1ull << 7)
 
 /* Launch geometry of a handle, as the reference's Kernel object exposes it
  * (pyptx/kernel.py:402-447: grid, block, cluster, smem). */

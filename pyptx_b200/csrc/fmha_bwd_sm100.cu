@@ -36,6 +36,7 @@
 
 #include <cuda_bf16.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cmath>
 
@@ -62,15 +63,18 @@ struct BwdParams {
     int hd;                            // head dimension of the tensors (multiple of 8, <= HD)
 };
 
-template <int HD>
+template <int HD, bool FUSED>
 struct BwdSmem {
     static constexpr int kStages = HD == 64 ? 3 : 2;
     static constexpr int kTileBytes = kTile * HD * 2;
+    static constexpr int kDsBytes = kTile * 128;                        // dS^T of one warpgroup: 128 keys x 64 queries, bf16
     static constexpr int kOffStat = 0;                                  // two stationary tiles
     static constexpr int kOffRing = 2 * kTileBytes;                     // kStages x two streamed tiles
-    static constexpr int kOffBar = kOffRing + kStages * 2 * kTileBytes;
-    static constexpr int kOffStats = kOffBar + 512;                     // MODE 0: lse2 / delta of the streamed queries
-    static constexpr int kTotal = kOffStats + 2 * 2 * 128 * 4 + 1024;
+    static constexpr int kOffDs = kOffRing + kStages * 2 * kTileBytes;  // fused pass: dS^T of both warpgroups
+    static constexpr int kOffBar = kOffDs + (FUSED ? 2 * kDsBytes : 0);
+    static constexpr int kOffStats = kOffBar + 256;                     // key-stationary passes: lse2 / delta of the streamed queries
+    static constexpr int kStatSets = FUSED ? 1 : 2;                     // buffers per warpgroup
+    static constexpr int kTotal = kOffStats + kStatSets * 2 * 128 * 4 + 1024;
     static_assert(kTotal <= 227 * 1024, "shared memory budget exceeded");
 };
 
@@ -115,20 +119,53 @@ fmha_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* _
     }
 }
 
+// dQ[bh, i, c] = scale * dq_acc[bh, i, c] for i < s_q, c < hd (dq_acc rows are HD_TILE floats, sq_pad rows per head).
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+fmha_bwd_dq_finish_kernel(const float* __restrict__ dq_acc, OutT* __restrict__ dq, int bh, int s_q, int sq_pad,
+                          int hd, int hd_tile, float scale) {
+    const int quads = hd >> 2;                            // hd is a multiple of 8
+    const size_t n = (size_t)bh * s_q * quads;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
+        const int c4 = (int)(idx % quads);
+        const size_t rowi = idx / quads;
+        const int i = (int)(rowi % s_q);
+        const size_t b = rowi / s_q;
+        const float4 v = *reinterpret_cast<const float4*>(dq_acc + (b * sq_pad + i) * hd_tile + 4 * c4);
+        OutT* dst = dq + rowi * hd + 4 * c4;
+        if (sizeof(OutT) == 4) {
+            *reinterpret_cast<float4*>(dst) = make_float4(v.x * scale, v.y * scale, v.z * scale, v.w * scale);
+        } else {
+            *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(v.x * scale, v.y * scale), pack_bf16(v.z * scale, v.w * scale));
+        }
+    }
+}
+
 // MODE 0: stationary = (K, V), streamed = (Q, dO), outputs dV (acc A) and dK (acc B).
 // MODE 1: stationary = (Q, dO), streamed = (K, V), output dQ (acc B).
+// MODE 2: MODE 0 plus dQ in the same pass (five MMAs per tile pair).  dS^T goes to shared memory
+//         instead of TMEM: it is the K-major A operand of dK += dS^T Q and the MN-major B operand of
+//         dQ^T = K^T dS^T (K tile as MN-major A, M = head_dim padded to 128 lanes, N = the
+//         warpgroup's 64 queries), which lands in the warpgroup's own dP columns once dP has been
+//         read.  The warpgroup reads it back (lane = head-dim index, column = query) and adds it
+//         to an fp32 accumulation buffer dq_acc[bh][sq_pad][HD] with red.global.add: coalesced
+//         128-byte rows, no ordering between key tiles, so dQ is not bit-reproducible from run to
+//         run.  A row kernel scales and rounds dq_acc afterwards.
 template <int HD, int MODE, typename OutT>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_constant__ CUtensorMap tmap_s2,
                 const __grid_constant__ CUtensorMap tmap_m1, const __grid_constant__ CUtensorMap tmap_m2,
                 const float* __restrict__ lse2, const float* __restrict__ delta,
-                OutT* __restrict__ out_a, OutT* __restrict__ out_b, BwdParams prm, int* status) {
-    using L = BwdSmem<HD>;
+                OutT* __restrict__ out_a, OutT* __restrict__ out_b, float* __restrict__ dq_acc, BwdParams prm, int* status) {
+    constexpr bool kFused = MODE == 2;
+    constexpr bool kKeyStat = MODE != 1;           // keys stationary, queries streamed
+    using L = BwdSmem<HD, kFused>;
     constexpr int kStages = L::kStages;
     constexpr int kDBlocks = HD / 64;
     constexpr int kHalf = kTile / 2;                                             // streamed rows per warpgroup
     constexpr uint32_t kIdescX = make_idesc_f16(kTile, kHalf, true, 0, 0);      // both operands K-major
     constexpr uint32_t kIdescAcc = make_idesc_f16(kTile, HD, true, 0, 1);       // B operand MN-major
+    constexpr uint32_t kIdescDq = make_idesc_f16(kTile, kHalf, true, 1, 1);     // both operands MN-major
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -141,8 +178,11 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
     const uint32_t bar_xfull = bar_empty + 8 * kStages;   // [2] S and dP of a warpgroup's half tile are in TMEM
     const uint32_t bar_pready = bar_xfull + 16;           // [2] its P and dS are written (4 warps)
     const uint32_t bar_outfull = bar_pready + 16;         // [1] accumulators complete
+    const uint32_t bar_dqfull = bar_outfull + 8;          // [2] fused: dQ^T of a warpgroup's half tile is in TMEM
+    const uint32_t bar_dqfree = bar_dqfull + 16;          // [2] fused: ... and has been read (4 warps)
     float* stats_gen = reinterpret_cast<float*>(gen + L::kOffStats);    // [parity][warpgroup][64 lse2 | 64 delta]
-    const uint32_t s_tmem_slot = bar_outfull + 8;
+    const uint32_t s_ds = base + L::kOffDs;
+    const uint32_t s_tmem_slot = bar_dqfree + 16;
     const uint32_t s_abort = s_tmem_slot + 8;
     volatile uint32_t* tmem_slot_gen = (volatile uint32_t*)(gen + (s_tmem_slot - base));
     volatile int* abort_gen = (volatile int*)(gen + (s_abort - base));
@@ -166,11 +206,11 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
         heavy_rank = rem / heads_here;
         bh = grp * kHeadGroup + rem % heads_here;
     }
-    const int st = MODE == 0 ? heavy_rank : (int)gridDim.x - 1 - heavy_rank;
+    const int st = kKeyStat ? heavy_rank : (int)gridDim.x - 1 - heavy_rank;
     const int st0 = st * kTile;
     // Range of streamed tiles [m_begin, m_end).
     int m_begin = 0, m_end;
-    if (MODE == 0) {
+    if (kKeyStat) {
         m_end = (prm.s_q + kTile - 1) / kTile;
         if (prm.causal) m_begin = min(max(st0 - prm.causal_offset, 0) / kTile, m_end);   // first query that sees key st0
     } else {
@@ -185,7 +225,10 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
         *abort_gen = 0;
         mbar_init(bar_stat, 1);
         for (int s = 0; s < kStages; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
-        for (int w = 0; w < 2; ++w) { mbar_init(bar_xfull + 8 * w, 1); mbar_init(bar_pready + 8 * w, 4); }
+        for (int w = 0; w < 2; ++w) {
+            mbar_init(bar_xfull + 8 * w, 1); mbar_init(bar_pready + 8 * w, 4);
+            mbar_init(bar_dqfull + 8 * w, 1); mbar_init(bar_dqfree + 8 * w, 4);
+        }
         mbar_init(bar_outfull, 1);
         fence_mbarrier_init();
         fence_proxy_async_smem();
@@ -261,6 +304,26 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
                     umma_f16_ts_lohi(acc, a_tmem + (uint32_t)(w * kHalf + k * 8), b + (uint32_t)(k * 128), b_hi,
                                      kIdescAcc, (first && k == 0) ? 0u : 1u);
             };
+            // fused pass: dK += dS^T_w Q_w with dS^T from shared memory (K-major A: one 128-byte row per key)
+            const uint64_t dsk = make_desc_kmajor_sw128(s_ds);
+            const uint64_t dsm = make_smem_desc(s_ds, kTile * 128, 1024, 2);         // the same bytes as MN-major B
+            const uint64_t ktd = make_smem_desc(s_stat, kTile * 128, 1024, 2);       // K tile as MN-major A (M = head_dim)
+            auto issue_dk_ss = [&](int w, int stage, bool first) {
+                const uint32_t a = (uint32_t)dsk + (uint32_t)(w * (L::kDsBytes >> 4));
+                const uint32_t b = b_lo + (uint32_t)(stage * 2) * kTileDesc + (uint32_t)(w * ((kHalf * 128) >> 4));
+#pragma unroll
+                for (int k = 0; k < kHalf / 16; ++k)
+                    umma_f16_ss_lohi(tmem_acc_b, a + (uint32_t)(k * 2), (uint32_t)(dsk >> 32), b + (uint32_t)(k * 128), b_hi,
+                                     kIdescAcc, (first && k == 0) ? 0u : 1u);
+            };
+            // dQ^T_w = K^T dS^T_w: contraction over the 128 keys, 16 per step (2048 bytes in both operands)
+            auto issue_dq = [&](int w) {
+                const uint32_t b = (uint32_t)dsm + (uint32_t)(w * (L::kDsBytes >> 4));
+#pragma unroll
+                for (int k = 0; k < kTile / 16; ++k)
+                    umma_f16_ss_lohi(tmem_x2 + (uint32_t)(w * kHalf), (uint32_t)ktd + (uint32_t)(k * 128), (uint32_t)(ktd >> 32),
+                                     b + (uint32_t)(k * 128), (uint32_t)(dsm >> 32), kIdescDq, k != 0 ? 1u : 0u);
+            };
             int stage = 0; uint32_t phase = 0;
             if (ok) ok = mbar_wait(bar_full, 0, ctx, 22);
             if (ok) {
@@ -277,10 +340,26 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
                 for (int w = 0; w < 2; ++w) {
                     if (!(ok = mbar_wait(bar_pready + 8 * w, (uint32_t)it & 1u, ctx, 23))) break;
                     tc_fence_after_sync();
-                    if (MODE == 0) issue_acc(tmem_acc_a, tmem_x1, 1, w, stage, it == 0 && w == 0);     // dV += P^T dO
-                    issue_acc(tmem_acc_b, tmem_x2, 0, w, stage, it == 0 && w == 0);                    // dK += dS^T Q  /  dQ += dS K
+                    if (kKeyStat) issue_acc(tmem_acc_a, tmem_x1, 1, w, stage, it == 0 && w == 0);     // dV += P^T dO
+                    if (kFused) {
+                        issue_dk_ss(w, stage, it == 0 && w == 0);
+                        issue_dq(w);
+                        umma_commit<1>(bar_dqfull + 8 * w);
+                    } else {
+                        issue_acc(tmem_acc_b, tmem_x2, 0, w, stage, it == 0 && w == 0);                // dK += dS^T Q  /  dQ += dS K
+                    }
                     if (w == 1) umma_commit<1>(bar_empty + 8 * stage);
-                    if (more) { issue_x(w, nstage); umma_commit<1>(bar_xfull + 8 * w); }
+                    if (!kFused && more) { issue_x(w, nstage); umma_commit<1>(bar_xfull + 8 * w); }
+                }
+                if (!ok) break;
+                if (kFused && more) {
+                    // the next dP^T of a half overwrites its dQ^T: wait until the warpgroup has read it
+#pragma unroll
+                    for (int w = 0; w < 2; ++w) {
+                        if (!(ok = mbar_wait(bar_dqfree + 8 * w, (uint32_t)it & 1u, ctx, 25))) break;
+                        tc_fence_after_sync();
+                        issue_x(w, nstage); umma_commit<1>(bar_xfull + 8 * w);
+                    }
                 }
                 stage = nstage; phase = nphase;
             }
@@ -300,7 +379,7 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
         const float* lse2_bh = lse2 + (size_t)bh * prm.sq_pad;
         const float* delta_bh = delta + (size_t)bh * prm.sq_pad;
         float my_lse2 = 0.f, my_delta = 0.f;
-        if (MODE == 1) { my_lse2 = lse2_bh[srow]; my_delta = delta_bh[srow]; }     // srow < sq_pad always
+        if (!kKeyStat) { my_lse2 = lse2_bh[srow]; my_delta = delta_bh[srow]; }     // srow < sq_pad always
         bool ok = true;
         const int wg_tid = (int)threadIdx.x - 128 - wg * 128;      // 0..127 inside the warpgroup
         for (int it = 0; it < n_iter && ok; ++it) {
@@ -308,9 +387,12 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
             // MODE 0: the columns are queries, so every thread needs the same 64 (lse2, delta) pairs.
             // The warpgroup stages them in shared memory (one value per thread, fetched before the
             // wait for the scores; two buffers by iteration parity) and reads them back as broadcasts.
-            float* stats = stats_gen + ((it & 1) * 2 + wg) * 128;
-            if (MODE == 0) {
-                stats[wg_tid] = wg_tid < 64 ? __ldg(lse2_bh + m0 + wg_tid) : __ldg(delta_bh + m0 + wg_tid - 64);
+            // (The fused pass has one buffer: its refill below follows the wait for dQ^T, which the
+            // MMA thread only produces after all four warps have finished their score math.)
+            float* stats = stats_gen + ((kFused ? 0 : (it & 1) * 2) + wg) * 128;
+            if (kKeyStat) {
+                if (!kFused || it == 0)
+                    stats[wg_tid] = wg_tid < 64 ? __ldg(lse2_bh + m0 + wg_tid) : __ldg(delta_bh + m0 + wg_tid - 64);
                 named_barrier_sync(1 + wg, 128);
             }
             ok = mbar_wait(bar_xfull + 8 * wg, (uint32_t)it & 1u, ctx, 31);
@@ -322,7 +404,7 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
             // of the pairing still sees the largest key.
             bool masked = false;
             if (prm.causal) {
-                if (MODE == 0) masked = st0 + q4 * 32 + 31 > m0 + prm.causal_offset;
+                if (kKeyStat) masked = st0 + q4 * 32 + 31 > m0 + prm.causal_offset;
                 else masked = m0 + 63 > st0 + q4 * 32 + prm.causal_offset;
             }
             // All 64 columns of S and dP at once: four TMEM loads in flight, one wait.
@@ -339,7 +421,7 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
 #pragma unroll
             for (int c2 = 0; c2 < 32; ++c2) {
                 float nl0, nl1, nd0, nd1;
-                if (MODE == 0) {
+                if (kKeyStat) {
                     const float2 lv = reinterpret_cast<const float2*>(stats)[c2];
                     const float2 dv = reinterpret_cast<const float2*>(stats + 64)[c2];
                     nl0 = -lv.x; nl1 = -lv.y; nd0 = -dv.x; nd1 = -dv.y;
@@ -352,8 +434,8 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
                 else { p0 = fast_exp2(t0); p1 = fast_exp2(t1); }
                 if (masked) {
                     const int mrow = m0 + 2 * c2;                 // streamed row (query in MODE 0, key in MODE 1)
-                    if (MODE == 0 ? (srow > mrow + prm.causal_offset) : (mrow > srow + prm.causal_offset)) p0 = 0.f;
-                    if (MODE == 0 ? (srow > mrow + 1 + prm.causal_offset) : (mrow + 1 > srow + prm.causal_offset)) p1 = 0.f;
+                    if (kKeyStat ? (srow > mrow + prm.causal_offset) : (mrow > srow + prm.causal_offset)) p0 = 0.f;
+                    if (kKeyStat ? (srow > mrow + 1 + prm.causal_offset) : (mrow + 1 > srow + prm.causal_offset)) p1 = 0.f;
                 }
                 add2v(u0, u1, __uint_as_float(dp[2 * c2]), __uint_as_float(dp[2 * c2 + 1]), nd0, nd1);
                 mul2v(g0, g1, p0, p1, u0, u1);
@@ -361,23 +443,55 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
                 ds[c2] = pack_bf16(g0, g1);
             }
             // P over the head of this warpgroup's own S columns, dS over the head of its dP columns.
-            if (MODE == 0) tmem_st_32x32b_x32(tx1, pp);
-            tmem_st_32x32b_x32(tx2, ds);
+            if (kKeyStat) tmem_st_32x32b_x32(tx1, pp);
+            if (kFused) {
+                // dS^T row of this key: 64 queries = 128 bytes = one row of the SWIZZLE_128B image
+                const uint32_t rowp = s_ds + (uint32_t)(wg * L::kDsBytes) + (uint32_t)row_in_tile * 128u;
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    st_shared_v4(rowp + (((uint32_t)j ^ (uint32_t)(row_in_tile & 7)) << 4), ds[4 * j], ds[4 * j + 1], ds[4 * j + 2], ds[4 * j + 3]);
+                fence_proxy_async_smem();
+            } else {
+                tmem_st_32x32b_x32(tx2, ds);
+            }
             tmem_st_wait();
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_pready + 8 * wg);
+            if (kFused) {
+                const bool more = it + 1 < n_iter;
+                float next_stat = 0.f;
+                if (more) next_stat = wg_tid < 64 ? __ldg(lse2_bh + m0 + kTile + wg_tid) : __ldg(delta_bh + m0 + kTile + wg_tid - 64);
+                ok = mbar_wait(bar_dqfull + 8 * wg, (uint32_t)it & 1u, ctx, 33);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after_sync();
+                uint32_t dq[64];
+                tmem_ld_32x32b_x32(tx2, *reinterpret_cast<uint32_t(*)[32]>(&dq[0]));
+                tmem_ld_32x32b_x32(tx2 + 32u, *reinterpret_cast<uint32_t(*)[32]>(&dq[32]));
+                tmem_ld_wait();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_dqfree + 8 * wg);
+                stats[wg_tid] = next_stat;
+                // lane = head-dim index, column = query: one coalesced 128-byte row segment per column
+                if (row_in_tile < HD) {
+                    float* dst = dq_acc + ((size_t)bh * prm.sq_pad + m0) * HD + row_in_tile;
+#pragma unroll
+                    for (int c = 0; c < 64; ++c) atomicAdd(dst + (size_t)c * HD, __uint_as_float(dq[c]));
+                }
+            }
         }
         // epilogue: accumulators -> global, one row per thread, each warpgroup half of head_dim
         if (ok && n_iter > 0) {
             ok = mbar_wait(bar_outfull, 0, ctx, 41);
             ok = __all_sync(0xffffffffu, ok);
         }
-        const int s_rows = MODE == 0 ? prm.s_kv : prm.s_q;
+        const int s_rows = kKeyStat ? prm.s_kv : prm.s_q;
         const bool row_exists = srow < s_rows;
         const size_t row_off = ((size_t)bh * s_rows + srow) * prm.hd;
 #pragma unroll 1
-        for (int which = (MODE == 0 ? 0 : 1); which < 2; ++which) {
+        for (int which = (kKeyStat ? 0 : 1); which < 2; ++which) {
             OutT* dst = (which == 0 ? out_a : out_b) + row_off;
             const uint32_t acc = (which == 0 ? tmem_acc_a : tmem_acc_b) + lane_off;
             const float mul = which == 0 ? 1.0f : prm.scale;
@@ -434,9 +548,9 @@ int tile_map(CUtensorMap* m, const void* p, int64_t hd, int64_t rows, int64_t bh
 
 template <int HD, int MODE, typename OutT>
 int launch_pass(const CUtensorMap& s1, const CUtensorMap& s2, const CUtensorMap& m1, const CUtensorMap& m2,
-                const float* lse2, const float* delta, void* out_a, void* out_b, const BwdParams& prm, int tiles,
-                cudaStream_t stream, char* err) {
-    using L = BwdSmem<HD>;
+                const float* lse2, const float* delta, void* out_a, void* out_b, float* dq_acc, const BwdParams& prm,
+                int tiles, cudaStream_t stream, char* err) {
+    using L = BwdSmem<HD, MODE == 2>;
     auto kernel = fmha_bwd_kernel<HD, MODE, OutT>;
     static std::atomic<uint64_t> attr_set{0};
     int dev = 0;
@@ -448,7 +562,7 @@ int launch_pass(const CUtensorMap& s1, const CUtensorMap& s2, const CUtensorMap&
     }
     dim3 grid((unsigned)tiles, (unsigned)prm.bh, 1);
     cudaError_t e = launch_with_pdl(kernel, grid, dim3(kBwdThreads), L::kTotal, stream, s1, s2, m1, m2, lse2, delta,
-                                    (OutT*)out_a, (OutT*)out_b, prm, device_status_ptr());
+                                    (OutT*)out_a, (OutT*)out_b, dq_acc, prm, device_status_ptr());
     if (e != cudaSuccess) { set_err(err, "attention backward launch failed (HD=%d mode=%d): %s", HD, MODE, cudaGetErrorString(e)); return PB200_ERR_LAUNCH; }
     return PB200_OK;
 }
@@ -472,14 +586,29 @@ int launch_bwd(const Record& r, cudaStream_t stream, void** p, char* err) {
     if (int rc = tile_map(&tdo, p[5], hd, SQ, BH, err)) return rc;
     float* delta = (float*)p[9];
     float* lse2 = delta + (size_t)BH * prm.sq_pad;
+    float* dq_acc = lse2 + (size_t)BH * prm.sq_pad;          // fused pass only
+    const bool fused = !(r.flags & PB200_F_DETERMINISTIC);
     const int rows = (int)(BH * prm.sq_pad);
+    if (fused) {
+        cudaError_t e = cudaMemsetAsync(dq_acc, 0, (size_t)rows * HD * sizeof(float), stream);
+        if (e != cudaSuccess) { set_err(err, "attention backward: clearing the dQ accumulator failed: %s", cudaGetErrorString(e)); return PB200_ERR_LAUNCH; }
+    }
     fmha_bwd_prep_kernel<<<(rows + 7) / 8, 256, 0, stream>>>((const __nv_bfloat16*)p[3], (const __nv_bfloat16*)p[5],
                                                             (const float*)p[4], delta, lse2, (int)BH, (int)SQ, prm.sq_pad, (int)hd);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { set_err(err, "attention backward (row pass) launch failed: %s", cudaGetErrorString(e)); return PB200_ERR_LAUNCH; }
     const int kv_tiles = (int)((SKV + kTile - 1) / kTile), q_tiles = (int)((SQ + kTile - 1) / kTile);
-    if (int rc = launch_pass<HD, 0, OutT>(tk, tv, tq, tdo, lse2, delta, p[8], p[7], prm, kv_tiles, stream, err)) return rc;   // dV, dK
-    return launch_pass<HD, 1, OutT>(tq, tdo, tk, tv, lse2, delta, nullptr, p[6], prm, q_tiles, stream, err);                 // dQ
+    if (fused) {
+        if (int rc = launch_pass<HD, 2, OutT>(tk, tv, tq, tdo, lse2, delta, p[8], p[7], dq_acc, prm, kv_tiles, stream, err)) return rc;
+        const size_t quads = (size_t)BH * SQ * (hd / 4);
+        const unsigned blocks = (unsigned)std::min<size_t>((quads + 255) / 256, 148 * 16);
+        fmha_bwd_dq_finish_kernel<OutT><<<blocks, 256, 0, stream>>>(dq_acc, (OutT*)p[6], (int)BH, (int)SQ, prm.sq_pad, (int)hd, HD, prm.scale);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) { set_err(err, "attention backward (dQ row pass) launch failed: %s", cudaGetErrorString(e)); return PB200_ERR_LAUNCH; }
+        return PB200_OK;
+    }
+    if (int rc = launch_pass<HD, 0, OutT>(tk, tv, tq, tdo, lse2, delta, p[8], p[7], nullptr, prm, kv_tiles, stream, err)) return rc;   // dV, dK
+    return launch_pass<HD, 1, OutT>(tq, tdo, tk, tv, lse2, delta, nullptr, p[6], nullptr, prm, q_tiles, stream, err);                 // dQ
 }
 
 }  // namespace
@@ -500,9 +629,13 @@ int plan_attention_bwd(Record& r, char* err) {
     g.grid[0] = (uint32_t)((SKV + kTile - 1) / kTile); g.grid[1] = (uint32_t)BH; g.grid[2] = 1;
     g.block[0] = kBwdThreads; g.block[1] = g.block[2] = 1;
     g.cluster[0] = g.cluster[1] = g.cluster[2] = 1;
-    g.smem_bytes = HD <= 64 ? BwdSmem<64>::kTotal : BwdSmem<128>::kTotal;
+    const bool fused = !(r.flags & PB200_F_DETERMINISTIC);
+    g.smem_bytes = HD <= 64 ? (fused ? BwdSmem<64, true>::kTotal : BwdSmem<64, false>::kTotal)
+                            : (fused ? BwdSmem<128, true>::kTotal : BwdSmem<128, false>::kTotal);
     g.n_inputs = 6; g.n_outputs = 3;
-    g.scratch_bytes = (uint64_t)(2 * BH * sq_pad * sizeof(float));
+    // delta and lse * log2(e) per padded query; the fused pass adds the fp32 dQ accumulator (rows of the tile's head_dim)
+    g.scratch_bytes = (uint64_t)(2 * BH * sq_pad * sizeof(float)) +
+                      (fused ? (uint64_t)(BH * sq_pad * (HD <= 64 ? 64 : 128) * sizeof(float)) : 0);
     return PB200_OK;
 }
 

@@ -13,7 +13,8 @@ from __future__ import annotations
 
 import math
 
-from ..._ids import F_CAUSAL, F_K_TRANSPOSED, F_OUT_BF16, F_RETURN_LSE, K_FLASH_ATTN, K_FLASH_ATTN_BWD
+from ..._ids import (F_CAUSAL, F_DETERMINISTIC, F_K_TRANSPOSED, F_OUT_BF16, F_RETURN_LSE, K_FLASH_ATTN,
+                      K_FLASH_ATTN_BWD)
 from ...kernel import NativeKernel
 from ...specs import Layout, Tile
 from ...types import PtxType, bf16, f32
@@ -65,7 +66,8 @@ def build_flash_attention(batch: int, heads: int, seq_q: int, seq_kv: int | None
 
 def build_flash_attention_bwd(batch: int, heads: int, seq_q: int, seq_kv: int | None = None,
                               head_dim: int = 64, *, causal: bool = False, sm_scale: float | None = None,
-                              out_dtype: PtxType = bf16, arch: str = "sm_100a") -> NativeKernel:
+                              out_dtype: PtxType = bf16, deterministic: bool = False,
+                              arch: str = "sm_100a") -> NativeKernel:
     """Kernel ``k(Q, K, V, O, lse, dO) -> (dQ, dK, dV)``: the backward half of
     ``build_flash_attention(..., return_lse=True)`` (same ``causal`` / ``sm_scale``).
 
@@ -73,8 +75,11 @@ def build_flash_attention_bwd(batch: int, heads: int, seq_q: int, seq_kv: int | 
     forward's second output (the argument order is the one ``differentiable_kernel`` uses: saved
     inputs, saved outputs, incoming gradient); the gradients come back as ``out_dtype`` (bf16 or f32).  The reference
     has the autograd hook for such a pair (pyptx/torch_support.py:446-519) but no backward kernel.
-    P and dS are recomputed from ``lse`` tile by tile: one pass over key tiles produces dK and dV,
-    one pass over query tiles produces dQ, so nothing is accumulated with atomics.
+    P and dS are recomputed from ``lse`` tile by tile.  By default one pass over key tiles produces
+    dK, dV and each tile pair's share of dQ, which is added into an fp32 buffer with atomics (five
+    products per tile pair; dQ may differ in the last bits from run to run).  ``deterministic=True``
+    takes dQ from a second pass over query tiles instead (seven products, no atomics,
+    bit-reproducible).
     """
     assert arch.startswith("sm_100"), "Blackwell attention is only implemented for sm_100*"
     seq_kv = seq_q if seq_kv is None else seq_kv
@@ -82,7 +87,8 @@ def build_flash_attention_bwd(batch: int, heads: int, seq_q: int, seq_kv: int | 
     assert batch >= 1 and heads >= 1 and batch * heads <= 65535, "batch*heads must be in [1, 65535]"
     assert out_dtype in (f32, bf16), f"out_dtype must be f32 or bf16, got {out_dtype}"
     scale = 1.0 / math.sqrt(head_dim) if sm_scale is None else float(sm_scale)
-    flags = (F_CAUSAL if causal else 0) | (F_OUT_BF16 if out_dtype == bf16 else 0)
+    flags = (F_CAUSAL if causal else 0) | (F_OUT_BF16 if out_dtype == bf16 else 0) | \
+            (F_DETERMINISTIC if deterministic else 0)
     q_tile = Tile(batch, heads, seq_q, head_dim, bf16, Layout.TMA_128B, tma_box=(BLOCK_M, 64))
     kv_tile = Tile(batch, heads, seq_kv, head_dim, bf16, Layout.TMA_128B, tma_box=(BLOCK_N, 64))
     return NativeKernel(
@@ -93,13 +99,14 @@ def build_flash_attention_bwd(batch: int, heads: int, seq_q: int, seq_kv: int | 
                    Tile(batch, heads, seq_kv, head_dim, out_dtype, Layout.ROW),
                    Tile(batch, heads, seq_kv, head_dim, out_dtype, Layout.ROW)),
         fparams=(scale,), flags=flags, arch=arch,
-        meta={"causal": causal, "sm_scale": scale, "block_m": BLOCK_M, "block_n": BLOCK_N},
+        meta={"causal": causal, "sm_scale": scale, "block_m": BLOCK_M, "block_n": BLOCK_N,
+              "deterministic": deterministic},
     )
 
 
 def build_differentiable_flash_attention(batch: int, heads: int, seq_q: int, seq_kv: int | None = None,
                                          head_dim: int = 64, *, causal: bool = False,
-                                         sm_scale: float | None = None):
+                                         sm_scale: float | None = None, deterministic: bool = False):
     """``attn(Q, K, V) -> O`` (bf16) that takes part in autograd: the forward kernel with its
     log-sum-exp output, and the backward kernel, joined by ``differentiable_kernel``
     (the reference's hook, pyptx/torch_support.py:446-519)."""
@@ -108,7 +115,7 @@ def build_differentiable_flash_attention(batch: int, heads: int, seq_q: int, seq
     fwd = build_flash_attention(batch, heads, seq_q, seq_kv, head_dim, causal=causal, sm_scale=sm_scale,
                                 out_dtype=bf16, return_lse=True)
     bwd = build_flash_attention_bwd(batch, heads, seq_q, seq_kv, head_dim, causal=causal, sm_scale=sm_scale,
-                                    out_dtype=bf16)
+                                    out_dtype=bf16, deterministic=deterministic)
     return differentiable_kernel(fwd, bwd, save_outputs=(0, 1), visible_outputs=(0,))
 
 

@@ -22,11 +22,12 @@ def _inputs(B, H, Sq, Skv, d, seed=11):
     return q.view(B, H, Sq, d), k.view(B, H, Skv, d), v.view(B, H, Skv, d), do
 
 
-def _run(q, k, v, do, *, causal, out_dtype=f32, sm_scale=None):
+def _run(q, k, v, do, *, causal, out_dtype=f32, sm_scale=None, deterministic=False):
     B, H, Sq, d = q.shape
     Skv = k.shape[2]
     fwd = build_flash_attention(B, H, Sq, Skv, d, causal=causal, sm_scale=sm_scale, out_dtype=bf16, return_lse=True)
-    bwd = build_flash_attention_bwd(B, H, Sq, Skv, d, causal=causal, sm_scale=sm_scale, out_dtype=out_dtype)
+    bwd = build_flash_attention_bwd(B, H, Sq, Skv, d, causal=causal, sm_scale=sm_scale, out_dtype=out_dtype,
+                                    deterministic=deterministic)
     qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
     o, lse = fwd(qc, kc, vc)
     dq, dk, dv = bwd(qc, kc, vc, o, lse, do.cuda())
@@ -44,40 +45,49 @@ def _check(got, ref, tol=TOL):
         assert err < tol, f"{name}: rel_fro {err:.3e}"
 
 
+DETERMINISTIC = pytest.mark.parametrize("deterministic", [False, True], ids=["fused", "two_pass"])
+
+
+@DETERMINISTIC
 @pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("d", [64, 128])
 @pytest.mark.parametrize("B,H,Sq,Skv", [(1, 1, 128, 128), (2, 3, 256, 256), (1, 2, 384, 384), (2, 2, 512, 1024),
                                         (1, 4, 1024, 1024), (1, 1, 128, 640)])
-def test_batched(B, H, Sq, Skv, d, causal):
+def test_batched(B, H, Sq, Skv, d, causal, deterministic):
     q, k, v, do = _inputs(B, H, Sq, Skv, d)
-    _check(_run(q, k, v, do, causal=causal), formulas.attention_bwd_ref(q, k, v, do, causal=causal))
+    _check(_run(q, k, v, do, causal=causal, deterministic=deterministic),
+           formulas.attention_bwd_ref(q, k, v, do, causal=causal))
 
 
+@DETERMINISTIC
 @pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("d", [64, 128])
 @pytest.mark.parametrize("Sq,Skv", [(1, 1), (5, 40), (100, 100), (129, 300), (200, 513), (257, 257), (383, 1000)])
-def test_ragged_sequence_lengths(Sq, Skv, d, causal):
+def test_ragged_sequence_lengths(Sq, Skv, d, causal, deterministic):
     """Lengths that are not multiples of the 128-wide tiles: zero-filled partial tiles; padding
     queries carry lse = +inf (P = 0), padding keys multiply zero rows of K and V."""
     q, k, v, do = _inputs(1, 3, Sq, Skv, d)
-    _check(_run(q, k, v, do, causal=causal), formulas.attention_bwd_ref(q, k, v, do, causal=causal))
+    _check(_run(q, k, v, do, causal=causal, deterministic=deterministic), formulas.attention_bwd_ref(q, k, v, do, causal=causal))
 
 
+@DETERMINISTIC
 @pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("d", [8, 32, 72, 120])
-def test_head_dims_narrower_than_the_tile(d, causal):
+def test_head_dims_narrower_than_the_tile(d, causal, deterministic):
     q, k, v, do = _inputs(2, 2, 200, 328, d)
-    _check(_run(q, k, v, do, causal=causal), formulas.attention_bwd_ref(q, k, v, do, causal=causal))
+    _check(_run(q, k, v, do, causal=causal, deterministic=deterministic), formulas.attention_bwd_ref(q, k, v, do, causal=causal))
 
 
-def test_bf16_gradients_and_scale():
+@DETERMINISTIC
+def test_bf16_gradients_and_scale(deterministic):
     q, k, v, do = _inputs(2, 2, 256, 256, 128)
-    got = _run(q, k, v, do, causal=True, out_dtype=bf16, sm_scale=0.05)
+    got = _run(q, k, v, do, causal=True, out_dtype=bf16, sm_scale=0.05, deterministic=deterministic)
     assert all(g.dtype == torch.bfloat16 for g in got)
     _check(got, formulas.attention_bwd_ref(q, k, v, do, causal=True, sm_scale=0.05))
 
 
-def test_one_hot_attention_gradients():
+@DETERMINISTIC
+def test_one_hot_attention_gradients(deterministic):
     """Sharp scores (each query attends to one key): dV is a permutation of dO and dQ, dK vanish
     up to the softmax's saturation, which pins the pairing of queries and keys in both passes."""
     B, H, S, d = 1, 1, 256, 64
@@ -88,7 +98,7 @@ def test_one_hot_attention_gradients():
     q = (k.float()[:, :, perm] * 200.0).to(torch.bfloat16)
     v = torch.randn(B, H, S, d, generator=g).to(torch.bfloat16)
     do = torch.randn(B, H, S, d, generator=g).to(torch.bfloat16)
-    dq, dk, dv = _run(q, k, v, do, causal=False, sm_scale=1.0)
+    dq, dk, dv = _run(q, k, v, do, causal=False, sm_scale=1.0, deterministic=deterministic)
     ref = formulas.attention_bwd_ref(q, k, v, do, sm_scale=1.0)
     assert formulas.rel_fro(dv, ref[2]) < TOL
     inv = torch.empty_like(perm)
@@ -113,18 +123,32 @@ def test_differentiable_attention_through_autograd():
         assert formulas.rel_fro(t.grad.float().cpu(), r) < TOL, name
 
 
+@DETERMINISTIC
 @pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("d", [64, 128])
-def test_benchmark_configuration(d, causal):
+def test_benchmark_configuration(d, causal, deterministic):
     """B=4, H=16, S=4096 on all 64 heads; float64 autograd on a sample of them."""
     B, H, S = 4, 16, 4096
     q, k, v, do = _inputs(B, H, S, S, d)
-    dq, dk, dv = _run(q, k, v, do, causal=causal, out_dtype=bf16)
+    dq, dk, dv = _run(q, k, v, do, causal=causal, out_dtype=bf16, deterministic=deterministic)
     for t in (dq, dk, dv):
         assert torch.isfinite(t.float()).all()
     for b, h in [(0, 0), (3, 15)]:
         ref = formulas.attention_bwd_ref(q[b, h], k[b, h], v[b, h], do[b, h], causal=causal)
         _check((dq[b, h], dk[b, h], dv[b, h]), ref)
+
+
+def test_two_pass_form_is_bit_reproducible_and_fused_dk_dv_too():
+    """The two-pass form uses no atomics: two runs agree bit for bit.  In the fused form only dQ is
+    accumulated with atomics; dK and dV come from the same MMAs in the same order."""
+    q, k, v, do = _inputs(2, 2, 640, 640, 128)
+    a = _run(q, k, v, do, causal=True, deterministic=True)
+    b = _run(q, k, v, do, causal=True, deterministic=True)
+    assert all(torch.equal(x, y) for x, y in zip(a, b))
+    c = _run(q, k, v, do, causal=True)
+    d = _run(q, k, v, do, causal=True)
+    assert torch.equal(c[1], d[1]) and torch.equal(c[2], d[2])
+    assert formulas.rel_fro(c[0], a[0]) < 1e-3
 
 
 def test_no_device_wait_gave_up():

@@ -406,6 +406,10 @@ def attention_table(torch) -> dict:
             flb = attention_bwd_flops(4, 16, 4096, 4096, d, causal)
             ms = time_cuda(lambda: bwd(q, kk, v, o, lse, d_o), 10, 3, torch)
             out[tag + "_bwd_tflops"] = flb / (ms * 1e-3) / 1e12
+            bwd2 = build_flash_attention_bwd(4, 16, 4096, 4096, d, causal=causal, deterministic=True)
+            ms = time_cuda(lambda: bwd2(q, kk, v, o, lse, d_o), 10, 3, torch)
+            out[tag + "_bwd_two_pass_tflops"] = flb / (ms * 1e-3) / 1e12
+            del bwd2
             qg, kg, vg = (t.detach().clone().requires_grad_() for t in (q, kk, v))
             og = F.scaled_dot_product_attention(qg, kg, vg, is_causal=causal)
             ms = time_cuda(lambda: torch.autograd.grad(og, (qg, kg, vg), d_o, retain_graph=True), 10, 3, torch)

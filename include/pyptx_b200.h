@@ -149,7 +149,7 @@ extern "C" {
  * reference has no backward kernel.  Row statistics as its forward keeps them
  * (examples/hopper/experimental/flash_attention_hopper.py:205-256), here read from lse.
  *   dims = {batch*heads, S_q, S_kv, head_dim}   fparams = {sm_scale (0 -> 1/sqrt(head_dim))}
- *   flags: PB200_F_CAUSAL, PB200_F_OUT_BF16 (dtype of dQ, dK, dV; default f32)
+ *   flags: PB200_F_CAUSAL, PB200_F_OUT_BF16 (dtype of dQ, dK, dV; default f32), PB200_F_DETERMINISTIC
  *   buffers: Q[BH,S_q,d], K[BH,S_kv,d], V[BH,S_kv,d], O[BH,S_q,d] bf16, lse[BH,S_q] f32, dO[BH,S_q,d] bf16
  *            -> dQ[BH,S_q,d], dK[BH,S_kv,d], dV[BH,S_kv,d], then scratch (geometry.scratch_bytes)   */
 #define PB200_K_FLASH_ATTN_BWD 16

@@ -9,15 +9,17 @@
 // forward here: bf16 operands, fp32 accumulation, P and dS rounded to bf16 before they become
 // MMA operands.
 //
-// Two passes of ONE kernel template, so that no gradient needs atomics or a second accumulation
-// buffer and the result is deterministic:
+// ONE kernel template in three modes.  The default is the fused pass (MODE 2): five MMAs per tile
+// pair, dQ summed over key tiles with fp32 reductions into a scratch buffer (not bit-reproducible).
+// With PB200_F_DETERMINISTIC two passes run instead (MODE 0, then MODE 1), so that no gradient needs
+// atomics and the result is bit-reproducible, at seven MMAs per tile pair (S and dP formed twice):
 //   MODE 0 (dK, dV): a CTA owns 128 keys (K, V tiles stay in shared memory) and streams the query
 //          tiles (Q, dO).  Scores are computed transposed, S^T = K Q^T and dP^T = V dO^T, so that
 //          keys are TMEM lanes and P^T / dS^T can be fed back as the TMEM A operand of
 //          dV += P^T dO and dK += dS^T Q (Q and dO tiles consumed as MN-major B operands).
 //   MODE 1 (dQ):     a CTA owns 128 queries (Q, dO stay) and streams K, V: S = Q K^T, dP = dO V^T,
 //          dS as the TMEM A operand of dQ += dS K.
-// Seven MMAs per tile pair instead of five (S and dP are formed in both passes).
+//   MODE 2 (dK, dV, dQ): MODE 0 with dQ^T = K^T dS^T formed per tile pair; see the kernel's comment.
 //   warp 0      TMA producer (stationary pair once, streamed pairs through a ring)
 //   warp 1      MMA issuer (single thread)
 //   warps 4-7   score math for streamed columns 0-63    (one TMEM lane per thread)
@@ -340,11 +342,15 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
                 for (int w = 0; w < 2; ++w) {
                     if (!(ok = mbar_wait(bar_pready + 8 * w, (uint32_t)it & 1u, ctx, 23))) break;
                     tc_fence_after_sync();
+                    // head_dim 128: dQ^T first, so that the warpgroup reads it while dV and dK run and the
+                    // next dP^T of this half (which overwrites it) is not held up (+2.5 %); at head_dim 64
+                    // the MMAs are short and the order dV, dK, dQ^T measured 6 % faster.
+                    constexpr bool kDqFirst = HD == 128;
+                    if (kFused && kDqFirst) { issue_dq(w); umma_commit<1>(bar_dqfull + 8 * w); }
                     if (kKeyStat) issue_acc(tmem_acc_a, tmem_x1, 1, w, stage, it == 0 && w == 0);     // dV += P^T dO
                     if (kFused) {
                         issue_dk_ss(w, stage, it == 0 && w == 0);
-                        issue_dq(w);
-                        umma_commit<1>(bar_dqfull + 8 * w);
+                        if (!kDqFirst) { issue_dq(w); umma_commit<1>(bar_dqfull + 8 * w); }
                     } else {
                         issue_acc(tmem_acc_b, tmem_x2, 0, w, stage, it == 0 && w == 0);                // dK += dS^T Q  /  dQ += dS K
                     }

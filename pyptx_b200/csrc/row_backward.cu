@@ -184,28 +184,43 @@ norm_bwd_kernel(const float4* __restrict__ x, const float4* __restrict__ w, cons
 // per row) and, next to the row it works on, the NEXT row's x and dy, whose loads are issued before
 // the reductions of the current row.  HBM then always has a row in flight per SM while the
 // barrier-separated phases of the current one run.  (Measured alternatives that were not faster:
-// column sums in registers with w in shared memory, and LayerNorm's four row sums in one shifted
-// pass with a single barrier.)
+// w in shared memory to make room for both column sums in registers, and LayerNorm's four row sums
+// in one shifted pass with a single barrier.)
+#ifndef PB200_RMS_ACC_REGS
+#define PB200_RMS_ACC_REGS 0      // RMSNorm's single column sum in registers measured 3 % slower than in shared memory
+#endif
+#ifndef PB200_LN_BOTH_REGS
+#define PB200_LN_BOTH_REGS 0       // both LayerNorm sums in registers spill (64-register limit at 1024 threads): 45 % slower
+#endif
+// does the streaming kernel keep dw's column sum in shared memory?
+constexpr bool stream_acc_in_smem(int mode) { return mode == 0 ? !PB200_RMS_ACC_REGS : !PB200_LN_BOTH_REGS; }
 template <int VPT, int MODE>
 __global__ void __launch_bounds__(1024, 1)
 norm_bwd_stream_kernel(const float4* __restrict__ x, const float4* __restrict__ w, const float4* __restrict__ dy,
                        float4* __restrict__ dx, float4* __restrict__ partial_w, float4* __restrict__ partial_b,
                        int rows, int n4, float inv_n, float eps) {
     constexpr int THREADS = 1024;
+    constexpr bool kAccWInRegs = MODE == 0 ? PB200_RMS_ACC_REGS : PB200_LN_BOTH_REGS;
+    constexpr bool kBoth = MODE == 1 && PB200_LN_BOTH_REGS;
     __shared__ float2 red[3][kWarp];
-    extern __shared__ float4 acc_smem[];              // [MODE + 1][THREADS * VPT]
+    extern __shared__ float4 acc_smem[];              // LayerNorm: [THREADS * VPT] column sums of dy * xhat
     float4* acc_w = acc_smem;
-    float4* acc_b = acc_smem + THREADS * VPT;
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
     ptx::pdl_launch_dependents();
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
         const int idx = threadIdx.x + i * THREADS;
-        acc_w[idx] = zero4;
-        if (MODE == 1) acc_b[idx] = zero4;
+        if (!kAccWInRegs) acc_w[idx] = zero4;
     }
     ptx::pdl_wait();
     float4 wv[VPT], xv[VPT], gv[VPT];
+    // LayerNorm keeps db's column sum in registers and dw's in shared memory: both in registers do not
+    // fit in 64, and each sum kept in shared memory costs 64 KiB of read-modify-write per row in the
+    // unit (L1 / shared memory) that also moves the rows: with both there the kernel ran at 0.76 of
+    // the copy bandwidth, with one 0.83.
+    float4 ab[VPT], aw2[VPT];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) { ab[i] = zero4; aw2[i] = zero4; }
     int row = blockIdx.x;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
@@ -265,14 +280,16 @@ norm_bwd_stream_kernel(const float4* __restrict__ x, const float4* __restrict__ 
                 o.z = r * (wv[i].z * gv[i].z - c2 - hz * c1);
                 o.w = r * (wv[i].w * gv[i].w - c2 - hw * c1);
                 st_stream4(dr + idx, o);
-                float4 aw = acc_w[idx];
-                aw.x += gv[i].x * hx; aw.y += gv[i].y * hy; aw.z += gv[i].z * hz; aw.w += gv[i].w * hw;
-                acc_w[idx] = aw;
-                if (MODE == 1) {
-                    float4 ab = acc_b[idx];
-                    ab.x += gv[i].x; ab.y += gv[i].y; ab.z += gv[i].z; ab.w += gv[i].w;
-                    acc_b[idx] = ab;
+                if (kBoth) {
+                    aw2[i].x += gv[i].x * hx; aw2[i].y += gv[i].y * hy; aw2[i].z += gv[i].z * hz; aw2[i].w += gv[i].w * hw;
+                } else if (kAccWInRegs) {
+                    ab[i].x += gv[i].x * hx; ab[i].y += gv[i].y * hy; ab[i].z += gv[i].z * hz; ab[i].w += gv[i].w * hw;
+                } else {
+                    float4 aw = acc_w[idx];
+                    aw.x += gv[i].x * hx; aw.y += gv[i].y * hy; aw.z += gv[i].z * hz; aw.w += gv[i].w * hw;
+                    acc_w[idx] = aw;
                 }
+                if (MODE == 1) { ab[i].x += gv[i].x; ab[i].y += gv[i].y; ab[i].z += gv[i].z; ab[i].w += gv[i].w; }
             }
         }
 #pragma unroll
@@ -283,8 +300,8 @@ norm_bwd_stream_kernel(const float4* __restrict__ x, const float4* __restrict__ 
     for (int i = 0; i < VPT; ++i) {
         const int idx = threadIdx.x + i * THREADS;
         if (idx < n4) {
-            partial_w[(size_t)blockIdx.x * n4 + idx] = acc_w[idx];
-            if (MODE == 1) partial_b[(size_t)blockIdx.x * n4 + idx] = acc_b[idx];
+            partial_w[(size_t)blockIdx.x * n4 + idx] = kBoth ? aw2[i] : kAccWInRegs ? ab[i] : acc_w[idx];
+            if (MODE == 1) partial_b[(size_t)blockIdx.x * n4 + idx] = ab[i];
         }
     }
 }
@@ -364,7 +381,10 @@ bool pick_bwd_config(int64_t n4, BwdConfig& c) {
         if ((int64_t)t.threads * t.vpt >= n4) { c = t; return true; }
     return false;
 }
-size_t bwd_acc_bytes(const BwdConfig& c, int mode) { return (size_t)(mode + 1) * c.threads * c.vpt * sizeof(float4); }
+size_t bwd_acc_bytes(const BwdConfig& c, int mode) {
+    if (c.threads == 1024) return stream_acc_in_smem(mode) ? (size_t)c.threads * c.vpt * sizeof(float4) : 0;   // streaming kernel
+    return (size_t)(mode + 1) * c.threads * c.vpt * sizeof(float4);
+}
 
 // CTAs of the persistent grid: two per SM where two fit (threads and the shared-memory column
 // sums), else one, so that no CTA waits for a slot.
@@ -398,7 +418,7 @@ void launch_norm(int mode, int parts, cudaStream_t s, const float4* x, const flo
 template <int VPT>
 void launch_norm_stream(int mode, int parts, cudaStream_t s, const float4* x, const float4* w, const float4* dy, float4* dx,
                         float4* pw, float4* pb, int rows, int n4, float inv_n, float eps) {
-    const size_t smem = (size_t)(mode + 1) * 1024 * VPT * sizeof(float4);
+    const size_t smem = stream_acc_in_smem(mode) ? (size_t)1024 * VPT * sizeof(float4) : 0;
     if (smem > 48 * 1024) {
         static std::atomic<uint64_t> done[2];
         int dev = 0;

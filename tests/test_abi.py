@@ -215,3 +215,22 @@ def test_registry_is_safe_under_concurrent_use(lib):
         assert lib.pb200_has_handle(h)
         lib.pb200_destroy(h)
     assert lib.pb200_registry_size() == before
+
+
+def test_attention_backward_geometry(lib):
+    """Scratch of the attention backward handle: delta and lse*log2(e) per padded query, plus (fused
+    form only) the fp32 dQ accumulator with rows of the tile's head dimension."""
+    BH, SQ, SKV = 6, 300, 520
+    sq_pad = 384
+    for hd, tile in ((64, 64), (40, 64), (128, 128), (72, 128)):
+        fused = _native.create_handle(_ids.K_FLASH_ATTN_BWD, (BH, SQ, SKV, hd), (0.0,), _ids.F_CAUSAL)
+        two_pass = _native.create_handle(_ids.K_FLASH_ATTN_BWD, (BH, SQ, SKV, hd), (0.0,),
+                                         _ids.F_CAUSAL | _ids.F_DETERMINISTIC)
+        gf, gt = _native.geometry_of(fused), _native.geometry_of(two_pass)
+        assert (gf.n_inputs, gf.n_outputs) == (6, 3) == (gt.n_inputs, gt.n_outputs)
+        assert gt.scratch_bytes == 2 * BH * sq_pad * 4
+        assert gf.scratch_bytes == gt.scratch_bytes + BH * sq_pad * tile * 4
+        assert tuple(gf.grid) == ((SKV + 127) // 128, BH, 1) and tuple(gf.block) == (384, 1, 1)
+        assert gf.smem_bytes <= 227 * 1024 and gt.smem_bytes <= 227 * 1024
+        lib.pb200_destroy(fused)
+        lib.pb200_destroy(two_pass)

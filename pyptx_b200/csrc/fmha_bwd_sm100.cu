@@ -488,6 +488,10 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
                 }
             }
         }
+        // A warp that gave up leaves its share of the warpgroup's barrier behind, so that the others,
+        // which may already wait there for the next tile, reach their own next bounded wait and see
+        // the abort flag instead of waiting for this warp for ever.
+        if (kKeyStat && !ok) named_barrier_arrive(1 + wg, 128);
         // epilogue: accumulators -> global, one row per thread, each warpgroup half of head_dim
         if (ok && n_iter > 0) {
             ok = mbar_wait(bar_outfull, 0, ctx, 41);

@@ -102,6 +102,12 @@ __device__ __forceinline__ void reg_dealloc() {
 __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
     asm volatile("bar.sync %0, %1;" :: "r"(id), "r"(threads) : "memory");
 }
+// Counts the calling warp towards the barrier without waiting: a warp that leaves a loop early
+// (a bounded wait gave up) uses it so that the warps it shares the barrier with cannot wait for it
+// for ever.
+__device__ __forceinline__ void named_barrier_arrive(int id, int threads) {
+    asm volatile("bar.arrive %0, %1;" :: "r"(id), "r"(threads) : "memory");
+}
 
 // ---------------------------------------------------------------------------
 // Programmatic dependent launch.  A kernel launched with the "programmatic stream serialization"

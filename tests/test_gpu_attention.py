@@ -129,6 +129,15 @@ def test_batched(B, H, Sq, Skv, d, causal):
     check_bf16_matmul(o, formulas.attention_ref(q, k, v, causal=causal))
 
 
+@pytest.mark.parametrize("d", [64, 128])
+def test_causal_head_groups_with_a_partial_last_group(d):
+    """Causal launches deal query blocks out heaviest-first across groups of 16 heads; 21 heads
+    leave a last group of 5, and 600 rows a partial last query block."""
+    q, k, v = _inputs(3, 7, 600, 600, d)
+    o = _run(q, k, v, causal=True)
+    check_bf16_matmul(o, formulas.attention_ref(q, k, v, causal=True))
+
+
 @pytest.mark.parametrize("causal", [False, True])
 def test_large_scores_rescale_path(causal):
     """Unnormalised Q.K with growing magnitude along the keys forces the running maximum to move

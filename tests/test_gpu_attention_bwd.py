@@ -79,6 +79,16 @@ def test_head_dims_narrower_than_the_tile(d, causal, deterministic):
 
 
 @DETERMINISTIC
+@pytest.mark.parametrize("d", [64, 128])
+def test_causal_head_groups_with_a_partial_last_group(d, deterministic):
+    """Causal launches deal the stationary tiles out heaviest-first across groups of 16 heads; 21
+    heads leave a last group of 5, and 600 rows a partial last tile."""
+    q, k, v, do = _inputs(3, 7, 600, 600, d)
+    _check(_run(q, k, v, do, causal=True, deterministic=deterministic),
+           formulas.attention_bwd_ref(q, k, v, do, causal=True))
+
+
+@DETERMINISTIC
 def test_bf16_gradients_and_scale(deterministic):
     q, k, v, do = _inputs(2, 2, 256, 256, 128)
     got = _run(q, k, v, do, causal=True, out_dtype=bf16, sm_scale=0.05, deterministic=deterministic)

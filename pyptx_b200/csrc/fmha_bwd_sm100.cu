@@ -85,6 +85,28 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// 32 accumulator columns of one row -> global (the first cols_here of them exist), scaled.
+template <typename OutT>
+__device__ __forceinline__ void store_row_chunk(OutT* dst, const uint32_t (&o)[32], int cols_here, float mul) {
+    if (sizeof(OutT) == 4) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (4 * i < cols_here)
+                reinterpret_cast<float4*>(dst)[i] =
+                    make_float4(__uint_as_float(o[4 * i]) * mul, __uint_as_float(o[4 * i + 1]) * mul,
+                                __uint_as_float(o[4 * i + 2]) * mul, __uint_as_float(o[4 * i + 3]) * mul);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            if (8 * i < cols_here)
+                reinterpret_cast<uint4*>(dst)[i] =
+                    make_uint4(pack_bf16(__uint_as_float(o[8 * i]) * mul, __uint_as_float(o[8 * i + 1]) * mul),
+                               pack_bf16(__uint_as_float(o[8 * i + 2]) * mul, __uint_as_float(o[8 * i + 3]) * mul),
+                               pack_bf16(__uint_as_float(o[8 * i + 4]) * mul, __uint_as_float(o[8 * i + 5]) * mul),
+                               pack_bf16(__uint_as_float(o[8 * i + 6]) * mul, __uint_as_float(o[8 * i + 7]) * mul));
+    }
+}
+
 // delta[bh, i] = sum_c O[bh, i, c] * dO[bh, i, c];  lse2[bh, i] = lse[bh, i] * log2(e).
 // One warp per row; rows in [s_q, sq_pad) are written as (0, +inf).
 __global__ void __launch_bounds__(256)
@@ -160,6 +182,10 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
                 const float* __restrict__ lse2, const float* __restrict__ delta,
                 OutT* __restrict__ out_a, OutT* __restrict__ out_b, float* __restrict__ dq_acc, BwdParams prm, int* status) {
     constexpr bool kFused = MODE == 2;
+    // Head dimension 64 leaves 128 TMEM columns free behind dV and dK: dQ^T gets columns of its own there,
+    // so the next S^T / dP^T of a half need not wait until its dQ^T has been read and follow its
+    // accumulator MMAs directly, as in the two-pass kernels.
+    constexpr bool kDqOwn = kFused && HD == 64;
     constexpr bool kKeyStat = MODE != 1;           // keys stationary, queries streamed
     using L = BwdSmem<HD, kFused>;
     constexpr int kStages = L::kStages;
@@ -248,6 +274,8 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
     const uint32_t tmem_base = *tmem_slot_gen;
     const uint32_t tmem_x1 = tmem_base, tmem_x2 = tmem_base + 128u;
     const uint32_t tmem_acc_a = tmem_base + 256u, tmem_acc_b = tmem_base + 384u;
+    // dQ^T of warpgroup w (fused pass): over its dP^T columns, or (head_dim 64) behind dV / dK
+    const uint32_t tmem_dq[2] = {kDqOwn ? tmem_base + 320u : tmem_x2, kDqOwn ? tmem_base + 448u : tmem_x2 + (uint32_t)(kTile / 2)};
 
     if (warp < 4) {
     reg_dealloc<kBwdRegsIssue>();
@@ -323,7 +351,7 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
                 const uint32_t b = (uint32_t)dsm + (uint32_t)(w * (L::kDsBytes >> 4));
 #pragma unroll
                 for (int k = 0; k < kTile / 16; ++k)
-                    umma_f16_ss_lohi(tmem_x2 + (uint32_t)(w * kHalf), (uint32_t)ktd + (uint32_t)(k * 128), (uint32_t)(ktd >> 32),
+                    umma_f16_ss_lohi(tmem_dq[w], (uint32_t)ktd + (uint32_t)(k * 128), (uint32_t)(ktd >> 32),
                                      b + (uint32_t)(k * 128), (uint32_t)(dsm >> 32), kIdescDq, k != 0 ? 1u : 0u);
             };
             int stage = 0; uint32_t phase = 0;
@@ -346,6 +374,10 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
                     // next dP^T of this half (which overwrites it) is not held up (+2.5 %); at head_dim 64
                     // the MMAs are short and the order dV, dK, dQ^T measured 6 % faster.
                     constexpr bool kDqFirst = HD == 128;
+                    if (kDqOwn && it > 0) {       // the previous dQ^T of this half must have been read
+                        if (!(ok = mbar_wait(bar_dqfree + 8 * w, (uint32_t)(it - 1) & 1u, ctx, 25))) break;
+                        tc_fence_after_sync();
+                    }
                     if (kFused && kDqFirst) { issue_dq(w); umma_commit<1>(bar_dqfull + 8 * w); }
                     if (kKeyStat) issue_acc(tmem_acc_a, tmem_x1, 1, w, stage, it == 0 && w == 0);     // dV += P^T dO
                     if (kFused) {
@@ -355,10 +387,10 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
                         issue_acc(tmem_acc_b, tmem_x2, 0, w, stage, it == 0 && w == 0);                // dK += dS^T Q  /  dQ += dS K
                     }
                     if (w == 1) umma_commit<1>(bar_empty + 8 * stage);
-                    if (!kFused && more) { issue_x(w, nstage); umma_commit<1>(bar_xfull + 8 * w); }
+                    if ((!kFused || kDqOwn) && more) { issue_x(w, nstage); umma_commit<1>(bar_xfull + 8 * w); }
                 }
                 if (!ok) break;
-                if (kFused && more) {
+                if (kFused && !kDqOwn && more) {
                     // the next dP^T of a half overwrites its dQ^T: wait until the warpgroup has read it
 #pragma unroll
                     for (int w = 0; w < 2; ++w) {
@@ -473,8 +505,9 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
                 if (!ok) break;
                 tc_fence_after_sync();
                 uint32_t dq[64];
-                tmem_ld_32x32b_x32(tx2, *reinterpret_cast<uint32_t(*)[32]>(&dq[0]));
-                tmem_ld_32x32b_x32(tx2 + 32u, *reinterpret_cast<uint32_t(*)[32]>(&dq[32]));
+                const uint32_t tdq = tmem_dq[wg] + lane_off;
+                tmem_ld_32x32b_x32(tdq, *reinterpret_cast<uint32_t(*)[32]>(&dq[0]));
+                tmem_ld_32x32b_x32(tdq + 32u, *reinterpret_cast<uint32_t(*)[32]>(&dq[32]));
                 tmem_ld_wait();
                 tc_fence_before_sync();
                 __syncwarp();
@@ -549,6 +582,404 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Fused pass at head_dim <= 64, whole-tile form.  A tcgen05.mma of N = 64 or 128 (K = 16) costs the
+// issuing thread and the tensor pipe about the same ~65 clocks here, so the half-tile MMAs of the
+// template above (48 per tile pair at head_dim 64) are replaced by whole-tile ones where the
+// operands allow (S^T, dP^T, dQ^T with N = 128: 32 per tile pair), and TMEM has room for it:
+//   S^T/P^T 128 | dP^T 128 | dV 64 | dK 64 | dQ^T 128 columns.
+// dQ^T has columns of its own, so nothing waits for it to be read except the next dQ^T; dS^T is
+// double-buffered in shared memory (two SWIZZLE_128B images [128 keys][64 queries] per buffer, one
+// per warpgroup), so the warpgroups write tile i's while the MMAs still read tile i-1's.
+//   MMA order per query tile i: dV(i), S^T(i+1), dP^T(i+1), dK(i), dQ^T(i)
+//   warpgroup per tile i: exponentials -> P^T to TMEM; dS^T to shared memory; then, off the MMA
+//   thread's critical path, dQ^T(i-1) from TMEM into dq_acc with red.global.add.
+// The two warpgroups work in step on the two 64-query halves of the same tile; the tensor pipe is
+// kept busy by the order above (the next scores are issued before this tile's dK and dQ^T).
+template <int HD>
+struct FusedSmem {
+    static_assert(HD == 64, "the whole-tile fused pass is the head_dim <= 64 kernel");
+    static constexpr int kStages = 3;
+    static constexpr int kTileBytes = kTile * HD * 2;
+    static constexpr int kDsBytes = kTile * 128;                        // dS^T of one warpgroup: 128 keys x 64 queries, bf16
+    static constexpr int kOffStat = 0;                                  // K, V
+    static constexpr int kOffRing = 2 * kTileBytes;                     // kStages x (Q, dO)
+    static constexpr int kOffDs = kOffRing + kStages * 2 * kTileBytes;
+    static constexpr int kStageBytes = 64 * HD * 4;                     // dQ staging of one warpgroup: 64 queries x head_dim fp32
+    static constexpr int kOffStage = kOffDs + 2 * 2 * kDsBytes;         // (dS^T: two buffers x two warpgroups)
+    static constexpr int kOffBar = kOffStage + 2 * kStageBytes;
+    static constexpr int kOffStats = kOffBar + 256;                     // [warpgroup][64 lse2 | 64 delta]
+    static constexpr int kTotal = kOffStats + 2 * 128 * 4 + 1024;
+    static_assert(kTotal <= 227 * 1024, "shared memory budget exceeded");
+};
+
+template <int HD, typename OutT>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+fmha_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                      const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
+                      const float* __restrict__ lse2, const float* __restrict__ delta,
+                      OutT* __restrict__ out_dv, OutT* __restrict__ out_dk, float* __restrict__ dq_acc,
+                      BwdParams prm, int* status) {
+    using L = FusedSmem<HD>;
+    constexpr int kStages = L::kStages;
+    constexpr int kDBlocks = HD / 64;
+    constexpr int kHalf = kTile / 2;
+    constexpr uint32_t kIdescX = make_idesc_f16(kTile, kTile, true, 0, 0);      // both operands K-major
+    constexpr uint32_t kIdescAcc = make_idesc_f16(kTile, HD, true, 0, 1);       // B operand MN-major
+    constexpr uint32_t kIdescDq = make_idesc_f16(kTile, kTile, true, 1, 1);     // both operands MN-major
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t s_stat = base + L::kOffStat, s_ring = base + L::kOffRing, s_ds = base + L::kOffDs;
+    const uint32_t bars = base + L::kOffBar;
+    const uint32_t bar_stat = bars;                       // K, V have landed
+    const uint32_t bar_full = bars + 8;                   // [kStages]
+    const uint32_t bar_empty = bar_full + 8 * kStages;    // [kStages]
+    const uint32_t bar_sfull = bar_empty + 8 * kStages;   // S^T is in TMEM
+    const uint32_t bar_dpfull = bar_sfull + 8;            // dP^T is in TMEM
+    const uint32_t bar_pready = bar_dpfull + 8;           // P^T and dS^T are written (8 warps)
+    const uint32_t bar_dqfull = bar_pready + 8;           // dQ^T is in TMEM
+    const uint32_t bar_dqfree = bar_dqfull + 8;           // ... and has been read (8 warps)
+    const uint32_t bar_outfull = bar_dqfree + 8;          // dV, dK complete
+    const uint32_t s_tmem_slot = bar_outfull + 8;
+    const uint32_t s_abort = s_tmem_slot + 8;
+    float* stats_gen = reinterpret_cast<float*>(gen + L::kOffStats);
+    volatile uint32_t* tmem_slot_gen = (volatile uint32_t*)(gen + (s_tmem_slot - base));
+    volatile int* abort_gen = (volatile int*)(gen + (s_abort - base));
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    // Causal launches deal the key tiles out heaviest-first (tile 0 meets every query tile) across a
+    // group of 16 heads at a time, as the two-pass kernel does.
+    constexpr int kHeadGroup = 16;
+    int bh = (int)blockIdx.y;
+    int st = (int)blockIdx.x;
+    if (prm.causal) {
+        const int n_st = (int)gridDim.x;
+        const int lin = (int)blockIdx.x + n_st * (int)blockIdx.y;
+        const int grp = lin / (n_st * kHeadGroup);
+        const int rem = lin - grp * (n_st * kHeadGroup);
+        const int heads_here = min(kHeadGroup, (int)gridDim.y - grp * kHeadGroup);
+        st = rem / heads_here;
+        bh = grp * kHeadGroup + rem % heads_here;
+    }
+    const int st0 = st * kTile;
+    const int m_end = (prm.s_q + kTile - 1) / kTile;
+    const int m_begin = prm.causal ? min(max(st0 - prm.causal_offset, 0) / kTile, m_end) : 0;   // first query tile that sees key st0
+    const int n_iter = m_end - m_begin;
+
+    WaitCtx ctx{status, abort_gen, PB200_K_FLASH_ATTN_BWD};
+
+    if (threadIdx.x == 0) {
+        *abort_gen = 0;
+        mbar_init(bar_stat, 1);
+        for (int s = 0; s < kStages; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+        mbar_init(bar_sfull, 1); mbar_init(bar_dpfull, 1); mbar_init(bar_pready, 8);
+        mbar_init(bar_dqfull, 1); mbar_init(bar_dqfree, 8); mbar_init(bar_outfull, 1);
+        fence_mbarrier_init();
+        fence_proxy_async_smem();
+        prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v); prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_do);
+    }
+    if (warp == 1) {
+        tmem_alloc<1>(s_tmem_slot, 512);
+        tmem_relinquish<1>();
+    }
+    pdl_launch_dependents();
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    pdl_wait();
+    const uint32_t tmem_base = *tmem_slot_gen;
+    const uint32_t tmem_x1 = tmem_base, tmem_x2 = tmem_base + 128u;
+    const uint32_t tmem_dv = tmem_base + 256u, tmem_dk = tmem_base + 320u, tmem_dq = tmem_base + 384u;
+
+    if (warp < 4) {
+    reg_dealloc<kBwdRegsIssue>();
+    if (warp == 0) {
+        // ------------------------------- TMA producer -------------------------------
+        if (lane == 0 && n_iter > 0) {
+            mbar_arrive_expect_tx(bar_stat, (uint32_t)(2 * L::kTileBytes));
+            for (int db = 0; db < kDBlocks; ++db) {
+                tma_load_3d(s_stat + db * (kTile * 128), &tmap_k, bar_stat, db * 64, st0, bh);
+                tma_load_3d(s_stat + L::kTileBytes + db * (kTile * 128), &tmap_v, bar_stat, db * 64, st0, bh);
+            }
+            int stage = 0; uint32_t phase = 0;
+            for (int it = 0; it < n_iter; ++it) {
+                if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, ctx, 11)) break;
+                const uint32_t dst = s_ring + stage * 2 * L::kTileBytes;
+                mbar_arrive_expect_tx(bar_full + 8 * stage, (uint32_t)(2 * L::kTileBytes));
+                for (int db = 0; db < kDBlocks; ++db) {
+                    tma_load_3d(dst + db * (kTile * 128), &tmap_q, bar_full + 8 * stage, db * 64, (m_begin + it) * kTile, bh);
+                    tma_load_3d(dst + L::kTileBytes + db * (kTile * 128), &tmap_do, bar_full + 8 * stage, db * 64,
+                                (m_begin + it) * kTile, bh);
+                }
+                if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------- MMA issuer ---------------------------------
+        if (lane == 0 && n_iter > 0) {
+            bool ok = mbar_wait(bar_stat, 0, ctx, 21);
+            const uint64_t sd = make_desc_kmajor_sw128(s_stat);                      // K, V as K-major A
+            const uint64_t md = make_desc_kmajor_sw128(s_ring);                      // Q, dO as K-major B
+            const uint64_t bd = make_smem_desc(s_ring, kTile * 128, 1024, 2);        // Q, dO as MN-major B
+            const uint64_t ktd = make_smem_desc(s_stat, kTile * 128, 1024, 2);       // K as MN-major A (M = head_dim)
+            const uint64_t dsk = make_desc_kmajor_sw128(s_ds);                       // dS^T as K-major A
+            const uint64_t dsm = make_smem_desc(s_ds, L::kDsBytes, 1024, 2);         // dS^T as MN-major B, N = 128 queries
+            const uint32_t s_lo = (uint32_t)sd, s_hi = (uint32_t)(sd >> 32);
+            const uint32_t m_lo = (uint32_t)md, m_hi = (uint32_t)(md >> 32);
+            const uint32_t b_lo = (uint32_t)bd, b_hi = (uint32_t)(bd >> 32);
+            constexpr uint32_t kTileDesc = (uint32_t)(L::kTileBytes >> 4);
+            // X = stationary tile t . (streamed tile t)^T, contraction over head_dim: S^T (t = 0) or dP^T (t = 1)
+            auto issue_x = [&](int t, int stage) {
+                const uint32_t a = s_lo + (uint32_t)t * kTileDesc;
+                const uint32_t b = m_lo + (uint32_t)(stage * 2 + t) * kTileDesc;
+                const uint32_t d = t == 0 ? tmem_x1 : tmem_x2;
+#pragma unroll
+                for (int k = 0; k < HD / 16; ++k) {
+                    const uint32_t off = (uint32_t)((k >> 2) * (kTile * 8) + (k & 3) * 2);
+                    umma_f16_ss_lohi(d, a + off, s_hi, b + off, m_hi, kIdescX, k != 0 ? 1u : 0u);
+                }
+            };
+            // dV += P^T_w dO_w: P^T of warpgroup w from TMEM (head of its 64 columns), contraction over its 64 queries
+            auto issue_dv = [&](int w, int stage, bool first) {
+                const uint32_t b = b_lo + (uint32_t)(stage * 2 + 1) * kTileDesc + (uint32_t)(w * ((kHalf * 128) >> 4));
+#pragma unroll
+                for (int k = 0; k < kHalf / 16; ++k)
+                    umma_f16_ts_lohi(tmem_dv, tmem_x1 + (uint32_t)(w * kHalf + k * 8), b + (uint32_t)(k * 128), b_hi,
+                                     kIdescAcc, (first && k == 0) ? 0u : 1u);
+            };
+            // dK += dS^T_w Q_w: dS^T from shared memory (one 128-byte row of 64 queries per key)
+            auto issue_dk = [&](int w, int stage, int buf, bool first) {
+                const uint32_t a = (uint32_t)dsk + (uint32_t)((buf * 2 + w) * (L::kDsBytes >> 4));
+                const uint32_t b = b_lo + (uint32_t)(stage * 2) * kTileDesc + (uint32_t)(w * ((kHalf * 128) >> 4));
+#pragma unroll
+                for (int k = 0; k < kHalf / 16; ++k)
+                    umma_f16_ss_lohi(tmem_dk, a + (uint32_t)(k * 2), (uint32_t)(dsk >> 32), b + (uint32_t)(k * 128), b_hi,
+                                     kIdescAcc, (first && k == 0) ? 0u : 1u);
+            };
+            // dQ^T = K^T dS^T: contraction over the 128 keys, 16 per step (2048 bytes in both operands)
+            auto issue_dq = [&](int buf) {
+                const uint32_t b = (uint32_t)dsm + (uint32_t)(buf * 2 * (L::kDsBytes >> 4));
+#pragma unroll
+                for (int k = 0; k < kTile / 16; ++k)
+                    umma_f16_ss_lohi(tmem_dq, (uint32_t)ktd + (uint32_t)(k * 128), (uint32_t)(ktd >> 32),
+                                     b + (uint32_t)(k * 128), (uint32_t)(dsm >> 32), kIdescDq, k != 0 ? 1u : 0u);
+            };
+            int stage = 0; uint32_t phase = 0;
+            if (ok) ok = mbar_wait(bar_full, 0, ctx, 22);
+            if (ok) {
+                tc_fence_after_sync();
+                issue_x(0, 0); umma_commit<1>(bar_sfull);
+                issue_x(1, 0); umma_commit<1>(bar_dpfull);
+            }
+            for (int it = 0; it < n_iter && ok; ++it) {
+                int nstage = stage + 1; uint32_t nphase = phase;
+                if (nstage == kStages) { nstage = 0; nphase ^= 1u; }
+                const bool more = it + 1 < n_iter;
+                const uint32_t par = (uint32_t)it & 1u;
+                if (!(ok = mbar_wait(bar_pready, par, ctx, 23))) break;
+                tc_fence_after_sync();
+                issue_dv(0, stage, it == 0); issue_dv(1, stage, false);
+                if (more) {
+                    // S^T of the next query tile overwrites P^T, which the dV MMAs above read (issue order);
+                    // dP^T of this tile has been read by the warpgroups (they have arrived)
+                    if (!(ok = mbar_wait(bar_full + 8 * nstage, nphase, ctx, 24))) break;
+                    tc_fence_after_sync();
+                    issue_x(0, nstage); umma_commit<1>(bar_sfull);
+                    issue_x(1, nstage); umma_commit<1>(bar_dpfull);
+                }
+                issue_dk(0, stage, (int)par, it == 0); issue_dk(1, stage, (int)par, false);
+                umma_commit<1>(bar_empty + 8 * stage);
+                if (it > 0) {       // the previous dQ^T must have been read
+                    if (!(ok = mbar_wait(bar_dqfree, (uint32_t)(it - 1) & 1u, ctx, 25))) break;
+                    tc_fence_after_sync();
+                }
+                issue_dq((int)par); umma_commit<1>(bar_dqfull);
+                stage = nstage; phase = nphase;
+            }
+            if (ok) umma_commit<1>(bar_outfull);
+        }
+    }
+    } else {
+        reg_alloc<kBwdRegsMath>();
+        // ------------------------------- score math + epilogue -----------------------
+        const int wg = (warp - 4) >> 2;                  // which 64 queries of the streamed tile
+        const int q4 = warp & 3;                         // TMEM lane quarter
+        const int row_in_tile = q4 * 32 + lane;
+        const int srow = st0 + row_in_tile;              // key of this thread
+        const uint32_t lane_off = (uint32_t)(q4 * 32) << 16;
+        const uint32_t col0 = (uint32_t)(wg * 64);
+        const uint32_t tx1 = tmem_x1 + lane_off + col0, tx2 = tmem_x2 + lane_off + col0;
+        const float* lse2_bh = lse2 + (size_t)bh * prm.sq_pad;
+        const float* delta_bh = delta + (size_t)bh * prm.sq_pad;
+        const int wg_tid = (int)threadIdx.x - 128 - wg * 128;      // 0..127 inside the warpgroup
+        float* stats = stats_gen + wg * 128;             // 64 lse2 | 64 delta of this warpgroup's queries
+        bool ok = true;
+        // Thread t < 64 of the warpgroup carries lse2 of query t, thread t >= 64 delta of query t - 64:
+        // fetched one tile ahead, stored where no warp can still be reading the previous tile's
+        // (lse2 after the barrier that follows the exponentials, delta after the one that opens a tile).
+        const float* stat_src = (wg_tid < 64 ? lse2_bh : delta_bh - 64) + wg * 64 + wg_tid;
+        float nxt = 0.f;
+        if (n_iter > 0) {
+            if (wg_tid < 64) stats[wg_tid] = __ldg(stat_src + m_begin * kTile);
+            else nxt = __ldg(stat_src + m_begin * kTile);
+        }
+        // dQ^T of query tile itq: TMEM -> registers -> fp32 rows in the warpgroup's staging buffer -> dq_acc
+        // by a bulk reduction of the TMA engine (cp.reduce.async.bulk .add.f32, 16 KB).  lane = head-dim
+        // index, column = query: a warp stores 128 contiguous bytes per query (lanes past head_dim hold
+        // nothing).  Issuing the 64 red.global.add per thread instead kept both warpgroups' LSU path busy
+        // for ~1200 clk per tile in their serial path; the engine has the same throughput but costs the
+        // warps only the staging stores.
+        const uint32_t tdq = tmem_dq + lane_off + col0;
+        const uint32_t s_stage = base + L::kOffStage + (uint32_t)(wg * L::kStageBytes);
+        auto move_dq = [&](int itq) -> bool {
+            bool good = mbar_wait(bar_dqfull, (uint32_t)itq & 1u, ctx, 33);
+            good = __all_sync(0xffffffffu, good);
+            if (!good) return false;
+            tc_fence_after_sync();
+            uint32_t dq[64];
+            tmem_ld_32x32b_x32(tdq, *reinterpret_cast<uint32_t(*)[32]>(&dq[0]));
+            tmem_ld_32x32b_x32(tdq + 32u, *reinterpret_cast<uint32_t(*)[32]>(&dq[32]));
+            tmem_ld_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_dqfree);
+            if (wg_tid == 0) bulk_wait_read0();           // the previous reduction has read the staging buffer
+            named_barrier_sync(1 + wg, 128);
+            if (row_in_tile < HD) {
+#pragma unroll
+                for (int c = 0; c < 64; ++c) st_shared_b32(s_stage + (uint32_t)(c * HD + row_in_tile) * 4u, dq[c]);
+            }
+            fence_proxy_async_smem();
+            named_barrier_sync(1 + wg, 128);
+            if (wg_tid == 0) {
+                bulk_reduce_add_f32(dq_acc + ((size_t)bh * prm.sq_pad + (m_begin + itq) * kTile + wg * 64) * HD, s_stage,
+                                    (uint32_t)L::kStageBytes);
+                bulk_commit_group();
+            }
+            return true;
+        };
+        for (int it = 0; it < n_iter && ok; ++it) {
+            const int m0 = (m_begin + it) * kTile + wg * 64;      // first query of this thread's columns
+            const uint32_t par = (uint32_t)it & 1u;
+            const bool more = it + 1 < n_iter;
+            named_barrier_sync(1 + wg, 128);                      // lse2 of this tile is visible; delta of the previous one is no longer read
+            if (wg_tid >= 64) stats[wg_tid] = nxt;
+            if (more) nxt = __ldg(stat_src + (m_begin + it + 1) * kTile);
+            ok = mbar_wait(bar_sfull, par, ctx, 31);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after_sync();
+            // Causal: key <= query + offset.  No element of these 64 columns is hidden for this warp
+            // when its largest key is still seen by the smallest query.
+            const bool masked = prm.causal && (st0 + q4 * 32 + 31 > m0 + prm.causal_offset);
+            uint32_t sx[64];
+            tmem_ld_32x32b_x32(tx1, *reinterpret_cast<uint32_t(*)[32]>(&sx[0]));
+            tmem_ld_32x32b_x32(tx1 + 32u, *reinterpret_cast<uint32_t(*)[32]>(&sx[32]));
+            tmem_ld_wait();
+            reg_fence(sx);
+            // P^T = exp2(S^T scale - lse2[query]): per pair of columns one FFMA2 and two exponentials; kept in fp32
+            // (in place) for dS, rounded to bf16 for the dV operand.
+            {
+                uint32_t pp[32];
+#pragma unroll
+                for (int c2 = 0; c2 < 32; ++c2) {
+                    const float2 lv = reinterpret_cast<const float2*>(stats)[c2];
+                    float t0, t1, p0, p1;
+                    fma2v(t0, t1, __uint_as_float(sx[2 * c2]), __uint_as_float(sx[2 * c2 + 1]), prm.scale_log2, prm.scale_log2, -lv.x, -lv.y);
+                    if ((c2 & 7) < PB200_BWD_FMA_EXP_PAIRS) exp2_fma_pair(p0, p1, t0, t1);
+                    else { p0 = fast_exp2(t0); p1 = fast_exp2(t1); }
+                    if (masked) {
+                        const int mq = m0 + 2 * c2;
+                        if (srow > mq + prm.causal_offset) p0 = 0.f;
+                        if (srow > mq + 1 + prm.causal_offset) p1 = 0.f;
+                    }
+                    sx[2 * c2] = __float_as_uint(p0); sx[2 * c2 + 1] = __float_as_uint(p1);
+                    pp[c2] = pack_bf16(p0, p1);
+                }
+                tmem_st_32x32b_x32(tx1, pp);             // over the head of this warp's own S^T columns
+            }
+            ok = mbar_wait(bar_dpfull, par, ctx, 32);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after_sync();
+            uint32_t dp[64];
+            tmem_ld_32x32b_x32(tx2, *reinterpret_cast<uint32_t(*)[32]>(&dp[0]));
+            tmem_ld_32x32b_x32(tx2 + 32u, *reinterpret_cast<uint32_t(*)[32]>(&dp[32]));
+            tmem_ld_wait();
+            reg_fence(dp);
+            named_barrier_sync(1 + wg, 128);                      // every warp is past its exponentials: lse2 may be replaced
+            if (wg_tid < 64 && more) stats[wg_tid] = nxt;
+            // dS^T = P^T o (dP^T - delta[query]) -> this key's row of the warpgroup's SWIZZLE_128B image in
+            // buffer it & 1 (its previous readers, the dK and dQ^T MMAs of tile it - 2, retired before the
+            // dQ^T barrier this warp passed at the end of tile it - 1)
+            const uint32_t rowp = s_ds + (uint32_t)((par * 2 + wg) * L::kDsBytes) + (uint32_t)row_in_tile * 128u;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                uint32_t ds[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int c2 = 4 * j + i;
+                    const float2 dv = reinterpret_cast<const float2*>(stats + 64)[c2];
+                    float u0, u1, g0, g1;
+                    add2v(u0, u1, __uint_as_float(dp[2 * c2]), __uint_as_float(dp[2 * c2 + 1]), -dv.x, -dv.y);
+                    mul2v(g0, g1, __uint_as_float(sx[2 * c2]), __uint_as_float(sx[2 * c2 + 1]), u0, u1);
+                    ds[i] = pack_bf16(g0, g1);
+                }
+                st_shared_v4(rowp + (((uint32_t)j ^ (uint32_t)(row_in_tile & 7)) << 4), ds[0], ds[1], ds[2], ds[3]);
+            }
+            fence_proxy_async_smem();
+            tmem_st_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_pready);
+            // off the MMA thread's critical path: the previous tile's dQ^T
+            if (it > 0 && !(ok = move_dq(it - 1))) break;
+        }
+        if (ok && n_iter > 0) ok = move_dq(n_iter - 1);
+        if (wg_tid == 0) bulk_wait_all();                // the reductions must have completed before the CTA exits
+        if (!ok) named_barrier_arrive(1 + wg, 128);      // see the template above: nobody may wait for this warp for ever
+        // epilogue: dV, dK -> global, one key row per thread, each warpgroup half of head_dim
+        if (ok && n_iter > 0) {
+            ok = mbar_wait(bar_outfull, 0, ctx, 41);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        const bool row_exists = srow < prm.s_kv;
+        const size_t row_off = ((size_t)bh * prm.s_kv + srow) * prm.hd;
+#pragma unroll 1
+        for (int which = 0; which < 2; ++which) {
+            OutT* dst = (which == 0 ? out_dv : out_dk) + row_off;
+            const uint32_t acc = (which == 0 ? tmem_dv : tmem_dk) + lane_off;
+            const float mul = which == 0 ? 1.0f : prm.scale;
+#pragma unroll 1
+            for (int c = wg * (HD / 64); c < (wg + 1) * (HD / 64); ++c) {
+                uint32_t o[32];
+                if (ok && n_iter > 0) {
+                    tc_fence_after_sync();
+                    tmem_ld_32x32b_x32(acc + (uint32_t)(c * 32), o);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = 0u;                      // a key tile that no query attends to
+                }
+                if (!ok || !row_exists || c * 32 >= prm.hd) continue;
+                store_row_chunk(dst + c * 32, o, prm.hd - c * 32, mul);
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after_sync();
+        tmem_dealloc<1>(tmem_base, 512);
+    }
+}
+
+
 int tile_map(CUtensorMap* m, const void* p, int64_t hd, int64_t rows, int64_t bh, char* err) {
     uint64_t dims[3] = {(uint64_t)hd, (uint64_t)rows, (uint64_t)bh};
     uint64_t str[2] = {(uint64_t)hd * 2, (uint64_t)rows * hd * 2};
@@ -574,6 +1005,27 @@ int launch_pass(const CUtensorMap& s1, const CUtensorMap& s2, const CUtensorMap&
     cudaError_t e = launch_with_pdl(kernel, grid, dim3(kBwdThreads), L::kTotal, stream, s1, s2, m1, m2, lse2, delta,
                                     (OutT*)out_a, (OutT*)out_b, dq_acc, prm, device_status_ptr());
     if (e != cudaSuccess) { set_err(err, "attention backward launch failed (HD=%d mode=%d): %s", HD, MODE, cudaGetErrorString(e)); return PB200_ERR_LAUNCH; }
+    return PB200_OK;
+}
+
+template <int HD, typename OutT>
+int launch_fused(const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tq, const CUtensorMap& tdo,
+                 const float* lse2, const float* delta, void* dv, void* dk, float* dq_acc, const BwdParams& prm, int tiles,
+                 cudaStream_t stream, char* err) {
+    using L = FusedSmem<HD>;
+    auto kernel = fmha_bwd_fused_kernel<HD, OutT>;
+    static std::atomic<uint64_t> attr_set{0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!(attr_set.load(std::memory_order_relaxed) & (1ull << (dev & 63)))) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
+        if (e != cudaSuccess) { set_err(err, "cudaFuncSetAttribute(smem=%d): %s", L::kTotal, cudaGetErrorString(e)); return PB200_ERR_LAUNCH; }
+        attr_set.fetch_or(1ull << (dev & 63), std::memory_order_relaxed);
+    }
+    dim3 grid((unsigned)tiles, (unsigned)prm.bh, 1);
+    cudaError_t e = launch_with_pdl(kernel, grid, dim3(kBwdThreads), L::kTotal, stream, tk, tv, tq, tdo, lse2, delta,
+                                    (OutT*)dv, (OutT*)dk, dq_acc, prm, device_status_ptr());
+    if (e != cudaSuccess) { set_err(err, "attention backward launch failed (HD=%d fused): %s", HD, cudaGetErrorString(e)); return PB200_ERR_LAUNCH; }
     return PB200_OK;
 }
 
@@ -609,7 +1061,10 @@ int launch_bwd(const Record& r, cudaStream_t stream, void** p, char* err) {
     if (e != cudaSuccess) { set_err(err, "attention backward (row pass) launch failed: %s", cudaGetErrorString(e)); return PB200_ERR_LAUNCH; }
     const int kv_tiles = (int)((SKV + kTile - 1) / kTile), q_tiles = (int)((SQ + kTile - 1) / kTile);
     if (fused) {
-        if (int rc = launch_pass<HD, 2, OutT>(tk, tv, tq, tdo, lse2, delta, p[8], p[7], dq_acc, prm, kv_tiles, stream, err)) return rc;
+        int rc;
+        if constexpr (HD == 64) rc = launch_fused<64, OutT>(tk, tv, tq, tdo, lse2, delta, p[8], p[7], dq_acc, prm, kv_tiles, stream, err);
+        else rc = launch_pass<HD, 2, OutT>(tk, tv, tq, tdo, lse2, delta, p[8], p[7], dq_acc, prm, kv_tiles, stream, err);
+        if (rc) return rc;
         const size_t quads = (size_t)BH * SQ * (hd / 4);
         const unsigned blocks = (unsigned)std::min<size_t>((quads + 255) / 256, 148 * 16);
         fmha_bwd_dq_finish_kernel<OutT><<<blocks, 256, 0, stream>>>(dq_acc, (OutT*)p[6], (int)BH, (int)SQ, prm.sq_pad, (int)hd, HD, prm.scale);
@@ -640,7 +1095,7 @@ int plan_attention_bwd(Record& r, char* err) {
     g.block[0] = kBwdThreads; g.block[1] = g.block[2] = 1;
     g.cluster[0] = g.cluster[1] = g.cluster[2] = 1;
     const bool fused = !(r.flags & PB200_F_DETERMINISTIC);
-    g.smem_bytes = HD <= 64 ? (fused ? BwdSmem<64, true>::kTotal : BwdSmem<64, false>::kTotal)
+    g.smem_bytes = HD <= 64 ? (fused ? FusedSmem<64>::kTotal : BwdSmem<64, false>::kTotal)
                             : (fused ? BwdSmem<128, true>::kTotal : BwdSmem<128, false>::kTotal);
     g.n_inputs = 6; g.n_outputs = 3;
     // delta and lse * log2(e) per padded query; the fused pass adds the fp32 dQ accumulator (rows of the tile's head_dim)

@@ -9,8 +9,9 @@
 // forward here: bf16 operands, fp32 accumulation, P and dS rounded to bf16 before they become
 // MMA operands.
 //
-// ONE kernel template in three modes.  The default is the fused pass (MODE 2): five MMAs per tile
-// pair, dQ summed over key tiles with fp32 reductions into a scratch buffer (not bit-reproducible).
+// ONE kernel template in three modes, plus a whole-tile fused kernel for head_dim <= 64 (further
+// down).  The default is a fused pass (MODE 2 at head_dim > 64): five MMAs per tile pair, dQ summed
+// over key tiles with fp32 reductions into a scratch buffer (not bit-reproducible).
 // With PB200_F_DETERMINISTIC two passes run instead (MODE 0, then MODE 1), so that no gradient needs
 // atomics and the result is bit-reproducible, at seven MMAs per tile pair (S and dP formed twice):
 //   MODE 0 (dK, dV): a CTA owns 128 keys (K, V tiles stay in shared memory) and streams the query
@@ -182,10 +183,7 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
                 const float* __restrict__ lse2, const float* __restrict__ delta,
                 OutT* __restrict__ out_a, OutT* __restrict__ out_b, float* __restrict__ dq_acc, BwdParams prm, int* status) {
     constexpr bool kFused = MODE == 2;
-    // Head dimension 64 leaves 128 TMEM columns free behind dV and dK: dQ^T gets columns of its own there,
-    // so the next S^T / dP^T of a half need not wait until its dQ^T has been read and follow its
-    // accumulator MMAs directly, as in the two-pass kernels.
-    constexpr bool kDqOwn = kFused && HD == 64;
+    static_assert(!kFused || HD == 128, "head_dim <= 64 takes the whole-tile fused kernel below");
     constexpr bool kKeyStat = MODE != 1;           // keys stationary, queries streamed
     using L = BwdSmem<HD, kFused>;
     constexpr int kStages = L::kStages;
@@ -274,8 +272,8 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
     const uint32_t tmem_base = *tmem_slot_gen;
     const uint32_t tmem_x1 = tmem_base, tmem_x2 = tmem_base + 128u;
     const uint32_t tmem_acc_a = tmem_base + 256u, tmem_acc_b = tmem_base + 384u;
-    // dQ^T of warpgroup w (fused pass): over its dP^T columns, or (head_dim 64) behind dV / dK
-    const uint32_t tmem_dq[2] = {kDqOwn ? tmem_base + 320u : tmem_x2, kDqOwn ? tmem_base + 448u : tmem_x2 + (uint32_t)(kTile / 2)};
+    // dQ^T of warpgroup w (fused pass): over its own dP^T columns
+    const uint32_t tmem_dq[2] = {tmem_x2, tmem_x2 + (uint32_t)(kTile / 2)};
 
     if (warp < 4) {
     reg_dealloc<kBwdRegsIssue>();
@@ -370,27 +368,20 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap tmap_s1, const __grid_consta
                 for (int w = 0; w < 2; ++w) {
                     if (!(ok = mbar_wait(bar_pready + 8 * w, (uint32_t)it & 1u, ctx, 23))) break;
                     tc_fence_after_sync();
-                    // head_dim 128: dQ^T first, so that the warpgroup reads it while dV and dK run and the
-                    // next dP^T of this half (which overwrites it) is not held up (+2.5 %); at head_dim 64
-                    // the MMAs are short and the order dV, dK, dQ^T measured 6 % faster.
-                    constexpr bool kDqFirst = HD == 128;
-                    if (kDqOwn && it > 0) {       // the previous dQ^T of this half must have been read
-                        if (!(ok = mbar_wait(bar_dqfree + 8 * w, (uint32_t)(it - 1) & 1u, ctx, 25))) break;
-                        tc_fence_after_sync();
-                    }
-                    if (kFused && kDqFirst) { issue_dq(w); umma_commit<1>(bar_dqfull + 8 * w); }
+                    // Fused: dQ^T first, so that the warpgroup reads it while dV and dK run and the next dP^T
+                    // of this half (which overwrites it) is not held up (+2.5 % against dV, dK, dQ^T).
+                    if (kFused) { issue_dq(w); umma_commit<1>(bar_dqfull + 8 * w); }
                     if (kKeyStat) issue_acc(tmem_acc_a, tmem_x1, 1, w, stage, it == 0 && w == 0);     // dV += P^T dO
                     if (kFused) {
                         issue_dk_ss(w, stage, it == 0 && w == 0);
-                        if (!kDqFirst) { issue_dq(w); umma_commit<1>(bar_dqfull + 8 * w); }
                     } else {
                         issue_acc(tmem_acc_b, tmem_x2, 0, w, stage, it == 0 && w == 0);                // dK += dS^T Q  /  dQ += dS K
                     }
                     if (w == 1) umma_commit<1>(bar_empty + 8 * stage);
-                    if ((!kFused || kDqOwn) && more) { issue_x(w, nstage); umma_commit<1>(bar_xfull + 8 * w); }
+                    if (!kFused && more) { issue_x(w, nstage); umma_commit<1>(bar_xfull + 8 * w); }
                 }
                 if (!ok) break;
-                if (kFused && !kDqOwn && more) {
+                if (kFused && more) {
                     // the next dP^T of a half overwrites its dQ^T: wait until the warpgroup has read it
 #pragma unroll
                     for (int w = 0; w < 2; ++w) {
@@ -627,6 +618,9 @@ fmha_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
     constexpr uint32_t kIdescX = make_idesc_f16(kTile, kTile, true, 0, 0);      // both operands K-major
     constexpr uint32_t kIdescAcc = make_idesc_f16(kTile, HD, true, 0, 1);       // B operand MN-major
     constexpr uint32_t kIdescDq = make_idesc_f16(kTile, kTile, true, 1, 1);     // both operands MN-major
+    // Both warpgroups take their exponentials at the same time here, so the MUFU is the limit of that
+    // phase: 2 of every 8 score pairs use the FMA-pipe form (+3 %; 3 of 8 is slower again).
+    constexpr int kFmaExpPairs = 2;
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -889,7 +883,7 @@ fmha_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
                     const float2 lv = reinterpret_cast<const float2*>(stats)[c2];
                     float t0, t1, p0, p1;
                     fma2v(t0, t1, __uint_as_float(sx[2 * c2]), __uint_as_float(sx[2 * c2 + 1]), prm.scale_log2, prm.scale_log2, -lv.x, -lv.y);
-                    if ((c2 & 7) < PB200_BWD_FMA_EXP_PAIRS) exp2_fma_pair(p0, p1, t0, t1);
+                    if ((c2 & 7) < kFmaExpPairs) exp2_fma_pair(p0, p1, t0, t1);
                     else { p0 = fast_exp2(t0); p1 = fast_exp2(t1); }
                     if (masked) {
                         const int mq = m0 + 2 * c2;

@@ -161,6 +161,30 @@ def test_two_pass_form_is_bit_reproducible_and_fused_dk_dv_too():
     assert formulas.rel_fro(c[0], a[0]) < 1e-3
 
 
+@pytest.mark.parametrize("d", [64, 128])
+def test_fused_backward_replays_from_a_cuda_graph(d):
+    """The fused form clears its fp32 dQ accumulator inside the call (a memset node in the graph), so a
+    replay must give the gradients of the inputs as they are at replay time, every time."""
+    B, H, S = 1, 3, 384
+    q, k, v, do = _inputs(B, H, S, S, d)
+    fwd = build_flash_attention(B, H, S, S, d, causal=True, return_lse=True)
+    bwd = build_flash_attention_bwd(B, H, S, S, d, causal=True, out_dtype=f32)
+    qc, kc, vc, dc = q.cuda(), k.cuda(), v.cuda(), do.cuda()
+    o, lse = fwd(qc, kc, vc)
+    bwd(qc, kc, vc, o, lse, dc)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        dq, dk, dv = bwd(qc, kc, vc, o, lse, dc)
+    for scale in (2.0, -0.5):
+        dc.copy_(do.cuda() * scale)
+        g.replay()
+        torch.cuda.synchronize()
+        # delta = rowsum(O o dO) scales with dO, so all three gradients are linear in dO
+        ref = formulas.attention_bwd_ref(q, k, v, (do.float() * scale).to(torch.bfloat16), causal=True)
+        _check((dq.cpu(), dk.cpu(), dv.cpu()), ref)
+
+
 def test_no_device_wait_gave_up():
     from pyptx_b200 import _native
     _native.device_status()

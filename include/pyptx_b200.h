@@ -151,7 +151,9 @@ extern "C" {
  *   dims = {batch*heads, S_q, S_kv, head_dim}   fparams = {sm_scale (0 -> 1/sqrt(head_dim))}
  *   flags: PB200_F_CAUSAL, PB200_F_OUT_BF16 (dtype of dQ, dK, dV; default f32), PB200_F_DETERMINISTIC
  *   buffers: Q[BH,S_q,d], K[BH,S_kv,d], V[BH,S_kv,d], O[BH,S_q,d] bf16, lse[BH,S_q] f32, dO[BH,S_q,d] bf16
- *            -> dQ[BH,S_q,d], dK[BH,S_kv,d], dV[BH,S_kv,d], then scratch (geometry.scratch_bytes)   */
+ *            -> dQ[BH,S_q,d], dK[BH,S_kv,d], dV[BH,S_kv,d], then scratch (geometry.scratch_bytes)
+ *   The scratch needs no initialisation: the call writes its row statistics there and (default form)
+ *   clears the fp32 dQ accumulator it keeps there with a stream-ordered memset.                      */
 #define PB200_K_FLASH_ATTN_BWD 16
 
 /* ---- create-time flags -------------------------------------------------- */

@@ -378,17 +378,29 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
             // every P <= 2^8 is implied by a tile sum <= 2^8, which is the lazy-rescale invariant.  A
             // larger sum (the running maximum moved, or many scores sit just below 2^8) sends the
             // whole warp to the exact path below, which reads S again (nothing was stored yet).
-            bool slow = (j == 0) || diag || !PB200_FMHA_SPEC_MAX;
+            bool slow = diag || !PB200_FMHA_SPEC_MAX;
             bool forced = false;
             uint32_t packed[kKvTile / 2];
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
             if (!slow) {
-                const float neg_m = -m_used;
                 uint32_t v0[32], v1[32];
                 tmem_ld_32x32b_x32(ts, v0);
                 tmem_ld_32x32b_x32(ts + 32u, v1);
                 tmem_ld_wait();
                 reg_fence(v0); reg_fence(v1);
+                if (j == 0) {
+                    // First tile: O and l are empty, so any reference maximum is valid as long as no P
+                    // exceeds 2^8, which the sum check below verifies.  The maximum of the row's first 64
+                    // scores stands in for the row maximum (the exact path follows if it was too low).
+                    float e0 = -INFINITY, e1 = -INFINITY;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        e0 = fmax3(e0, __uint_as_float(v0[i]), __uint_as_float(v0[i + 1]));
+                        e1 = fmax3(e1, __uint_as_float(v1[i]), __uint_as_float(v1[i + 1]));
+                    }
+                    m_used = fmaxf(e0, e1) * prm.scale_log2;
+                }
+                const float neg_m = -m_used;
                 exp_chunk<kFmaExpPairsOf8<HD>>(v0, &packed[0], sum4, prm.scale_log2, neg_m);
                 tmem_ld_32x32b_x32(ts + 64u, v0);
                 exp_chunk<kFmaExpPairsOf8<HD>>(v1, &packed[16], sum4, prm.scale_log2, neg_m);

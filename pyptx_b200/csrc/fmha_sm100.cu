@@ -69,7 +69,10 @@ struct FmhaParams {
 
 template <int HD, bool P_SMEM>
 struct FmhaSmem {
-    static constexpr int kStages = HD == 64 ? 3 : 2;
+#ifndef PB200_FMHA_STAGES_D64
+#define PB200_FMHA_STAGES_D64 3
+#endif
+    static constexpr int kStages = HD == 64 ? PB200_FMHA_STAGES_D64 : 2;
     static constexpr int kQBytes = kQTile * HD * 2;          // per tile
     static constexpr int kKvBytes = kKvTile * HD * 2;        // per stage, K or V
     static constexpr int kPBytes = P_SMEM ? kQTile * kKvTile * 2 : 0;   // per tile

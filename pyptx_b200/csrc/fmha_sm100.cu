@@ -379,9 +379,10 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
             // Tiles that cross the diagonal (for any row of this warp) or the end of K/V take the masked path.
             const bool diag = (prm.causal && (key0 + kKvTile - 1 > q0 + t * kQTile + q * 32 + prm.causal_offset)) ||
                               (key0 + kKvTile > prm.s_kv);
-            // Fast path (every tile but the first, the diagonal and the ragged ones): the exponentials
-            // are taken against the reference maximum already in use, without a maximum pass and so
-            // without its serial dependency.  P stays in registers until the row sums say it is valid:
+            // Fast path (every unmasked tile; masked ones have a variant of their own further down, and a
+            // masked FIRST tile takes the exact path): the exponentials are taken against the reference
+            // maximum already in use (first tile: an estimate), without a maximum pass and so without its
+            // serial dependency.  P stays in registers until the row sums say it is valid:
             // every P <= 2^8 is implied by a tile sum <= 2^8, which is the lazy-rescale invariant.  A
             // larger sum (the running maximum moved, or many scores sit just below 2^8) sends the
             // whole warp to the exact path below, which reads S again (nothing was stored yet).

@@ -150,15 +150,20 @@ def test_large_scores_rescale_path(causal):
     check_bf16_matmul(o, formulas.attention_ref(q, k, v, causal=causal, sm_scale=1.0))
 
 
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("first_tile", [False, True])
 @pytest.mark.parametrize("d", [64, 128])
 @pytest.mark.parametrize("jump", [12.0, 60.0, 140.0, 400.0])
-def test_late_dominant_key_at_every_chunk_position(d, jump):
+def test_late_dominant_key_at_every_chunk_position(d, jump, first_tile, causal):
     """Interior K/V tiles are exponentiated against the maximum already in use and accepted only if
     the row sums stay small.  A key far above everything seen so far, placed in a later tile at each
     position of a 32-key chunk in turn (positions differ in whether the MUFU unit or the FMA-pipe
     polynomial, whose argument is clamped, evaluates them), must send the rows to the exact path.
     ``jump`` is the score gap in natural units: around the 2^8 acceptance bound, far above it, and
-    beyond what fp32 can exponentiate.  For the large gaps the output is that key's V row."""
+    beyond what fp32 can exponentiate.  For the large gaps the output is that key's V row.
+    ``first_tile`` puts the key into the second half of the FIRST tile instead, where the reference
+    maximum is an estimate from the tile's first 64 scores; ``causal`` makes the key's tile the
+    masked (diagonal) one for a third of the queries, which has a speculative path of its own."""
     B, H, S = 1, 1, 384
     g = torch.Generator().manual_seed(17)
     q = torch.zeros(B, H, S, d)
@@ -166,14 +171,15 @@ def test_late_dominant_key_at_every_chunk_position(d, jump):
     qb = q.to(torch.bfloat16)
     v = torch.randn(B, H, S, d, generator=g).to(torch.bfloat16)
     for pos in range(32):
-        hot = 128 + 32 + pos                         # a key of the second tile
+        hot = (64 if first_tile else 128) + 32 + pos     # a key of the first tile's second half / of the second tile
         k = torch.zeros(B, H, S, d)
         k[0, 0, hot, 0] = jump
         kb = k.to(torch.bfloat16)
-        o = _run(qb, kb, v, sm_scale=1.0)
-        check_bf16_matmul(o, formulas.attention_ref(qb, kb, v, sm_scale=1.0))
+        o = _run(qb, kb, v, sm_scale=1.0, causal=causal)
+        check_bf16_matmul(o, formulas.attention_ref(qb, kb, v, sm_scale=1.0, causal=causal))
         if jump >= 60.0:
-            assert formulas.rel_fro(o[0, 0], v[0, 0, hot].float().expand(S, d)) < 1e-2, pos
+            seen = slice(hot, S) if causal else slice(0, S)      # queries that see the key
+            assert formulas.rel_fro(o[0, 0, seen], v[0, 0, hot].float().expand(S, d)[seen]) < 1e-2, pos
 
 
 @pytest.mark.parametrize("causal", [False, True])
